@@ -1,0 +1,151 @@
+/* souffle_b200.h -- C ABI of libsouffle_b200.so (sm_100a).
+ *
+ * Drop-in boundary for the reference's fused global-sync kernels.  Every entry point takes
+ * plain device pointers and sizes (no torch types), is asynchronous on the given CUDA stream
+ * unless stated otherwise, returns 0 on success or a SouffleStatus code, and leaves a
+ * human-readable message in souffle_last_error() (thread-local).
+ *
+ * Reference interfaces replaced (paths relative to the reference project root):
+ *   cpp/bert/bert_binding.cu:23-535          souffle_bert_layer<1,12,384,64,3072>      -> souffle_bert_*
+ *   cpp/bert/bert_base_impl.cu:277-308       souffle_bert_base() (12-layer loop)       -> souffle_bert_* with n_layers=12
+ *   cpp/lstm/lstm_binding.cu:30-72           fused_lstm<1,10,256,100>                  -> souffle_lstm_*
+ *   cpp/swin_transformer/swin_transformer_binding.cu:155-209  swin_fused_feed_mlp      -> souffle_swin_mlp_forward
+ *   cpp/swin_transformer/swin_transformer_binding.cu:62-100   swin_ffn                 -> souffle_gemm_f16
+ *   cpp/swin_transformer/swin_trans_fc2_binding.cu:19-55      swin_trans_fc2           -> souffle_gemm_f16
+ *   cpp/souffle_utils/cuda_utils.h:11-19,86-98  checkCuda / check_compatability        -> status codes + souffle_last_error
+ */
+#ifndef SOUFFLE_B200_H_
+#define SOUFFLE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* souffle_stream_t; /* a cudaStream_t */
+
+typedef enum SouffleStatus {
+  SOUFFLE_OK = 0,
+  SOUFFLE_BAD_SHAPE = 1,       /* a dimension is unsupported (see each function) */
+  SOUFFLE_BAD_POINTER = 2,     /* null or misaligned (16 B) pointer */
+  SOUFFLE_BAD_DEVICE = 3,      /* not an sm_100 device, or no device */
+  SOUFFLE_NOT_CORESIDENT = 4,  /* the persistent grid would not be co-resident */
+  SOUFFLE_CUDA_ERROR = 5,      /* a CUDA runtime/driver call failed; message has the detail */
+  SOUFFLE_DEVICE_TIMEOUT = 6,  /* a bounded device-side wait expired (reported by souffle_*_status) */
+  SOUFFLE_BAD_ARGUMENT = 7
+} SouffleStatus;
+
+/* Message of the last failing call on this thread ("" if none). */
+const char* souffle_last_error(void);
+/* ABI version of this library (bumped on incompatible changes). */
+int souffle_abi_version(void);
+
+/* ------------------------------------------------------------------------------------------
+ * BERT encoder layers.  Replaces cpp/bert/bert_binding.cu:23-535 (one layer, compile-time
+ * 1x384x768) and the 12-layer loop of cpp/bert/bert_base_impl.cu:590-678 with one persistent
+ * launch over runtime shapes.
+ * ------------------------------------------------------------------------------------------ */
+typedef enum SouffleBertVariant {
+  SOUFFLE_BERT_STD = 0,        /* scale 1/sqrt(head_dim), additive length mask, tanh-GELU, biases, vector gamma/beta */
+  SOUFFLE_BERT_REF_COMPAT = 1  /* what the reference's fused kernel computes: scale 1/sqrt(hidden), ReLU,
+                                  no proj/FFN bias, LayerNorm without affine (fused_sqq_bert.cu:2934,
+                                  fused_sqq_feedforward.cu:2120-2133, bert_binding.cu:115) */
+} SouffleBertVariant;
+
+typedef struct SouffleBertDesc {
+  int32_t batch;      /* sequences per call */
+  int32_t seq;        /* tokens per sequence: multiple of 16, <= 128, or 256 / 384 */
+  int32_t heads;
+  int32_t head_dim;   /* 64 */
+  int32_t ffn;        /* intermediate size, multiple of 64 */
+  int32_t n_layers;   /* >= 1: layers chained inside one launch */
+  int32_t variant;    /* SouffleBertVariant */
+  int32_t keep_probs; /* 1: also materialise softmax probabilities of the LAST layer (parity output) */
+  float eps;          /* LayerNorm epsilon (applied in fp32) */
+  /* Optional tiling overrides, 0 = choose automatically. */
+  int32_t bn_qkv, bn_fc1, bn_proj, split_proj, bn_fc2, split_fc2;
+  int32_t max_ctas;   /* 0 = one CTA per SM */
+  int32_t timeout_ms; /* device-side wait limit, 0 = 2000 ms */
+} SouffleBertDesc;
+
+/* Device pointers to one layer's parameters, fp16.  Matrices use the reference's [K][N]
+ * row-major layout (cpp/bert/test_souffle_bert_layer.py:139-143).  Vectors may be null
+ * (bias = 0, gamma = 1, beta = 0). */
+typedef struct SouffleBertLayerWeights {
+  const void* qkv_w;  /* [3][H][H]  */
+  const void* qkv_b;  /* [3][H]     */
+  const void* proj_w; /* [H][H]     */
+  const void* proj_b; /* [H]        */
+  const void* ln1_g;  /* [H]        */
+  const void* ln1_b;  /* [H]        */
+  const void* fc1_w;  /* [H][F]     */
+  const void* fc1_b;  /* [F]        */
+  const void* fc2_w;  /* [F][H]     */
+  const void* fc2_b;  /* [H]        */
+  const void* ln2_g;  /* [H]        */
+  const void* ln2_b;  /* [H]        */
+} SouffleBertLayerWeights;
+
+typedef struct SouffleBertPlan SouffleBertPlan;
+
+/* Set-up (allocates the plan's device workspace, repacks the weights for the tensor cores and
+ * builds the stage program; synchronous, not on the hot path).  `layers` is a host array of
+ * desc->n_layers records.  The caller's weight buffers are not referenced afterwards. */
+int souffle_bert_plan_create(const SouffleBertDesc* desc, const SouffleBertLayerWeights* layers,
+                             SouffleBertPlan** plan_out);
+int souffle_bert_plan_destroy(SouffleBertPlan* plan);
+
+/* y[B*S][H] = encoder(x[B*S][H]); fp16 device buffers, 16-byte aligned.  `seq_lens` (device
+ * int32[B]) is optional: keys at positions >= len get the additive -10000 mask
+ * (cpp/bert/kernels/softmax.cu:22-24).  Asynchronous on `stream`; calls on one plan must not
+ * overlap. */
+int souffle_bert_forward(SouffleBertPlan* plan, const void* x, const int32_t* seq_lens, void* y,
+                         souffle_stream_t stream);
+/* Same with HOST buffers (pinned or pageable): copies x in, runs, copies y out, synchronises. */
+int souffle_bert_forward_host(SouffleBertPlan* plan, const void* x_host, const int32_t* seq_lens_host,
+                              void* y_host, souffle_stream_t stream);
+
+/* The stage outputs the reference binding returns (cpp/bert/bert_binding.cu:534), for the
+ * LAST layer of the plan.  Valid after a forward call has completed. */
+typedef enum SouffleBertBuffer {
+  SOUFFLE_BUF_QKV = 0,   /* fp16 [3][B][heads][S][d]            */
+  SOUFFLE_BUF_PROBS = 1, /* fp16 [B*heads][S][S] (keep_probs=1) */
+  SOUFFLE_BUF_CTX = 2,   /* fp16 [B*S][H]  attention value output, heads merged */
+  SOUFFLE_BUF_LN1 = 3,   /* fp16 [B*S][H]  post-LayerNorm attention block output */
+  SOUFFLE_BUF_FC1 = 4    /* fp16 [B*S][F]  post-activation FFN hidden */
+} SouffleBertBuffer;
+int souffle_bert_plan_buffer(SouffleBertPlan* plan, int which, void** ptr_out, size_t* bytes_out);
+
+/* Synchronises the plan's device and reports the device-side status of the last launch:
+ * SOUFFLE_OK, or SOUFFLE_DEVICE_TIMEOUT with the stage/CTA in souffle_last_error(). */
+int souffle_bert_plan_status(SouffleBertPlan* plan);
+/* Number of kernels launched by the last forward call and the persistent grid size. */
+int souffle_bert_plan_info(SouffleBertPlan* plan, int* launches_out, int* grid_out, int* n_stages_out);
+
+/* ------------------------------------------------------------------------------------------
+ * Plain fp16 GEMM with fp32 accumulation: c[M][N] = a[M][K] . w[K][N].
+ * Replaces swin_ffn (swin_transformer_binding.cu:62-100, shapes (256,2048,512),(256,512,2048))
+ * and swin_trans_fc2 (swin_trans_fc2_binding.cu:19-55) for any K % 64 == 0, N % 64 == 0.
+ * `workspace` must hold souffle_gemm_workspace_bytes() bytes and is reusable across calls
+ * that do not overlap.
+ * ------------------------------------------------------------------------------------------ */
+size_t souffle_gemm_workspace_bytes(void);
+int souffle_gemm_f16(const void* a, const void* w_kn, void* c, int32_t M, int32_t N, int32_t K,
+                     void* workspace, size_t workspace_bytes, souffle_stream_t stream);
+
+/* fc1 -> grid barrier -> fc2 in one launch, no bias/activation, both results returned:
+ * hidden[M][F] = src[M][C] . fc1_w[C][F];  out[M][C] = hidden . fc2_w[F][C]
+ * (cpp/swin_transformer/swin_transformer_binding.cu:155-209). */
+int souffle_swin_mlp_forward(const void* src, const void* fc1_w, const void* fc2_w, void* hidden, void* out,
+                             int32_t M, int32_t C, int32_t F, void* workspace, size_t workspace_bytes,
+                             souffle_stream_t stream);
+
+/* Blocks until `stream` is idle, then decodes the status words in `workspace`. */
+int souffle_workspace_status(void* workspace, souffle_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SOUFFLE_B200_H_ */

@@ -1,0 +1,161 @@
+"""Host-side mirror of the reference's BERT bindings over the C ABI.
+
+`souffle_bert_layer` keeps the name, positional signature and six-tensor return of
+cpp/bert/bert_binding.cu:23-46,534-540; `BertEncoder` is the plan-based interface the
+benchmark configs use (any batch, 1..12 layers, length masks).  torch is used only for
+device memory and streams.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from . import _lib
+
+STD, REF_COMPAT = 0, 1
+_BUF = dict(qkv=0, probs=1, ctx=2, ln1=3, fc1=4)
+_VEC_KEYS = ("qkv_b", "proj_b", "ln1_g", "ln1_b", "fc1_b", "fc2_b", "ln2_g", "ln2_b")
+_MAT_KEYS = ("qkv_w", "proj_w", "fc1_w", "fc2_w")
+
+
+def _stream_ptr() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check_f16_cuda(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor")
+    if t.dtype != torch.float16:
+        raise ValueError(f"{name} must be float16")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+
+
+class BertEncoder:
+    """A plan: `n_layers` encoder layers of fixed (batch, seq) fused into one launch."""
+
+    def __init__(self, batch: int, seq: int, heads: int, head_dim: int, ffn: int,
+                 layers: Sequence[Dict[str, torch.Tensor]], variant: int = STD, eps: Optional[float] = None,
+                 keep_probs: bool = False, tuning: Optional[Dict[str, int]] = None):
+        lib = _lib.load()
+        self.batch, self.seq, self.heads, self.head_dim, self.ffn = batch, seq, heads, head_dim, ffn
+        self.hidden = heads * head_dim
+        self.variant = variant
+        if eps is None:
+            eps = 1e-12 if variant == STD else 1e-5
+        d = _lib.BertDesc(batch=batch, seq=seq, heads=heads, head_dim=head_dim, ffn=ffn, n_layers=len(layers),
+                          variant=variant, keep_probs=int(keep_probs), eps=eps)
+        for k, v in (tuning or {}).items():
+            setattr(d, k, v)
+        arr = (_lib.BertLayerWeights * len(layers))()
+        for i, w in enumerate(layers):
+            for k in _MAT_KEYS:
+                _check_f16_cuda(w[k], k)
+                setattr(arr[i], k, w[k].data_ptr())
+            for k in _VEC_KEYS:
+                t = w.get(k)
+                if t is not None:
+                    _check_f16_cuda(t, k)
+                setattr(arr[i], k, t.data_ptr() if t is not None else None)
+        self._h = C.c_void_p()
+        _lib.check(lib.souffle_bert_plan_create(C.byref(d), arr, C.byref(self._h)))
+        self._lib = lib
+
+    def close(self) -> None:
+        if getattr(self, "_h", None) is not None and self._h.value:
+            self._lib.souffle_bert_plan_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def forward(self, x: torch.Tensor, seq_lens: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """x: fp16 CUDA [B,S,H] (or [B*S,H]); seq_lens: int32 CUDA [B] or None.  Asynchronous."""
+        _check_f16_cuda(x, "x")
+        if x.numel() != self.batch * self.seq * self.hidden:
+            raise ValueError(f"x has {x.numel()} elements, plan expects {self.batch}x{self.seq}x{self.hidden}")
+        if out is None:
+            out = torch.empty_like(x)
+        lens_ptr = None
+        if seq_lens is not None:
+            if seq_lens.dtype != torch.int32 or not seq_lens.is_cuda or seq_lens.numel() != self.batch:
+                raise ValueError("seq_lens must be an int32 CUDA tensor of length batch")
+            lens_ptr = seq_lens.data_ptr()
+        _lib.check(self._lib.souffle_bert_forward(self._h, x.data_ptr(), lens_ptr, out.data_ptr(), _stream_ptr()))
+        return out
+
+    def forward_host(self, x_host: torch.Tensor, seq_lens_host: Optional[torch.Tensor], y_host: torch.Tensor) -> None:
+        """Host buffers in and out (pinned preferred); synchronous."""
+        lens_ptr = seq_lens_host.data_ptr() if seq_lens_host is not None else None
+        _lib.check(self._lib.souffle_bert_forward_host(self._h, x_host.data_ptr(), lens_ptr, y_host.data_ptr(),
+                                                       _stream_ptr()))
+
+    def status(self) -> None:
+        """Synchronises and raises SouffleError if a device-side wait expired."""
+        _lib.check(self._lib.souffle_bert_plan_status(self._h))
+
+    def info(self) -> Dict[str, int]:
+        a, b, c = C.c_int(), C.c_int(), C.c_int()
+        _lib.check(self._lib.souffle_bert_plan_info(self._h, C.byref(a), C.byref(b), C.byref(c)))
+        return dict(launches=a.value, grid=b.value, stages=c.value)
+
+    def buffer(self, name: str) -> torch.Tensor:
+        """Copy of a last-layer stage output (see SouffleBertBuffer in the header)."""
+        ptr, nbytes = C.c_void_p(), C.c_size_t()
+        _lib.check(self._lib.souffle_bert_plan_buffer(self._h, _BUF[name], C.byref(ptr), C.byref(nbytes)))
+        B, S, h, d, H, F = self.batch, self.seq, self.heads, self.head_dim, self.hidden, self.ffn
+        shape = dict(qkv=(3, B, h, S, d), probs=(B * h, S, S), ctx=(B * S, H), ln1=(B * S, H), fc1=(B * S, F))[name]
+        out = torch.empty(shape, dtype=torch.float16, device="cuda")
+        assert out.numel() * 2 == nbytes.value
+        torch.cuda.current_stream().synchronize()
+        rc = torch.cuda.cudart().cudaMemcpy(out.data_ptr(), ptr.value, nbytes.value, 3)  # device to device
+        if int(rc) != 0:
+            raise _lib.SouffleError(5, f"cudaMemcpy failed with {int(rc)}")
+        return out
+
+
+_layer_cache: Dict[tuple, BertEncoder] = {}
+
+
+def souffle_bert_layer(src: torch.Tensor, qkv_weight: torch.Tensor, attn_fc_weight: torch.Tensor,
+                       feed_forward_fc1_weight: torch.Tensor, feed_forward_fc2_weight: torch.Tensor,
+                       opt_level: int) -> List[torch.Tensor]:
+    """Drop-in for bert_binding.souffle_bert_layer (cpp/bert/bert_binding.cu:23-46, 534).
+
+    src [1,S,768] fp16, weights in [K][N] layout; returns [output_qkv, query_key_output,
+    attn_value_output, attn_fc_output, feed_forward_fc1_output, feed_forward_fc2_output].
+    Computes what the reference's fused kernels compute (REF_COMPAT variant).  Every
+    opt_level 0..4 runs the same single fused launch; other values raise, where the reference
+    prints and returns zeros (bert_binding.cu:529-531).  The plan (repacked weights) is cached
+    on the weights' addresses and versions.
+    """
+    if opt_level not in (0, 1, 2, 3, 4):
+        raise ValueError(f"opt level {opt_level} not supported")
+    for name, t in (("src", src), ("qkv_weight", qkv_weight), ("attn_fc_weight", attn_fc_weight),
+                    ("feed_forward_fc1_weight", feed_forward_fc1_weight),
+                    ("feed_forward_fc2_weight", feed_forward_fc2_weight)):
+        _check_f16_cuda(t, name)
+    B, S, H = src.shape
+    F = feed_forward_fc1_weight.shape[1]
+    heads = H // 64
+    key = (B, S, H, F) + tuple((t.data_ptr(), t._version) for t in
+                               (qkv_weight, attn_fc_weight, feed_forward_fc1_weight, feed_forward_fc2_weight))
+    enc = _layer_cache.get(key)
+    if enc is None:
+        if len(_layer_cache) >= 4:
+            _layer_cache.pop(next(iter(_layer_cache))).close()
+        w = dict(qkv_w=qkv_weight, proj_w=attn_fc_weight, fc1_w=feed_forward_fc1_weight,
+                 fc2_w=feed_forward_fc2_weight)
+        enc = BertEncoder(B, S, heads, 64, F, [w], variant=REF_COMPAT, keep_probs=True)
+        _layer_cache[key] = enc
+    out = enc.forward(src).reshape(B * S, H)
+    torch.cuda.current_stream().synchronize()      # the reference call is blocking (bert_binding.cu:532)
+    enc.status()
+    return [enc.buffer("qkv").reshape(3 * B, heads, S, 64), enc.buffer("probs"), enc.buffer("ctx"),
+            enc.buffer("ln1"), enc.buffer("fc1"), out]

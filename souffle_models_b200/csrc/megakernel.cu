@@ -1,0 +1,672 @@
+// Persistent global-sync megakernel for sm_100a.
+//
+// One CTA per SM interprets a stage program (stage_program.h).  Dense contractions run on
+// tcgen05.mma with fp32 accumulators in tensor memory, operands arrive by TMA into a
+// 128B-swizzled shared-memory ring, and the softmax / LayerNorm / GELU epilogues read the
+// accumulators straight out of TMEM.  Stages are separated by a bounded grid barrier.
+//
+// Reference behaviour covered (paths relative to the reference project root):
+//   cpp/bert/kernels/fused_sqq_bert.cu:34-2305   whole encoder layer in one cooperative launch
+//   cpp/bert/kernels/fused_sqq_bert.cu:2308-3785 attention half (QKV, QK^T, softmax, PV, proj, LN)
+//   cpp/bert/kernels/fused_sqq_feedforward.cu:1728-2617 FFN half (FC1+act, FC2+residual, LN)
+//   cpp/swin_transformer/kernels/swin_fused_ffn_m256n2048k512_m256n512k2048.cu:9-769 fc1 -> fc2
+//   cpp/swin_transformer/kernels/gemm_three_stages.h:8-379 and kernels/gemm_k6.cu:9-339 single GEMMs
+//
+// Warp roles (192 threads): warp 0 = TMA producer (one elected lane), warp 1 = MMA issuer and
+// TMEM owner, warps 2..5 = epilogue / softmax (warp w reads TMEM lanes 32*(w%4) .. +31).
+// Every wait (mbarrier, grid barrier) is bounded by a wall-clock deadline; on expiry the CTA
+// records a status word, drains and returns, so a fault never leaves the GPU spinning.
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "sm100_ptx.cuh"
+#include "stage_program.h"
+
+namespace souffle {
+
+constexpr int kThreads = 192;
+constexpr int kRingBytes = 212992;          // 208 KiB operand ring (4 x 48 KiB or 6 x 32 KiB slots)
+constexpr int kCtlBytes = 1024;             // barriers + control words
+constexpr int kSmemBytes = kCtlBytes + kRingBytes + 1024;  // + alignment slack
+constexpr int kMaxSlots = 8;
+constexpr uint32_t kTmemCols = 512;
+constexpr int kATileBytes = 128 * 64 * 2;   // 128 rows x 64 halves
+constexpr int kAccStride = 256;             // TMEM columns between the two accumulator buffers
+constexpr int kOCol = 384;                  // TMEM column of the attention output accumulator
+
+struct MegaParams {
+  const Stage* stages;        // plan-owned stage list, or null to use the inline stages
+  int n_stages;
+  const CUtensorMap* maps;    // plan-owned tensor maps (indices >= 0)
+  const void* x;
+  void* y;
+  const int* lens;
+  unsigned* sync;       // [0] arrival count, [1] generation used by this launch
+  unsigned* sync_next;  // the pair the next launch will use; cleared by this launch
+  int* status;        // [0] code, [1] where, [2] cta
+  unsigned long long timeout_ns;
+};
+
+// Everything a launch needs, passed in parameter space: per-call tensor maps (negative map
+// indices: -1 -> call_maps[0], -2 -> call_maps[1], ...), up to two inline stages for the
+// plan-less entry points, and the pointers above.
+constexpr int kCallMaps = 4;
+struct CallArgs {
+  CUtensorMap call_maps[kCallMaps];
+  Stage inline_stages[2];
+  MegaParams p;
+};
+__device__ __forceinline__ const CUtensorMap* map_ptr(const CallArgs& a, int idx) {
+  return idx < 0 ? &a.call_maps[-idx - 1] : a.p.maps + idx;
+}
+
+struct __align__(8) SmemCtl {
+  uint64_t full[kMaxSlots];
+  uint64_t empty[kMaxSlots];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint64_t qk_full, qk_empty, v_full, v_empty, s_full, p_full, o_full;
+  uint32_t tmem_base;
+  int abort;
+  Stage stage;        // current stage, copied once per stage
+};
+static_assert(sizeof(SmemCtl) <= kCtlBytes, "control block too large");
+
+// Per-thread view of the pipelines; identical arithmetic in every role keeps them in step.
+struct RoleState {
+  uint32_t slot = 0;       // next ring slot
+  uint32_t slot_bits = 0;  // phase bit per ring slot
+  uint32_t acc = 0;        // next accumulator buffer
+  uint32_t acc_bits = 0;   // phase bit per accumulator buffer
+  uint32_t attn_bit = 0;   // phase bit of the attention barriers
+};
+
+__device__ __forceinline__ const void* sel_ptr(int sel, const void* plan, const MegaParams& p) {
+  return sel == PTR_CALL_X ? p.x : (sel == PTR_CALL_Y ? (const void*)p.y : plan);
+}
+
+// ------------------------------------------------------------------------------------
+// grid barrier: sense by generation, self-resetting, bounded
+// ------------------------------------------------------------------------------------
+__device__ bool grid_barrier(const MegaParams& p, const WaitCtl& ctl, int where) {
+  __threadfence();
+  fence_proxy_async();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned* count = p.sync;
+    unsigned* gen = p.sync + 1;
+    const unsigned g = ld_acquire_u32(gen);
+    const unsigned prev = atom_add_release_u32(count, 1u);
+    if (prev == gridDim.x - 1) {
+      *reinterpret_cast<volatile unsigned*>(count) = 0u;
+      st_release_u32(gen, g + 1u);
+    } else {
+      uint32_t spins = 0;
+      while (ld_acquire_u32(gen) == g) {
+        if (((++spins) & 0x3F) == 0) {
+          if (*ctl.abort_smem) break;
+          if (globaltimer_ns() > ctl.deadline_ns) {
+            record_timeout(ctl, DEV_TIMEOUT_GRID, where);
+            break;
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+  fence_proxy_async();
+  return *ctl.abort_smem == 0;
+}
+
+// ------------------------------------------------------------------------------------
+// GEMM stage
+// ------------------------------------------------------------------------------------
+struct GemmGeom {
+  int tiles_n, splitk, items, kchunks, bn, slot_bytes, nslots;
+};
+__device__ __forceinline__ GemmGeom gemm_geom(const Stage& st) {
+  GemmGeom g;
+  g.bn = st.bn;
+  g.tiles_n = st.N / st.bn;
+  g.splitk = st.splitk;
+  g.items = ((st.M + 127) / 128) * g.tiles_n * g.splitk;
+  g.kchunks = st.K / 64 / st.splitk;
+  g.slot_bytes = kATileBytes + st.bn * 128;
+  int n = kRingBytes / g.slot_bytes;
+  g.nslots = n > kMaxSlots ? kMaxSlots : n;
+  return g;
+}
+
+template <int NC>
+__device__ __forceinline__ void epilogue_chunk(const Stage& st, const MegaParams& p, const uint32_t* r, int row,
+                                               int col, int ks, bool valid) {
+  if (st.epi == EPI_PARTIAL) {
+    if (valid) {
+      float4* dst = reinterpret_cast<float4*>(st.partial + ((size_t)ks * st.M + row) * st.N + col);
+#pragma unroll
+      for (int i = 0; i < NC / 4; ++i)
+        dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                             __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+    }
+    return;
+  }
+  float v[NC];
+#pragma unroll
+  for (int i = 0; i < NC; ++i) v[i] = __uint_as_float(r[i]);
+  if (st.bias) {
+    const uint4* b4 = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(st.bias) + col);
+#pragma unroll
+    for (int i = 0; i < NC / 8; ++i) {
+      const uint4 u = __ldg(b4 + i);
+      const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(h[j]);
+        v[8 * i + 2 * j] += f.x;
+        v[8 * i + 2 * j + 1] += f.y;
+      }
+    }
+  }
+  if (st.act == ACT_RELU) {
+#pragma unroll
+    for (int i = 0; i < NC; ++i) v[i] = fmaxf(v[i], 0.0f);
+  } else if (st.act == ACT_GELU) {
+#pragma unroll
+    for (int i = 0; i < NC; ++i) v[i] = gelu_tanh(v[i]);
+  }
+  if (!valid) return;
+  const __half* resid = reinterpret_cast<const __half*>(sel_ptr(st.resid_sel, st.resid, p));
+  if (resid) {
+    const uint4* r4 = reinterpret_cast<const uint4*>(resid + (size_t)row * st.ldo + col);
+#pragma unroll
+    for (int i = 0; i < NC / 8; ++i) {
+      const uint4 u = r4[i];
+      const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(h[j]);
+        v[8 * i + 2 * j] += f.x;
+        v[8 * i + 2 * j + 1] += f.y;
+      }
+    }
+  }
+  __half* out = reinterpret_cast<__half*>(const_cast<void*>(sel_ptr(st.out_sel, st.out, p)));
+  __half* dst;
+  if (st.epi == EPI_QKV) {
+    const int hidden = st.heads * st.head_dim;
+    const int j = col / hidden, rem = col - j * hidden;
+    const int hh = rem / st.head_dim, dd = rem - hh * st.head_dim;
+    const int b = row / st.seq, s = row - b * st.seq;
+    dst = out + ((((size_t)j * st.batch + b) * st.heads + hh) * st.seq + s) * st.head_dim + dd;
+  } else {
+    dst = out + (size_t)row * st.ldo + col;
+  }
+  uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+  for (int i = 0; i < NC / 8; ++i)
+    d4[i] = make_uint4(pack_h2(v[8 * i], v[8 * i + 1]), pack_h2(v[8 * i + 2], v[8 * i + 3]),
+                       pack_h2(v[8 * i + 4], v[8 * i + 5]), pack_h2(v[8 * i + 6], v[8 * i + 7]));
+}
+
+__device__ void gemm_stage(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s,
+                           uint32_t ring, RoleState& rs, const WaitCtl& ctl, int warp, int lane) {
+  const MegaParams& p = ca.p;
+  const GemmGeom g = gemm_geom(st);
+  if (rs.slot >= (uint32_t)g.nslots) rs.slot = 0;
+  const uint32_t full0 = smem_u32(&ctl_s.full[0]), empty0 = smem_u32(&ctl_s.empty[0]);
+  const uint32_t tfull0 = smem_u32(&ctl_s.tmem_full[0]), tempty0 = smem_u32(&ctl_s.tmem_empty[0]);
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      const CUtensorMap* tmA = map_ptr(ca, st.tm_a);
+      const CUtensorMap* tmB = map_ptr(ca, st.tm_b);
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < g.items; item += gridDim.x) {
+        const int ks = item % g.splitk;
+        const int nt = (item / g.splitk) % g.tiles_n;
+        const int mt = item / (g.splitk * g.tiles_n);
+        for (int kc = 0; kc < g.kchunks; ++kc) {
+          const uint32_t s = rs.slot;
+          if (!mbar_wait(empty0 + 8 * s, ((rs.slot_bits >> s) & 1u) ^ 1u, ctl, 100 + (int)s)) { ok = false; break; }
+          const uint32_t fb = full0 + 8 * s;
+          mbar_expect_tx(fb, (uint32_t)g.slot_bytes);
+          const uint32_t a_dst = ring + s * g.slot_bytes, b_dst = a_dst + kATileBytes;
+          const int k0 = (ks * g.kchunks + kc) * 64;
+          tma_load_2d(a_dst, tmA, fb, k0, mt * 128);
+          if (!st.b_mn_major) {
+            tma_load_2d(b_dst, tmB, fb, k0, nt * g.bn);
+          } else {
+            for (int j = 0; j < g.bn / 64; ++j) tma_load_2d(b_dst + j * 8192, tmB, fb, nt * g.bn + j * 64, k0);
+          }
+          rs.slot_bits ^= 1u << s;
+          rs.slot = (s + 1 == (uint32_t)g.nslots) ? 0 : s + 1;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_f16((uint32_t)g.bn, (uint32_t)st.b_mn_major);
+      const uint32_t tmem = ctl_s.tmem_base;
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < g.items; item += gridDim.x) {
+        const uint32_t acc = rs.acc;
+        if (!mbar_wait(tempty0 + 8 * acc, ((rs.acc_bits >> acc) & 1u) ^ 1u, ctl, 200 + (int)acc)) break;
+        tc_fence_after_sync();
+        const uint32_t d = tmem + acc * kAccStride;
+        for (int kc = 0; kc < g.kchunks; ++kc) {
+          const uint32_t s = rs.slot;
+          if (!mbar_wait(full0 + 8 * s, (rs.slot_bits >> s) & 1u, ctl, 300 + (int)s)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_addr = ring + s * g.slot_bytes, b_addr = a_addr + kATileBytes;
+          const uint64_t ad = umma_desc_sw128(a_addr, 16, 1024);
+          const uint64_t bd = st.b_mn_major ? umma_desc_sw128(b_addr, 8192, 1024) : umma_desc_sw128(b_addr, 16, 1024);
+          const uint32_t bstep = st.b_mn_major ? 128u : 2u;   // 16 K-rows = 2048 B, or 16 halves = 32 B
+#pragma unroll
+          for (uint32_t k = 0; k < 4; ++k)
+            umma_f16(d, ad + 2u * k, bd + bstep * k, idesc, (uint32_t)((kc | (int)k) != 0));
+          umma_commit(empty0 + 8 * s);
+          rs.slot_bits ^= 1u << s;
+          rs.slot = (s + 1 == (uint32_t)g.nslots) ? 0 : s + 1;
+        }
+        if (!ok) break;
+        umma_commit(tfull0 + 8 * acc);
+        rs.acc_bits ^= 1u << acc;
+        rs.acc ^= 1u;
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue: TMEM -> registers -> global ----------------
+    const int q = warp & 3;
+    const uint32_t tmem = ctl_s.tmem_base + ((uint32_t)(q * 32) << 16);
+    for (int item = blockIdx.x; item < g.items; item += gridDim.x) {
+      const int ks = item % g.splitk;
+      const int nt = (item / g.splitk) % g.tiles_n;
+      const int mt = item / (g.splitk * g.tiles_n);
+      const uint32_t acc = rs.acc;
+      bool ok = mbar_wait(tfull0 + 8 * acc, (rs.acc_bits >> acc) & 1u, ctl, 400 + (int)acc);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int row = mt * 128 + q * 32 + lane;
+      const bool valid = row < st.M;
+      const uint32_t t0 = tmem + acc * kAccStride;
+      int c0 = 0;
+      for (; c0 + 32 <= g.bn; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(t0 + c0, r);
+        tmem_ld_wait();
+        epilogue_chunk<32>(st, p, r, row, nt * g.bn + c0, ks, valid);
+      }
+      if (c0 < g.bn) {
+        uint32_t r[16];
+        tmem_ld16(t0 + c0, r);
+        tmem_ld_wait();
+        epilogue_chunk<16>(st, p, r, row, nt * g.bn + c0, ks, valid);
+      }
+      tc_fence_before_sync();
+      mbar_arrive(tempty0 + 8 * acc);
+      rs.acc_bits ^= 1u << acc;
+      rs.acc ^= 1u;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// attention stage: one work item = (sequence, head, 128-query tile); S <= 384, head_dim 64
+// ------------------------------------------------------------------------------------
+__device__ void attn_stage(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, uint32_t ring, uint8_t* ring_ptr,
+                           RoleState& rs, const WaitCtl& ctl, int warp, int lane) {
+  const MegaParams& p = ca.p;
+  const int S = st.seq, B = st.batch, H = st.heads;
+  const int n_kb = (S + 127) / 128;
+  const int items = B * H * n_kb;
+  const uint32_t q_off = 0, k_off = kATileBytes, v_off = k_off + n_kb * kATileBytes,
+                 p_off = v_off + n_kb * kATileBytes;
+  const uint32_t qk_full = smem_u32(&ctl_s.qk_full), qk_empty = smem_u32(&ctl_s.qk_empty);
+  const uint32_t v_full = smem_u32(&ctl_s.v_full), v_empty = smem_u32(&ctl_s.v_empty);
+  const uint32_t s_full = smem_u32(&ctl_s.s_full), p_full = smem_u32(&ctl_s.p_full),
+                 o_full = smem_u32(&ctl_s.o_full);
+  const CUtensorMap* tm = map_ptr(ca, st.tm_qkv);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int item = blockIdx.x; item < items; item += gridDim.x) {
+        const int qt = item % n_kb, h = (item / n_kb) % H, b = item / (n_kb * H);
+        const int rq = ((0 * B + b) * H + h) * S, rk = ((1 * B + b) * H + h) * S, rv = ((2 * B + b) * H + h) * S;
+        if (!mbar_wait(qk_empty, rs.attn_bit ^ 1u, ctl, 500)) break;
+        mbar_expect_tx(qk_full, (uint32_t)(kATileBytes * (1 + n_kb)));
+        tma_load_2d(ring + q_off, tm, qk_full, 0, rq + qt * 128);
+        for (int kb = 0; kb < n_kb; ++kb) tma_load_2d(ring + k_off + kb * kATileBytes, tm, qk_full, 0, rk + kb * 128);
+        if (!mbar_wait(v_empty, rs.attn_bit ^ 1u, ctl, 501)) break;
+        mbar_expect_tx(v_full, (uint32_t)(kATileBytes * n_kb));
+        for (int kb = 0; kb < n_kb; ++kb) tma_load_2d(ring + v_off + kb * kATileBytes, tm, v_full, 0, rv + kb * 128);
+        rs.attn_bit ^= 1u;
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = umma_idesc_f16(128u, 0u);
+      const uint32_t idesc_o = umma_idesc_f16(64u, 1u);
+      const uint32_t tmem = ctl_s.tmem_base;
+      for (int item = blockIdx.x; item < items; item += gridDim.x) {
+        if (!mbar_wait(qk_full, rs.attn_bit, ctl, 510)) break;
+        tc_fence_after_sync();
+        const uint64_t qd = umma_desc_sw128(ring + q_off, 16, 1024);
+        for (int kb = 0; kb < n_kb; ++kb) {
+          const uint64_t kd = umma_desc_sw128(ring + k_off + kb * kATileBytes, 16, 1024);
+#pragma unroll
+          for (uint32_t k = 0; k < 4; ++k) umma_f16(tmem + kb * 128, qd + 2u * k, kd + 2u * k, idesc_s, (uint32_t)(k != 0));
+        }
+        umma_commit(s_full);
+        umma_commit(qk_empty);
+        if (!mbar_wait(p_full, rs.attn_bit, ctl, 511)) break;
+        if (!mbar_wait(v_full, rs.attn_bit, ctl, 512)) break;
+        tc_fence_after_sync();
+        for (int kk = 0; kk < n_kb * 8; ++kk) {
+          const uint64_t pd = umma_desc_sw128(ring + p_off + (kk >> 2) * kATileBytes, 16, 1024) + 2u * (kk & 3);
+          const uint64_t vd = umma_desc_sw128(ring + v_off + (kk >> 3) * kATileBytes, 8192, 1024) + 128u * (kk & 7);
+          umma_f16(tmem + kOCol, pd, vd, idesc_o, (uint32_t)(kk != 0));
+        }
+        umma_commit(o_full);
+        umma_commit(v_empty);
+        rs.attn_bit ^= 1u;
+      }
+    }
+    __syncwarp();
+  } else {
+    const int q = warp & 3;
+    const int r_in = q * 32 + lane;
+    const uint32_t tmem = ctl_s.tmem_base + ((uint32_t)(q * 32) << 16);
+    const float sl2 = st.scale * 1.4426950408889634f;
+    const float mask_l2 = -10000.0f * 1.4426950408889634f;
+    const int* lens = st.lens_from_call ? p.lens : st.lens;
+    __half* ctx = reinterpret_cast<__half*>(st.out);
+    __half* probs = reinterpret_cast<__half*>(st.probs);
+    const int hidden = H * st.head_dim;
+    for (int item = blockIdx.x; item < items; item += gridDim.x) {
+      const int qt = item % n_kb, h = (item / n_kb) % H, b = item / (n_kb * H);
+      const int kv_len = lens ? lens[b] : S;
+      bool ok = mbar_wait(s_full, rs.attn_bit, ctl, 520);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int n_chunks = n_kb * 4;
+      // pass 1: row maximum of the scaled, masked scores (base-2 domain)
+      float mx = -INFINITY;
+      for (int c = 0; c < n_chunks; ++c) {
+        if (c * 32 >= S) break;
+        uint32_t r[32];
+        tmem_ld32(tmem + c * 32, r);
+        tmem_ld_wait();
+        if (c * 32 + 32 <= kv_len) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]) * sl2);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int key = c * 32 + i;
+            const float t = __uint_as_float(r[i]) * sl2 + (key >= kv_len ? mask_l2 : 0.0f);
+            if (key < S) mx = fmaxf(mx, t);
+          }
+        }
+      }
+      // pass 2: unnormalised probabilities -> fp16 A-operand tile in shared memory
+      float sum = 0.0f;
+      for (int c = 0; c < n_chunks; ++c) {
+        uint32_t w[16];
+        if (c * 32 >= S) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) w[i] = 0u;
+        } else {
+          uint32_t r[32];
+          tmem_ld32(tmem + c * 32, r);
+          tmem_ld_wait();
+          float pv[32];
+          if (c * 32 + 32 <= kv_len) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) pv[i] = ex2_fast(__uint_as_float(r[i]) * sl2 - mx);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int key = c * 32 + i;
+              const float t = __uint_as_float(r[i]) * sl2 + (key >= kv_len ? mask_l2 : 0.0f);
+              pv[i] = key < S ? ex2_fast(t - mx) : 0.0f;
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) sum += pv[i];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) w[i] = pack_h2(pv[2 * i], pv[2 * i + 1]);
+        }
+        uint8_t* base = ring_ptr + p_off + (c >> 1) * kATileBytes + r_in * 128;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int j = (c & 1) * 4 + i;
+          *reinterpret_cast<uint4*>(base + ((j ^ (r_in & 7)) << 4)) =
+              make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+        }
+      }
+      const float inv = 1.0f / sum;
+      const int qrow = qt * 128 + r_in;
+      if (probs) {
+        // parity output: normalised probabilities [B*heads][S][S]
+        for (int c = 0; c < n_chunks && c * 32 < S; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tmem + c * 32, r);
+          tmem_ld_wait();
+          if (qrow < S) {
+            __half* dst = probs + ((size_t)(b * H + h) * S + qrow) * S + c * 32;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int key = c * 32 + i;
+              const float t = __uint_as_float(r[i]) * sl2 + (key >= kv_len ? mask_l2 : 0.0f);
+              if (key < S) dst[i] = __float2half_rn(ex2_fast(t - mx) * inv);
+            }
+          }
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(p_full);
+      ok = mbar_wait(o_full, rs.attn_bit, ctl, 521);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      {
+        uint32_t r0[32], r1[32];
+        tmem_ld32(tmem + kOCol, r0);
+        tmem_ld32(tmem + kOCol + 32, r1);
+        tmem_ld_wait();
+        if (qrow < S) {
+          uint4* dst = reinterpret_cast<uint4*>(ctx + ((size_t)b * S + qrow) * hidden + h * st.head_dim);
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            dst[i] = make_uint4(pack_h2(__uint_as_float(r0[8 * i]) * inv, __uint_as_float(r0[8 * i + 1]) * inv),
+                                pack_h2(__uint_as_float(r0[8 * i + 2]) * inv, __uint_as_float(r0[8 * i + 3]) * inv),
+                                pack_h2(__uint_as_float(r0[8 * i + 4]) * inv, __uint_as_float(r0[8 * i + 5]) * inv),
+                                pack_h2(__uint_as_float(r0[8 * i + 6]) * inv, __uint_as_float(r0[8 * i + 7]) * inv));
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            dst[4 + i] = make_uint4(pack_h2(__uint_as_float(r1[8 * i]) * inv, __uint_as_float(r1[8 * i + 1]) * inv),
+                                    pack_h2(__uint_as_float(r1[8 * i + 2]) * inv, __uint_as_float(r1[8 * i + 3]) * inv),
+                                    pack_h2(__uint_as_float(r1[8 * i + 4]) * inv, __uint_as_float(r1[8 * i + 5]) * inv),
+                                    pack_h2(__uint_as_float(r1[8 * i + 6]) * inv, __uint_as_float(r1[8 * i + 7]) * inv));
+        }
+      }
+      tc_fence_before_sync();
+      rs.attn_bit ^= 1u;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// LayerNorm stage: one warp per row; sums split-K partial planes, adds bias and residual
+// ------------------------------------------------------------------------------------
+__device__ void ln_stage(const Stage& st, const MegaParams& p, int warp, int lane) {
+  const int N = st.N, M = st.M;
+  const __half* resid = reinterpret_cast<const __half*>(sel_ptr(st.resid_sel, st.resid, p));
+  __half* out = reinterpret_cast<__half*>(const_cast<void*>(sel_ptr(st.out_sel, st.out, p)));
+  const __half* bias = reinterpret_cast<const __half*>(st.bias);
+  const __half* gamma = reinterpret_cast<const __half*>(st.gamma);
+  const __half* beta = reinterpret_cast<const __half*>(st.beta);
+  const int nwarps = kThreads / 32;
+  for (int row = blockIdx.x * nwarps + warp; row < M; row += gridDim.x * nwarps) {
+    float z[4][8];
+    float s1 = 0.0f;
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int c = (lane + 32 * it) * 8;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) z[it][i] = 0.0f;
+      if (c < N) {
+        for (int pl = 0; pl < st.n_partial; ++pl) {
+          const float4* src = reinterpret_cast<const float4*>(st.partial + ((size_t)pl * M + row) * N + c);
+          const float4 a = src[0], b = src[1];
+          z[it][0] += a.x; z[it][1] += a.y; z[it][2] += a.z; z[it][3] += a.w;
+          z[it][4] += b.x; z[it][5] += b.y; z[it][6] += b.z; z[it][7] += b.w;
+        }
+        if (bias) {
+          const uint4 u = __ldg(reinterpret_cast<const uint4*>(bias + c));
+          const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { const float2 f = __half22float2(h[j]); z[it][2 * j] += f.x; z[it][2 * j + 1] += f.y; }
+        }
+        if (resid) {
+          const uint4 u = *reinterpret_cast<const uint4*>(resid + (size_t)row * st.ldo + c);
+          const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { const float2 f = __half22float2(h[j]); z[it][2 * j] += f.x; z[it][2 * j + 1] += f.y; }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s1 += z[it][i];
+      }
+    }
+    const float mean = warp_sum(s1) / (float)N;
+    float s2 = 0.0f;
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int c = (lane + 32 * it) * 8;
+      if (c < N) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { const float dlt = z[it][i] - mean; s2 += dlt * dlt; }
+      }
+    }
+    const float rstd = rsqrtf(warp_sum(s2) / (float)N + st.eps);
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int c = (lane + 32 * it) * 8;
+      if (c < N) {
+        float y[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) y[i] = (z[it][i] - mean) * rstd;
+        if (gamma) {
+          const uint4 ug = __ldg(reinterpret_cast<const uint4*>(gamma + c));
+          const uint4 ub = __ldg(reinterpret_cast<const uint4*>(beta + c));
+          const __half2* hg = reinterpret_cast<const __half2*>(&ug);
+          const __half2* hb = reinterpret_cast<const __half2*>(&ub);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 fg = __half22float2(hg[j]), fb = __half22float2(hb[j]);
+            y[2 * j] = y[2 * j] * fg.x + fb.x;
+            y[2 * j + 1] = y[2 * j + 1] * fg.y + fb.y;
+          }
+        }
+        *reinterpret_cast<uint4*>(out + (size_t)row * st.ldo + c) =
+            make_uint4(pack_h2(y[0], y[1]), pack_h2(y[2], y[3]), pack_h2(y[4], y[5]), pack_h2(y[6], y[7]));
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// the kernel
+// ------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads, 1)
+souffle_megakernel(const __grid_constant__ CallArgs ca) {
+  const MegaParams& p = ca.p;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t pad = ((raw + 1023u) & ~1023u) - raw;      // 1024-byte alignment for swizzled tiles
+  SmemCtl& cs = *reinterpret_cast<SmemCtl*>(smem_raw + pad);
+  uint8_t* ring_ptr = smem_raw + pad + kCtlBytes;
+  const uint32_t ring = raw + pad + kCtlBytes;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kMaxSlots; ++i) {
+      mbar_init(smem_u32(&cs.full[i]), 1);
+      mbar_init(smem_u32(&cs.empty[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&cs.tmem_full[i]), 1);
+      mbar_init(smem_u32(&cs.tmem_empty[i]), 128);
+    }
+    mbar_init(smem_u32(&cs.qk_full), 1);
+    mbar_init(smem_u32(&cs.qk_empty), 1);
+    mbar_init(smem_u32(&cs.v_full), 1);
+    mbar_init(smem_u32(&cs.v_empty), 1);
+    mbar_init(smem_u32(&cs.s_full), 1);
+    mbar_init(smem_u32(&cs.p_full), 128);
+    mbar_init(smem_u32(&cs.o_full), 1);
+    cs.abort = 0;
+    fence_mbar_init();
+    if (blockIdx.x == 0) {          // the other launch parity's barrier words start clean
+      p.sync_next[0] = 0u;
+      p.sync_next[1] = 0u;
+    }
+  }
+  if (warp == 1) tmem_alloc(smem_u32(&cs.tmem_base), kTmemCols);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+
+  WaitCtl ctl;
+  ctl.abort_smem = &cs.abort;
+  ctl.status_g = p.status;
+  ctl.deadline_ns = globaltimer_ns() + p.timeout_ns;
+
+  RoleState rs;
+  for (int si = 0; si < p.n_stages; ++si) {
+    // stage record -> shared memory (uniform, read-only afterwards)
+    {
+      const uint32_t* src = reinterpret_cast<const uint32_t*>(p.stages ? p.stages + si : &ca.inline_stages[si]);
+      uint32_t* dst = reinterpret_cast<uint32_t*>(&cs.stage);
+      for (int i = threadIdx.x; i < (int)(sizeof(Stage) / 4); i += kThreads) dst[i] = src[i];
+    }
+    __syncthreads();
+    const Stage& st = cs.stage;
+    if (st.type == STAGE_GEMM) {
+      gemm_stage(st, ca, cs, ring, rs, ctl, warp, lane);
+    } else if (st.type == STAGE_ATTN) {
+      attn_stage(st, ca, cs, ring, ring_ptr, rs, ctl, warp, lane);
+    } else {
+      ln_stage(st, p, warp, lane);
+    }
+    if (si + 1 < p.n_stages) {
+      if (!grid_barrier(p, ctl, si)) break;
+    } else {
+      __syncthreads();
+    }
+    if (cs.abort) break;
+  }
+
+  __syncthreads();
+  if (cs.abort) {
+    // let copies that were already issued land before the CTA's shared memory is released
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(cs.tmem_base, kTmemCols);
+}
+
+}  // namespace souffle

@@ -1,0 +1,630 @@
+// Host side of libsouffle_b200.so: plan construction, tensor maps, launches, C ABI.
+//
+// Mirrors the host half of the reference bindings -- cpp/bert/bert_binding.cu:23-535 (allocate
+// intermediates, pack kernel arguments, cooperative launch), cpp/swin_transformer/
+// swin_transformer_binding.cu:62-209 and cpp/souffle_utils/cuda_utils.h:11-19,86-98 (error
+// check, co-residency check) -- with set-up split from the call: buffers, repacked weights and
+// the stage program are built once per plan; a forward call is one cooperative launch.
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "../../include/souffle_b200.h"
+#include "megakernel.cu"
+#include "lstm_kernel.cu"
+
+namespace souffle {
+
+// ------------------------------------------------------------------------------------
+// errors
+// ------------------------------------------------------------------------------------
+static thread_local std::string g_last_error;
+
+static int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+  return code;
+}
+#define SF_CUDA(call)                                                                          \
+  do {                                                                                         \
+    cudaError_t e_ = (call);                                                                   \
+    if (e_ != cudaSuccess)                                                                     \
+      return fail(SOUFFLE_CUDA_ERROR, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_),  \
+                  __FILE__, __LINE__);                                                         \
+  } while (0)
+
+static bool aligned16(const void* p) { return p && (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ------------------------------------------------------------------------------------
+// tensor maps (driver entry point fetched at run time: no link-time libcuda dependency)
+// ------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// fp16 matrix [rows][cols] (cols contiguous), box = 64 columns x box_rows rows, 128B swizzle,
+// out-of-range elements read as zero.
+static int make_map(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(SOUFFLE_CUDA_ERROR, "cuTensorMapEncodeTiled is not available from the driver");
+  if (!aligned16(ptr) || (cols * 2) % 16 != 0) return fail(SOUFFLE_BAD_POINTER, "tensor map needs 16-byte alignment");
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(SOUFFLE_CUDA_ERROR, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return SOUFFLE_OK;
+}
+
+// ------------------------------------------------------------------------------------
+// weight repack: [K][N] (reference layout) -> [N][K] so the B operand is K-major and any
+// tile width that is a multiple of 16 can be fed to the tensor cores.  Set-up only.
+// ------------------------------------------------------------------------------------
+__global__ void transpose_kn_to_nk(const __half* __restrict__ src, __half* __restrict__ dst, int K, int N) {
+  __shared__ __half tile[32][33];
+  const int n0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int k = k0 + i, n = n0 + threadIdx.x;
+    if (k < K && n < N) tile[i][threadIdx.x] = src[(size_t)k * N + n];
+  }
+  __syncthreads();
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int n = n0 + i, k = k0 + threadIdx.x;
+    if (k < K && n < N) dst[(size_t)n * K + k] = tile[threadIdx.x][i];
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// tiling choice.  Cost unit: one 128-byte row moved L2 -> shared memory by one CTA.
+// ------------------------------------------------------------------------------------
+static void choose_tiles(int M, int N, int K, int sms, bool allow_split, bool b_mn, int* bn_out, int* split_out) {
+  const int tiles_m = (M + 127) / 128;
+  const int kch = K / 64;
+  double best = 1e300;
+  int best_bn = 0, best_split = 1;
+  const int cands[5] = {256, 128, 64, 32, 16};
+  for (int ci = 0; ci < 5; ++ci) {
+    const int bn = cands[ci];
+    if (N % bn) continue;
+    if (b_mn && bn % 64) continue;
+    for (int split = 1; split <= (allow_split ? 16 : 1); ++split) {
+      if (kch % split) continue;
+      const long items = (long)tiles_m * (N / bn) * split;
+      const long waves = (items + sms - 1) / sms;
+      double cost = (double)waves * (kch / split) * (128.0 + 1.5 * bn) + (double)waves * 40.0;
+      if (allow_split) cost += (double)split * M * N * 8.0 / sms / 128.0;
+      if (cost < best - 1e-9) {
+        best = cost;
+        best_bn = bn;
+        best_split = split;
+      }
+    }
+  }
+  *bn_out = best_bn;
+  *split_out = best_split;
+}
+
+// ------------------------------------------------------------------------------------
+// launch helper shared by every entry point
+// ------------------------------------------------------------------------------------
+struct DeviceInfo {
+  int device = -1, sms = 0, cc_major = 0, max_ctas = 0;
+  bool attr_set = false;
+};
+static DeviceInfo g_dev[16];
+
+static int device_info(DeviceInfo** out) {
+  int dev = 0;
+  SF_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 16) return fail(SOUFFLE_BAD_DEVICE, "device index %d out of range", dev);
+  DeviceInfo& d = g_dev[dev];
+  if (d.device < 0) {
+    SF_CUDA(cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev));
+    SF_CUDA(cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev));
+    if (d.cc_major != 10)
+      return fail(SOUFFLE_BAD_DEVICE, "device %d has compute capability %d.x; this library needs sm_100", dev, d.cc_major);
+    SF_CUDA(cudaFuncSetAttribute(souffle_megakernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    int per_sm = 0;
+    SF_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, souffle_megakernel, kThreads, kSmemBytes));
+    d.max_ctas = per_sm * d.sms;
+    if (d.max_ctas < 1) return fail(SOUFFLE_NOT_CORESIDENT, "megakernel does not fit on an SM of device %d", dev);
+    d.device = dev;
+  }
+  *out = &d;
+  return SOUFFLE_OK;
+}
+
+static int launch_mega(const CallArgs& args, int grid, cudaStream_t stream) {
+  void* kargs[] = {const_cast<CallArgs*>(&args)};
+  SF_CUDA(cudaLaunchCooperativeKernel((const void*)souffle_megakernel, dim3(grid), dim3(kThreads), kargs,
+                                      (size_t)kSmemBytes, stream));
+  return SOUFFLE_OK;
+}
+
+static int stage_items(const Stage& s) {
+  if (s.type == STAGE_GEMM) return ((s.M + 127) / 128) * (s.N / s.bn) * s.splitk;
+  if (s.type == STAGE_ATTN) return s.batch * s.heads * ((s.seq + 127) / 128);
+  return (s.M + 5) / 6;
+}
+
+static int decode_status(const int* h, const char* what) {
+  if (h[0] == DEV_OK) return SOUFFLE_OK;
+  return fail(SOUFFLE_DEVICE_TIMEOUT, "%s: device wait expired (code %d, where %d, cta %d)", what, h[0], h[1], h[2]);
+}
+
+}  // namespace souffle
+
+using namespace souffle;
+
+// ======================================================================================
+// BERT plan
+// ======================================================================================
+struct SouffleBertPlan {
+  SouffleBertDesc desc;
+  int device = 0, grid = 0, launches = 0;
+  unsigned launch_id = 0;
+  std::vector<Stage> stages;
+  std::vector<CUtensorMap> maps;
+  std::vector<void*> allocs;
+  Stage* d_stages = nullptr;
+  CUtensorMap* d_maps = nullptr;
+  unsigned* d_sync = nullptr;   // two (count, generation) pairs
+  int* d_status = nullptr;
+  // plan-owned activations
+  __half *qkv = nullptr, *ctx = nullptr, *ln1 = nullptr, *fc1 = nullptr, *probs = nullptr, *act[2] = {nullptr, nullptr};
+  float* partial = nullptr;
+  // host-buffer path
+  __half *x_dev = nullptr, *y_dev = nullptr;
+  int* lens_dev = nullptr;
+  // per-call map cache for x
+  const void* last_x = nullptr;
+  CUtensorMap x_map;
+};
+
+namespace souffle {
+
+static int plan_alloc(SouffleBertPlan* p, void** ptr, size_t bytes) {
+  SF_CUDA(cudaMalloc(ptr, bytes));
+  p->allocs.push_back(*ptr);
+  return SOUFFLE_OK;
+}
+
+static int add_map(SouffleBertPlan* p, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows, int* idx) {
+  if ((int)p->maps.size() >= kMaxTensorMaps) return fail(SOUFFLE_BAD_SHAPE, "too many tensor maps");
+  CUtensorMap m;
+  int rc = make_map(&m, ptr, rows, cols, box_rows);
+  if (rc) return rc;
+  *idx = (int)p->maps.size();
+  p->maps.push_back(m);
+  return SOUFFLE_OK;
+}
+
+static Stage blank_stage(int type) {
+  Stage s;
+  memset(&s, 0, sizeof(s));
+  s.type = type;
+  s.splitk = 1;
+  s.n_partial = 0;
+  return s;
+}
+
+static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* layers) {
+  const SouffleBertDesc& d = p->desc;
+  DeviceInfo* di = nullptr;
+  int rc = device_info(&di);
+  if (rc) return rc;
+  p->device = di->device;
+  const int B = d.batch, S = d.seq, Hh = d.heads, hd = d.head_dim, H = Hh * hd, F = d.ffn, M = B * S, L = d.n_layers;
+  const bool std_variant = d.variant == SOUFFLE_BERT_STD;
+  const float scale = std_variant ? 1.0f / sqrtf((float)hd) : 1.0f / sqrtf((float)H);
+  int sms = di->sms;
+  if (d.max_ctas > 0 && d.max_ctas < sms) sms = d.max_ctas;
+  if (sms > di->max_ctas) sms = di->max_ctas;
+
+  // ---- buffers ----
+  if ((rc = plan_alloc(p, (void**)&p->qkv, (size_t)3 * M * H * 2))) return rc;
+  if ((rc = plan_alloc(p, (void**)&p->ctx, (size_t)M * H * 2))) return rc;
+  if ((rc = plan_alloc(p, (void**)&p->ln1, (size_t)M * H * 2))) return rc;
+  if ((rc = plan_alloc(p, (void**)&p->fc1, (size_t)M * F * 2))) return rc;
+  if (L > 1) {
+    if ((rc = plan_alloc(p, (void**)&p->act[0], (size_t)M * H * 2))) return rc;
+    if (L > 2 && (rc = plan_alloc(p, (void**)&p->act[1], (size_t)M * H * 2))) return rc;
+  }
+  if (d.keep_probs) {
+    if ((rc = plan_alloc(p, (void**)&p->probs, (size_t)B * Hh * S * S * 2))) return rc;
+  }
+  if ((rc = plan_alloc(p, (void**)&p->d_sync, 64))) return rc;
+  if ((rc = plan_alloc(p, (void**)&p->d_status, 64))) return rc;
+  SF_CUDA(cudaMemset(p->d_sync, 0, 64));
+  SF_CUDA(cudaMemset(p->d_status, 0, 64));
+
+  // ---- tiling ----
+  int bn_qkv = d.bn_qkv, bn_fc1 = d.bn_fc1, bn_proj = d.bn_proj, sp_proj = d.split_proj, bn_fc2 = d.bn_fc2,
+      sp_fc2 = d.split_fc2, one = 1;
+  if (!bn_qkv) choose_tiles(M, 3 * H, H, sms, false, false, &bn_qkv, &one);
+  if (!bn_fc1) choose_tiles(M, F, H, sms, false, false, &bn_fc1, &one);
+  if (!bn_proj || !sp_proj) {
+    int a, b;
+    choose_tiles(M, H, H, sms, true, false, &a, &b);
+    if (!bn_proj) bn_proj = a;
+    if (!sp_proj) sp_proj = b;
+  }
+  if (!bn_fc2 || !sp_fc2) {
+    int a, b;
+    choose_tiles(M, H, F, sms, true, false, &a, &b);
+    if (!bn_fc2) bn_fc2 = a;
+    if (!sp_fc2) sp_fc2 = b;
+  }
+  auto bad_bn = [](int bn, int N) { return bn < 16 || bn > 256 || bn % 16 || N % bn; };
+  if (bad_bn(bn_qkv, 3 * H) || bad_bn(bn_fc1, F) || bad_bn(bn_proj, H) || bad_bn(bn_fc2, H))
+    return fail(SOUFFLE_BAD_SHAPE, "tile widths (%d,%d,%d,%d) do not divide the layer's widths", bn_qkv, bn_fc1, bn_proj, bn_fc2);
+  if ((H / 64) % sp_proj || (F / 64) % sp_fc2) return fail(SOUFFLE_BAD_SHAPE, "split-K factors must divide K/64");
+  const int max_split = sp_proj > sp_fc2 ? sp_proj : sp_fc2;
+  if ((rc = plan_alloc(p, (void**)&p->partial, (size_t)max_split * M * H * 4))) return rc;
+
+  // ---- activation maps (A operands, box 64 x 128) ----
+  int m_ctx, m_ln1, m_fc1, m_act[2] = {-1, -1}, m_qkv;
+  if ((rc = add_map(p, p->ctx, M, H, 128, &m_ctx))) return rc;
+  if ((rc = add_map(p, p->ln1, M, H, 128, &m_ln1))) return rc;
+  if ((rc = add_map(p, p->fc1, M, F, 128, &m_fc1))) return rc;
+  for (int i = 0; i < 2; ++i)
+    if (p->act[i] && (rc = add_map(p, p->act[i], M, H, 128, &m_act[i]))) return rc;
+  if ((rc = add_map(p, p->qkv, (uint64_t)3 * B * Hh * S, hd, 128, &m_qkv))) return rc;
+
+  // ---- per layer: repack weights, maps, stages ----
+  for (int l = 0; l < L; ++l) {
+    const SouffleBertLayerWeights& w = layers[l];
+    if (!aligned16(w.qkv_w) || !aligned16(w.proj_w) || !aligned16(w.fc1_w) || !aligned16(w.fc2_w))
+      return fail(SOUFFLE_BAD_POINTER, "layer %d: weight matrices must be non-null and 16-byte aligned", l);
+    __half *wqkv_t, *wo_t, *w1_t, *w2_t;
+    if ((rc = plan_alloc(p, (void**)&wqkv_t, (size_t)3 * H * H * 2))) return rc;
+    if ((rc = plan_alloc(p, (void**)&wo_t, (size_t)H * H * 2))) return rc;
+    if ((rc = plan_alloc(p, (void**)&w1_t, (size_t)H * F * 2))) return rc;
+    if ((rc = plan_alloc(p, (void**)&w2_t, (size_t)F * H * 2))) return rc;
+    const dim3 tb(32, 8);
+    for (int j = 0; j < 3; ++j)
+      transpose_kn_to_nk<<<dim3(H / 32, H / 32), tb>>>(reinterpret_cast<const __half*>(w.qkv_w) + (size_t)j * H * H,
+                                                        wqkv_t + (size_t)j * H * H, H, H);
+    transpose_kn_to_nk<<<dim3(H / 32, H / 32), tb>>>(reinterpret_cast<const __half*>(w.proj_w), wo_t, H, H);
+    transpose_kn_to_nk<<<dim3(F / 32, H / 32), tb>>>(reinterpret_cast<const __half*>(w.fc1_w), w1_t, H, F);
+    transpose_kn_to_nk<<<dim3(H / 32, F / 32), tb>>>(reinterpret_cast<const __half*>(w.fc2_w), w2_t, F, H);
+    SF_CUDA(cudaGetLastError());
+    // vectors are copied so the plan does not alias caller memory
+    auto copy_vec = [&](const void* src, size_t n, const void** dst) -> int {
+      *dst = nullptr;
+      if (!src) return SOUFFLE_OK;
+      void* v;
+      int r2 = plan_alloc(p, &v, n * 2);
+      if (r2) return r2;
+      if (cudaMemcpy(v, src, n * 2, cudaMemcpyDeviceToDevice) != cudaSuccess)
+        return fail(SOUFFLE_CUDA_ERROR, "copying a parameter vector failed");
+      *dst = v;
+      return SOUFFLE_OK;
+    };
+    const void *qkv_b, *proj_b, *ln1_g, *ln1_b, *fc1_b, *fc2_b, *ln2_g, *ln2_b;
+    if ((rc = copy_vec(w.qkv_b, 3 * H, &qkv_b))) return rc;
+    if ((rc = copy_vec(std_variant ? w.proj_b : nullptr, H, &proj_b))) return rc;
+    if ((rc = copy_vec(std_variant ? w.ln1_g : nullptr, H, &ln1_g))) return rc;
+    if ((rc = copy_vec(std_variant ? w.ln1_b : nullptr, H, &ln1_b))) return rc;
+    if ((rc = copy_vec(std_variant ? w.fc1_b : nullptr, F, &fc1_b))) return rc;
+    if ((rc = copy_vec(std_variant ? w.fc2_b : nullptr, H, &fc2_b))) return rc;
+    if ((rc = copy_vec(std_variant ? w.ln2_g : nullptr, H, &ln2_g))) return rc;
+    if ((rc = copy_vec(std_variant ? w.ln2_b : nullptr, H, &ln2_b))) return rc;
+    if ((ln1_g == nullptr) != (ln1_b == nullptr) || (ln2_g == nullptr) != (ln2_b == nullptr))
+      return fail(SOUFFLE_BAD_ARGUMENT, "layer %d: gamma and beta must be given together", l);
+
+    int m_wqkv, m_wo, m_w1, m_w2;
+    if ((rc = add_map(p, wqkv_t, 3 * H, H, bn_qkv, &m_wqkv))) return rc;
+    if ((rc = add_map(p, wo_t, H, H, bn_proj, &m_wo))) return rc;
+    if ((rc = add_map(p, w1_t, F, H, bn_fc1, &m_w1))) return rc;
+    if ((rc = add_map(p, w2_t, H, F, bn_fc2, &m_w2))) return rc;
+
+    // layer input / output routing
+    const bool first = l == 0, last = l == L - 1;
+    const int in_map = first ? -1 : m_act[(l - 1) & 1];
+    const void* in_ptr = first ? nullptr : p->act[(l - 1) & 1];
+    const int in_sel = first ? PTR_CALL_X : PTR_PLAN;
+    void* out_ptr = last ? nullptr : p->act[l & 1];
+    const int out_sel = last ? PTR_CALL_Y : PTR_PLAN;
+
+    Stage s = blank_stage(STAGE_GEMM);                 // QKV projection, head-split store
+    s.tm_a = in_map; s.tm_b = m_wqkv; s.M = M; s.N = 3 * H; s.K = H; s.bn = bn_qkv;
+    s.epi = EPI_QKV; s.bias = qkv_b; s.out = p->qkv; s.batch = B; s.heads = Hh; s.seq = S; s.head_dim = hd;
+    p->stages.push_back(s);
+
+    s = blank_stage(STAGE_ATTN);                       // softmax(QK^T) V
+    s.tm_qkv = m_qkv; s.batch = B; s.heads = Hh; s.seq = S; s.head_dim = hd; s.scale = scale;
+    s.lens_from_call = 1; s.out = p->ctx; s.probs = (last && d.keep_probs) ? p->probs : nullptr;
+    p->stages.push_back(s);
+
+    s = blank_stage(STAGE_GEMM);                       // output projection -> fp32 partials
+    s.tm_a = m_ctx; s.tm_b = m_wo; s.M = M; s.N = H; s.K = H; s.bn = bn_proj; s.splitk = sp_proj;
+    s.epi = EPI_PARTIAL; s.partial = p->partial;
+    p->stages.push_back(s);
+
+    s = blank_stage(STAGE_LN);                         // + bias + residual, LayerNorm 1
+    s.M = M; s.N = H; s.ldo = H; s.partial = p->partial; s.n_partial = sp_proj; s.bias = proj_b;
+    s.resid = in_ptr; s.resid_sel = in_sel; s.out = p->ln1; s.gamma = ln1_g; s.beta = ln1_b; s.eps = d.eps;
+    p->stages.push_back(s);
+
+    s = blank_stage(STAGE_GEMM);                       // FC1 + bias + activation
+    s.tm_a = m_ln1; s.tm_b = m_w1; s.M = M; s.N = F; s.K = H; s.bn = bn_fc1;
+    s.epi = EPI_F16; s.act = std_variant ? ACT_GELU : ACT_RELU; s.bias = fc1_b; s.out = p->fc1; s.ldo = F;
+    p->stages.push_back(s);
+
+    s = blank_stage(STAGE_GEMM);                       // FC2 -> fp32 partials
+    s.tm_a = m_fc1; s.tm_b = m_w2; s.M = M; s.N = H; s.K = F; s.bn = bn_fc2; s.splitk = sp_fc2;
+    s.epi = EPI_PARTIAL; s.partial = p->partial;
+    p->stages.push_back(s);
+
+    s = blank_stage(STAGE_LN);                         // + bias + residual, LayerNorm 2
+    s.M = M; s.N = H; s.ldo = H; s.partial = p->partial; s.n_partial = sp_fc2; s.bias = fc2_b;
+    s.resid = p->ln1; s.resid_sel = PTR_PLAN; s.out = out_ptr; s.out_sel = out_sel;
+    s.gamma = ln2_g; s.beta = ln2_b; s.eps = d.eps;
+    p->stages.push_back(s);
+  }
+  if ((int)p->stages.size() > kMaxStages) return fail(SOUFFLE_BAD_SHAPE, "too many stages (%zu)", p->stages.size());
+
+  int max_items = 1;
+  for (const Stage& s : p->stages) {
+    const int it = stage_items(s);
+    if (it > max_items) max_items = it;
+  }
+  p->grid = max_items < sms ? max_items : sms;
+
+  if ((rc = plan_alloc(p, (void**)&p->d_stages, p->stages.size() * sizeof(Stage)))) return rc;
+  if ((rc = plan_alloc(p, (void**)&p->d_maps, p->maps.size() * sizeof(CUtensorMap)))) return rc;
+  SF_CUDA(cudaMemcpy(p->d_stages, p->stages.data(), p->stages.size() * sizeof(Stage), cudaMemcpyHostToDevice));
+  SF_CUDA(cudaMemcpy(p->d_maps, p->maps.data(), p->maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice));
+  SF_CUDA(cudaDeviceSynchronize());
+  return SOUFFLE_OK;
+}
+
+}  // namespace souffle
+
+extern "C" {
+
+const char* souffle_last_error(void) { return g_last_error.c_str(); }
+int souffle_abi_version(void) { return 1; }
+
+int souffle_bert_plan_create(const SouffleBertDesc* desc, const SouffleBertLayerWeights* layers,
+                             SouffleBertPlan** plan_out) {
+  if (!desc || !layers || !plan_out) return fail(SOUFFLE_BAD_ARGUMENT, "null argument");
+  *plan_out = nullptr;
+  const SouffleBertDesc& d = *desc;
+  if (d.batch < 1 || d.heads < 1 || d.n_layers < 1 || d.n_layers > 12)
+    return fail(SOUFFLE_BAD_SHAPE, "batch, heads must be >= 1 and 1 <= n_layers <= 12");
+  if (d.head_dim != 64) return fail(SOUFFLE_BAD_SHAPE, "head_dim must be 64 (got %d)", d.head_dim);
+  const bool seq_ok = (d.seq >= 16 && d.seq <= 128 && d.seq % 16 == 0) || d.seq == 256 || d.seq == 384;
+  if (!seq_ok) return fail(SOUFFLE_BAD_SHAPE, "seq must be a multiple of 16 up to 128, or 256, or 384 (got %d)", d.seq);
+  const int H = d.heads * d.head_dim;
+  if (H > 1024) return fail(SOUFFLE_BAD_SHAPE, "hidden size %d exceeds 1024", H);
+  if (d.ffn < 64 || d.ffn % 64) return fail(SOUFFLE_BAD_SHAPE, "ffn must be a positive multiple of 64 (got %d)", d.ffn);
+  if (d.variant != SOUFFLE_BERT_STD && d.variant != SOUFFLE_BERT_REF_COMPAT)
+    return fail(SOUFFLE_BAD_ARGUMENT, "unknown variant %d", d.variant);
+  SouffleBertPlan* p = new SouffleBertPlan();
+  p->desc = d;
+  int rc = build_bert_plan(p, layers);
+  if (rc) {
+    const std::string keep = g_last_error;
+    souffle_bert_plan_destroy(p);
+    g_last_error = keep;
+    return rc;
+  }
+  *plan_out = p;
+  return SOUFFLE_OK;
+}
+
+int souffle_bert_plan_destroy(SouffleBertPlan* plan) {
+  if (!plan) return SOUFFLE_OK;
+  cudaDeviceSynchronize();
+  for (void* a : plan->allocs) cudaFree(a);
+  if (plan->x_dev) cudaFree(plan->x_dev);
+  if (plan->y_dev) cudaFree(plan->y_dev);
+  if (plan->lens_dev) cudaFree(plan->lens_dev);
+  delete plan;
+  return SOUFFLE_OK;
+}
+
+int souffle_bert_forward(SouffleBertPlan* plan, const void* x, const int32_t* seq_lens, void* y,
+                         souffle_stream_t stream) {
+  if (!plan) return fail(SOUFFLE_BAD_ARGUMENT, "null plan");
+  if (!aligned16(x) || !aligned16(y)) return fail(SOUFFLE_BAD_POINTER, "x and y must be non-null and 16-byte aligned");
+  const SouffleBertDesc& d = plan->desc;
+  const int M = d.batch * d.seq, H = d.heads * d.head_dim;
+  if (x != plan->last_x) {
+    int rc = make_map(&plan->x_map, x, M, H, 128);
+    if (rc) return rc;
+    plan->last_x = x;
+  }
+  CallArgs args;
+  memset(&args, 0, sizeof(args));
+  args.call_maps[0] = plan->x_map;
+  MegaParams& mp = args.p;
+  mp.stages = plan->d_stages;
+  mp.n_stages = (int)plan->stages.size();
+  mp.maps = plan->d_maps;
+  mp.x = x;
+  mp.y = y;
+  mp.lens = seq_lens;
+  const unsigned par = plan->launch_id & 1u;
+  mp.sync = plan->d_sync + 2 * par;
+  mp.sync_next = plan->d_sync + 2 * (par ^ 1u);
+  mp.status = plan->d_status;
+  mp.timeout_ns = (unsigned long long)(d.timeout_ms > 0 ? d.timeout_ms : 2000) * 1000000ull;
+  int rc = launch_mega(args, plan->grid, reinterpret_cast<cudaStream_t>(stream));
+  if (rc) return rc;
+  plan->launch_id++;
+  plan->launches = 1;
+  return SOUFFLE_OK;
+}
+
+int souffle_bert_forward_host(SouffleBertPlan* plan, const void* x_host, const int32_t* seq_lens_host,
+                              void* y_host, souffle_stream_t stream) {
+  if (!plan || !x_host || !y_host) return fail(SOUFFLE_BAD_ARGUMENT, "null argument");
+  const SouffleBertDesc& d = plan->desc;
+  const size_t bytes = (size_t)d.batch * d.seq * d.heads * d.head_dim * 2;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (!plan->x_dev) {
+    SF_CUDA(cudaMalloc((void**)&plan->x_dev, bytes));
+    SF_CUDA(cudaMalloc((void**)&plan->y_dev, bytes));
+    SF_CUDA(cudaMalloc((void**)&plan->lens_dev, (size_t)d.batch * 4));
+  }
+  SF_CUDA(cudaMemcpyAsync(plan->x_dev, x_host, bytes, cudaMemcpyHostToDevice, st));
+  if (seq_lens_host)
+    SF_CUDA(cudaMemcpyAsync(plan->lens_dev, seq_lens_host, (size_t)d.batch * 4, cudaMemcpyHostToDevice, st));
+  int rc = souffle_bert_forward(plan, plan->x_dev, seq_lens_host ? plan->lens_dev : nullptr, plan->y_dev, stream);
+  if (rc) return rc;
+  SF_CUDA(cudaMemcpyAsync(y_host, plan->y_dev, bytes, cudaMemcpyDeviceToHost, st));
+  SF_CUDA(cudaStreamSynchronize(st));
+  return SOUFFLE_OK;
+}
+
+int souffle_bert_plan_buffer(SouffleBertPlan* plan, int which, void** ptr_out, size_t* bytes_out) {
+  if (!plan || !ptr_out) return fail(SOUFFLE_BAD_ARGUMENT, "null argument");
+  const SouffleBertDesc& d = plan->desc;
+  const size_t M = (size_t)d.batch * d.seq, H = (size_t)d.heads * d.head_dim;
+  void* ptr = nullptr;
+  size_t bytes = 0;
+  switch (which) {
+    case SOUFFLE_BUF_QKV: ptr = plan->qkv; bytes = 3 * M * H * 2; break;
+    case SOUFFLE_BUF_PROBS: ptr = plan->probs; bytes = (size_t)d.batch * d.heads * d.seq * d.seq * 2; break;
+    case SOUFFLE_BUF_CTX: ptr = plan->ctx; bytes = M * H * 2; break;
+    case SOUFFLE_BUF_LN1: ptr = plan->ln1; bytes = M * H * 2; break;
+    case SOUFFLE_BUF_FC1: ptr = plan->fc1; bytes = M * (size_t)d.ffn * 2; break;
+    default: return fail(SOUFFLE_BAD_ARGUMENT, "unknown buffer id %d", which);
+  }
+  if (!ptr) return fail(SOUFFLE_BAD_ARGUMENT, "buffer %d was not requested at plan creation", which);
+  *ptr_out = ptr;
+  if (bytes_out) *bytes_out = bytes;
+  return SOUFFLE_OK;
+}
+
+int souffle_bert_plan_status(SouffleBertPlan* plan) {
+  if (!plan) return fail(SOUFFLE_BAD_ARGUMENT, "null plan");
+  SF_CUDA(cudaDeviceSynchronize());
+  int h[4] = {0, 0, 0, 0};
+  SF_CUDA(cudaMemcpy(h, plan->d_status, sizeof(h), cudaMemcpyDeviceToHost));
+  if (h[0] != DEV_OK) {
+    // leave the plan usable: clear the status and both barrier pairs
+    cudaMemset(plan->d_status, 0, 64);
+    cudaMemset(plan->d_sync, 0, 64);
+  }
+  return decode_status(h, "souffle_bert_forward");
+}
+
+int souffle_bert_plan_info(SouffleBertPlan* plan, int* launches_out, int* grid_out, int* n_stages_out) {
+  if (!plan) return fail(SOUFFLE_BAD_ARGUMENT, "null plan");
+  if (launches_out) *launches_out = plan->launches;
+  if (grid_out) *grid_out = plan->grid;
+  if (n_stages_out) *n_stages_out = (int)plan->stages.size();
+  return SOUFFLE_OK;
+}
+
+// ======================================================================================
+// plan-less GEMM / Swin MLP: tensor maps and stages travel in the launch parameters
+// ======================================================================================
+size_t souffle_gemm_workspace_bytes(void) { return 256; }
+
+static int ws_prepare(void* workspace, size_t ws_bytes, cudaStream_t st, MegaParams* mp) {
+  if (!aligned16(workspace) || ws_bytes < souffle_gemm_workspace_bytes())
+    return fail(SOUFFLE_BAD_POINTER, "workspace must be 16-byte aligned and hold %zu bytes", souffle_gemm_workspace_bytes());
+  SF_CUDA(cudaMemsetAsync(workspace, 0, 128, st));
+  mp->sync = reinterpret_cast<unsigned*>(workspace);
+  mp->sync_next = mp->sync + 2;
+  mp->status = reinterpret_cast<int*>(reinterpret_cast<char*>(workspace) + 64);
+  mp->timeout_ns = 2000ull * 1000000ull;
+  return SOUFFLE_OK;
+}
+
+static int fill_gemm_stage(Stage* s, int tm_a, int tm_b, const void* out, int M, int N, int K, int sms) {
+  *s = blank_stage(STAGE_GEMM);
+  int bn = 0, split = 1;
+  choose_tiles(M, N, K, sms, false, true, &bn, &split);
+  if (!bn) return fail(SOUFFLE_BAD_SHAPE, "N=%d must be a multiple of 64", N);
+  s->tm_a = tm_a; s->tm_b = tm_b; s->M = M; s->N = N; s->K = K; s->bn = bn; s->b_mn_major = 1;
+  s->epi = EPI_F16; s->out = const_cast<void*>(out); s->ldo = N;
+  return SOUFFLE_OK;
+}
+
+int souffle_gemm_f16(const void* a, const void* w_kn, void* c, int32_t M, int32_t N, int32_t K, void* workspace,
+                     size_t workspace_bytes, souffle_stream_t stream) {
+  if (M < 1 || N < 64 || N % 64 || K < 64 || K % 64)
+    return fail(SOUFFLE_BAD_SHAPE, "GEMM needs M >= 1, N %% 64 == 0, K %% 64 == 0 (got %d, %d, %d)", M, N, K);
+  if (!aligned16(a) || !aligned16(w_kn) || !aligned16(c)) return fail(SOUFFLE_BAD_POINTER, "operands must be 16-byte aligned");
+  DeviceInfo* di = nullptr;
+  int rc = device_info(&di);
+  if (rc) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  CallArgs args;
+  memset(&args, 0, sizeof(args));
+  if ((rc = ws_prepare(workspace, workspace_bytes, st, &args.p))) return rc;
+  if ((rc = make_map(&args.call_maps[0], a, M, K, 128))) return rc;
+  if ((rc = make_map(&args.call_maps[1], w_kn, K, N, 64))) return rc;     // [K][N]: box 64 (N) x 64 (K rows)
+  const int sms = di->sms < di->max_ctas ? di->sms : di->max_ctas;
+  if ((rc = fill_gemm_stage(&args.inline_stages[0], -1, -2, c, M, N, K, sms))) return rc;
+  args.p.n_stages = 1;
+  const int items = stage_items(args.inline_stages[0]);
+  return launch_mega(args, items < sms ? items : sms, st);
+}
+
+int souffle_swin_mlp_forward(const void* src, const void* fc1_w, const void* fc2_w, void* hidden, void* out, int32_t M,
+                             int32_t C, int32_t F, void* workspace, size_t workspace_bytes, souffle_stream_t stream) {
+  if (M < 1 || C < 64 || C % 64 || F < 64 || F % 64)
+    return fail(SOUFFLE_BAD_SHAPE, "MLP needs M >= 1 and C, F multiples of 64 (got %d, %d, %d)", M, C, F);
+  if (!aligned16(src) || !aligned16(fc1_w) || !aligned16(fc2_w) || !aligned16(hidden) || !aligned16(out))
+    return fail(SOUFFLE_BAD_POINTER, "operands must be 16-byte aligned");
+  DeviceInfo* di = nullptr;
+  int rc = device_info(&di);
+  if (rc) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  CallArgs args;
+  memset(&args, 0, sizeof(args));
+  if ((rc = ws_prepare(workspace, workspace_bytes, st, &args.p))) return rc;
+  if ((rc = make_map(&args.call_maps[0], src, M, C, 128))) return rc;
+  if ((rc = make_map(&args.call_maps[1], fc1_w, C, F, 64))) return rc;
+  if ((rc = make_map(&args.call_maps[2], hidden, M, F, 128))) return rc;
+  if ((rc = make_map(&args.call_maps[3], fc2_w, F, C, 64))) return rc;
+  const int sms = di->sms < di->max_ctas ? di->sms : di->max_ctas;
+  if ((rc = fill_gemm_stage(&args.inline_stages[0], -1, -2, hidden, M, F, C, sms))) return rc;
+  if ((rc = fill_gemm_stage(&args.inline_stages[1], -3, -4, out, M, C, F, sms))) return rc;
+  args.p.n_stages = 2;
+  int items = stage_items(args.inline_stages[0]);
+  const int i2 = stage_items(args.inline_stages[1]);
+  if (i2 > items) items = i2;
+  return launch_mega(args, items < sms ? items : sms, st);
+}
+
+int souffle_workspace_status(void* workspace, souffle_stream_t stream) {
+  if (!workspace) return fail(SOUFFLE_BAD_ARGUMENT, "null workspace");
+  SF_CUDA(cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(stream)));
+  int h[4] = {0, 0, 0, 0};
+  SF_CUDA(cudaMemcpy(h, reinterpret_cast<char*>(workspace) + 64, sizeof(h), cudaMemcpyDeviceToHost));
+  return decode_status(h, "souffle workspace");
+}
+
+}  // extern "C"

@@ -1,0 +1,66 @@
+// Stage program: the host-built description a persistent megakernel interprets.
+//
+// The reference fuses an encoder layer into one cooperative launch whose stages are separated
+// by grid.sync() (cpp/bert/kernels/fused_sqq_bert.cu:34-2305: nine stages, compile-time shapes
+// from cpp/bert/kernels/bert.h:8-52).  Here the stage list is data: every stage is a record in
+// global memory, shapes are runtime values, and the same kernel runs a BERT layer, a chain of
+// layers, the Swin MLP pair or a single GEMM.
+#pragma once
+#include <stdint.h>
+
+namespace souffle {
+
+enum StageType : int {
+  STAGE_GEMM = 0,   // C = A . B with a fused epilogue
+  STAGE_ATTN = 1,   // per (sequence, head, query tile): softmax(Q K^T * scale + mask) V
+  STAGE_LN = 2,     // z = sum_p partial[p] + bias + resid ; y = LayerNorm(z)
+};
+
+enum EpilogueKind : int {
+  EPI_F16 = 0,      // out[row, col] = f16(act(acc + bias)) (+ resid)
+  EPI_QKV = 1,      // like EPI_F16 but scattered head-split to [3][B][heads][S][d]
+  EPI_PARTIAL = 2,  // raw fp32 accumulators to partial[split][row][col]
+};
+
+enum Activation : int { ACT_NONE = 0, ACT_RELU = 1, ACT_GELU = 2 };
+
+// Pointer selectors: a stage either carries a plan-owned pointer or names a per-call argument.
+enum PtrSel : int { PTR_PLAN = 0, PTR_CALL_X = 1, PTR_CALL_Y = 2 };
+
+struct Stage {
+  int type;
+  // ---- GEMM ----
+  int tm_a;          // tensor-map index of the A operand ([M][K], box 64 x 128); -1 = per-call x map
+  int tm_b;          // tensor-map index of the B operand
+  int M, N, K;
+  int bn;            // tile width in N (multiple of 16, <= 256, divides N)
+  int splitk;        // K is cut into this many independent partial products
+  int b_mn_major;    // 0: B stored [N][K] (K contiguous); 1: B stored [K][N] (N contiguous, bn % 64 == 0)
+  int epi;           // EpilogueKind
+  int act;           // Activation
+  int out_sel;       // PtrSel for `out`
+  int resid_sel;     // PtrSel for `resid`
+  int ldo;           // leading dimension of out / resid (elements)
+  const void* bias;  // fp16 [N] or null
+  const void* resid; // fp16 [M][ldo] or null
+  void* out;         // fp16 output
+  float* partial;    // fp32 [splitk][M][N] (EPI_PARTIAL and STAGE_LN)
+  // ---- attention / head split ----
+  int batch, heads, seq, head_dim;
+  float scale;       // softmax scale applied to Q.K
+  const int* lens;   // per-sequence valid length or null (selected at call time when lens_from_call)
+  int lens_from_call;
+  int tm_qkv;        // tensor map over the head-split buffer viewed as [3*B*heads*S][d], box 64 x 128
+  void* probs;       // optional fp16 [B*heads][S][S] normalised probabilities (debug / parity output)
+  // ---- layer norm ----
+  const void* gamma; // fp16 [N] or null
+  const void* beta;  // fp16 [N] or null
+  float eps;
+  int n_partial;     // number of fp32 partial planes to sum
+  int pad_;
+};
+
+constexpr int kMaxTensorMaps = 80;
+constexpr int kMaxStages = 96;
+
+}  // namespace souffle

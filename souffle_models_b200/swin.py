@@ -1,0 +1,107 @@
+"""Host-side mirror of the reference's Swin bindings over the C ABI
+(cpp/swin_transformer/swin_transformer_binding.cu:62-289, swin_trans_fc2_binding.cu:19-61)."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List
+
+import torch
+
+from . import _lib
+from .bert import _check_f16_cuda, _stream_ptr
+
+_ws = {}
+
+
+def _workspace() -> torch.Tensor:
+    dev = torch.cuda.current_device()
+    if dev not in _ws:
+        _ws[dev] = torch.zeros(int(_lib.load().souffle_gemm_workspace_bytes()), dtype=torch.uint8, device="cuda")
+    return _ws[dev]
+
+
+def gemm(a: torch.Tensor, w_kn: torch.Tensor, check: bool = True) -> torch.Tensor:
+    """c[M,N] = a[M,K] . w[K,N], fp16 in/out, fp32 accumulate."""
+    _check_f16_cuda(a, "a")
+    _check_f16_cuda(w_kn, "w")
+    M, K = a.shape
+    K2, N = w_kn.shape
+    if K2 != K:
+        raise ValueError(f"inner dimensions differ: {K} vs {K2}")
+    c = torch.empty(M, N, dtype=torch.float16, device=a.device)
+    ws = _workspace()
+    lib = _lib.load()
+    _lib.check(lib.souffle_gemm_f16(a.data_ptr(), w_kn.data_ptr(), c.data_ptr(), M, N, K, ws.data_ptr(),
+                                    ws.numel(), _stream_ptr()))
+    if check:
+        _lib.check(lib.souffle_workspace_status(ws.data_ptr(), _stream_ptr()))
+    return c
+
+
+def swin_ffn(src: torch.Tensor, weight: torch.Tensor, M: int, N: int, K: int) -> torch.Tensor:
+    """swin_transformer_binding.swin_ffn (swin_transformer_binding.cu:62-100): one GEMM.  The
+    reference only accepts (M,N,K) in {(256,2048,512), (256,512,2048)}; any K, N multiple of 64 works here."""
+    if tuple(src.shape) != (M, K) or tuple(weight.shape) != (K, N):
+        raise ValueError("src must be [M,K] and weight [K,N]")
+    return gemm(src, weight)
+
+
+def swin_trans_fc2(src: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """swin_trans_fc2.swin_trans_fc2 (swin_trans_fc2_binding.cu:19-55): src [1,256,2048] x weight [2048,512]."""
+    s2 = src.reshape(-1, src.shape[-1])
+    return gemm(s2, weight).reshape(*src.shape[:-1], weight.shape[1])
+
+
+def swin_fused_feed_mlp(src: torch.Tensor, fc1_weight: torch.Tensor, fc2_weight: torch.Tensor,
+                        check: bool = True) -> List[torch.Tensor]:
+    """swin_transformer_binding.swin_fused_feed_mlp (swin_transformer_binding.cu:155-209):
+    returns [fc1_output[M,F], fc2_output[M,C]] from one launch with a grid barrier between the GEMMs."""
+    for n, t in (("src", src), ("fc1_weight", fc1_weight), ("fc2_weight", fc2_weight)):
+        _check_f16_cuda(t, n)
+    M, Cc = src.shape
+    F = fc1_weight.shape[1]
+    if tuple(fc1_weight.shape) != (Cc, F) or tuple(fc2_weight.shape) != (F, Cc):
+        raise ValueError("fc1_weight must be [C,F] and fc2_weight [F,C]")
+    hidden = torch.empty(M, F, dtype=torch.float16, device=src.device)
+    out = torch.empty(M, Cc, dtype=torch.float16, device=src.device)
+    ws = _workspace()
+    lib = _lib.load()
+    _lib.check(lib.souffle_swin_mlp_forward(src.data_ptr(), fc1_weight.data_ptr(), fc2_weight.data_ptr(),
+                                            hidden.data_ptr(), out.data_ptr(), M, Cc, F, ws.data_ptr(), ws.numel(),
+                                            _stream_ptr()))
+    if check:
+        _lib.check(lib.souffle_workspace_status(ws.data_ptr(), _stream_ptr()))
+    return [hidden, out]
+
+
+def _bench(fn, num_warmup: int, num_bench: int, repeat: int) -> float:
+    """Minimum over `repeat` of the mean latency in microseconds of `num_bench` calls, timed
+    with CUDA events after `num_warmup` calls (cpp/souffle_utils/cuda_utils.h:102-136)."""
+    for _ in range(num_warmup):
+        fn()
+    best = float("inf")
+    for _ in range(repeat):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(num_bench):
+            fn()
+        e1.record()
+        e1.synchronize()
+        best = min(best, e0.elapsed_time(e1) * 1000.0 / num_bench)
+    return best
+
+
+def bench_swin_ffn(M: int, N: int, K: int, num_warmup: int, num_bench: int, repeat: int) -> float:
+    """swin_transformer_binding.bench_swin_ffn (swin_transformer_binding.cu:102-152)."""
+    src = torch.rand(M, K, device="cuda").half()
+    w = torch.rand(K, N, device="cuda").half()
+    return _bench(lambda: gemm(src, w, check=False), num_warmup, num_bench, repeat)
+
+
+def bench_swin_fused_feed_mlp(num_warmup: int, num_bench: int, repeat: int, M: int = 256, C_: int = 512,
+                              F: int = 2048) -> float:
+    """swin_transformer_binding.bench_swin_fused_feed_mlp (swin_transformer_binding.cu:211-273)."""
+    src = torch.rand(M, C_, device="cuda").half()
+    w1 = (torch.rand(C_, F, device="cuda") * 0.05).half()
+    w2 = (torch.rand(F, C_, device="cuda") * 0.05).half()
+    return _bench(lambda: swin_fused_feed_mlp(src, w1, w2, check=False), num_warmup, num_bench, repeat)
