@@ -68,6 +68,10 @@ typedef struct SouffleBertDesc {
   int32_t bn_qkv, bn_fc1, bn_proj, split_proj, bn_fc2, split_fc2;
   int32_t max_ctas;   /* 0 = one CTA per SM */
   int32_t timeout_ms; /* device-side wait limit, 0 = 2000 ms */
+  int32_t profile;    /* 1: record per-stage, per-CTA SM clock stamps (souffle_bert_plan_read_profile) */
+  int32_t debug_skip_arrival; /* failure-detection test hook, 0 = off: CTA (value-1) leaves at the first grid
+                                 barrier without arriving, so the others run into the wait limit and the
+                                 launch ends with SOUFFLE_DEVICE_TIMEOUT (nothing is in flight at that point) */
 } SouffleBertDesc;
 
 /* Device pointers to one layer's parameters, fp16.  Matrices use the reference's [K][N]
@@ -117,12 +121,43 @@ typedef enum SouffleBertBuffer {
   SOUFFLE_BUF_FC1 = 4    /* fp16 [B*S][F]  post-activation FFN hidden */
 } SouffleBertBuffer;
 int souffle_bert_plan_buffer(SouffleBertPlan* plan, int which, void** ptr_out, size_t* bytes_out);
+/* Copies one of those buffers into caller memory (device pointer, `dst_bytes` >= its size) on `stream`. */
+int souffle_bert_plan_copy_buffer(SouffleBertPlan* plan, int which, void* dst, size_t dst_bytes,
+                                  souffle_stream_t stream);
 
 /* Synchronises the plan's device and reports the device-side status of the last launch:
  * SOUFFLE_OK, or SOUFFLE_DEVICE_TIMEOUT with the stage/CTA in souffle_last_error(). */
 int souffle_bert_plan_status(SouffleBertPlan* plan);
+/* Per-stage stamps of the last launch (desc.profile=1): out[stage][cta][4] int64 SM-clock values
+ * {stage start, this CTA's work done, barrier left, 0}; differences within one CTA are cycles.
+ * The in-kernel counterpart of the reference's profile_grid_clock buffers
+ * (cpp/bert/kernels/fused_sqq_bert.cu:2330,2770; cpp/bert/bert_binding.cu:67-76).  Synchronises. */
+int souffle_bert_plan_read_profile(SouffleBertPlan* plan, int64_t* out, size_t capacity_elems);
 /* Number of kernels launched by the last forward call and the persistent grid size. */
 int souffle_bert_plan_info(SouffleBertPlan* plan, int* launches_out, int* grid_out, int* n_stages_out);
+
+/* ------------------------------------------------------------------------------------------
+ * Stacked LSTM, batch 1, as one wavefront launch.  Replaces fused_lstm<1,10,256,100>
+ * (cpp/lstm/lstm_binding.cu:30-72).  Gate order i, j, f, o with the forget bias of +1
+ * (cpp/lstm/lstm_reuse_shared_memory.cu:309-318).
+ * ------------------------------------------------------------------------------------------ */
+typedef struct SouffleLstmDesc {
+  int32_t layers;          /* 1..18 (8 CTAs per layer must be co-resident) */
+  int32_t hidden;          /* 64, 128 or 256 (input width == hidden) */
+  int32_t steps;           /* >= 1 */
+  int32_t ref_input_delay; /* 1: feed x one step late like the reference kernel (step 0 sees zeros, the last
+                              x is never consumed: lstm_reuse_shared_memory.cu:324-326); 0: standard */
+  int32_t timeout_ms;      /* device-side wait limit, 0 = 2000 ms */
+} SouffleLstmDesc;
+typedef struct SouffleLstmPlan SouffleLstmPlan;
+/* w_in / w_state: fp16 device [4*layers][hidden][hidden], index [4*layer + gate][out][in] (the reference's
+ * layout with fp16 storage); bias: fp32 device [layers][hidden] or null.  The plan keeps its own copies. */
+int souffle_lstm_plan_create(const SouffleLstmDesc* desc, const void* w_in, const void* w_state, const float* bias,
+                             SouffleLstmPlan** plan_out);
+int souffle_lstm_plan_destroy(SouffleLstmPlan* plan);
+/* y[steps][hidden] (fp32, top layer's h per step) from x[steps][hidden] (fp32); zero initial state. */
+int souffle_lstm_forward(SouffleLstmPlan* plan, const float* x, float* y, souffle_stream_t stream);
+int souffle_lstm_plan_status(SouffleLstmPlan* plan);
 
 /* ------------------------------------------------------------------------------------------
  * Plain fp16 GEMM with fp32 accumulation: c[M][N] = a[M][K] . w[K][N].

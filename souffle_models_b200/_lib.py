@@ -23,7 +23,7 @@ class BertDesc(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("batch", "seq", "heads", "head_dim", "ffn", "n_layers", "variant",
                                          "keep_probs")] + [("eps", C.c_float)] + \
                [(n, C.c_int32) for n in ("bn_qkv", "bn_fc1", "bn_proj", "split_proj", "bn_fc2", "split_fc2",
-                                         "max_ctas", "timeout_ms")]
+                                         "max_ctas", "timeout_ms", "profile", "debug_skip_arrival")]
 
 
 class BertLayerWeights(C.Structure):
@@ -44,8 +44,14 @@ SIGNATURES = {
     "souffle_bert_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "souffle_bert_forward_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "souffle_bert_plan_buffer": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_void_p), C.POINTER(C.c_size_t)]),
+    "souffle_bert_plan_copy_buffer": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]),
     "souffle_bert_plan_status": (C.c_int, [C.c_void_p]),
+    "souffle_bert_plan_read_profile": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),
     "souffle_bert_plan_info": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "souffle_lstm_plan_create": (C.c_int, [C.POINTER(LstmDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)]),
+    "souffle_lstm_plan_destroy": (C.c_int, [C.c_void_p]),
+    "souffle_lstm_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "souffle_lstm_plan_status": (C.c_int, [C.c_void_p]),
     "souffle_gemm_workspace_bytes": (C.c_size_t, []),
     "souffle_gemm_f16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
                                    C.c_void_p, C.c_size_t, C.c_void_p]),

@@ -105,18 +105,20 @@ class BertEncoder:
         _lib.check(self._lib.souffle_bert_plan_info(self._h, C.byref(a), C.byref(b), C.byref(c)))
         return dict(launches=a.value, grid=b.value, stages=c.value)
 
+    def read_profile(self) -> torch.Tensor:
+        """[stages, grid, 4] int64 SM-clock stamps of the last launch (needs tuning={'profile': 1})."""
+        i = self.info()
+        out = torch.zeros(i["stages"], i["grid"], 4, dtype=torch.int64)
+        _lib.check(self._lib.souffle_bert_plan_read_profile(self._h, out.data_ptr(), out.numel()))
+        return out
+
     def buffer(self, name: str) -> torch.Tensor:
         """Copy of a last-layer stage output (see SouffleBertBuffer in the header)."""
-        ptr, nbytes = C.c_void_p(), C.c_size_t()
-        _lib.check(self._lib.souffle_bert_plan_buffer(self._h, _BUF[name], C.byref(ptr), C.byref(nbytes)))
         B, S, h, d, H, F = self.batch, self.seq, self.heads, self.head_dim, self.hidden, self.ffn
         shape = dict(qkv=(3, B, h, S, d), probs=(B * h, S, S), ctx=(B * S, H), ln1=(B * S, H), fc1=(B * S, F))[name]
         out = torch.empty(shape, dtype=torch.float16, device="cuda")
-        assert out.numel() * 2 == nbytes.value
-        torch.cuda.current_stream().synchronize()
-        rc = torch.cuda.cudart().cudaMemcpy(out.data_ptr(), ptr.value, nbytes.value, 3)  # device to device
-        if int(rc) != 0:
-            raise _lib.SouffleError(5, f"cudaMemcpy failed with {int(rc)}")
+        _lib.check(self._lib.souffle_bert_plan_copy_buffer(self._h, _BUF[name], out.data_ptr(), out.numel() * 2,
+                                                           _stream_ptr()))
         return out
 
 

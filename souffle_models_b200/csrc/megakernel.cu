@@ -47,6 +47,8 @@ struct MegaParams {
   unsigned* sync_next;  // the pair the next launch will use; cleared by this launch
   int* status;        // [0] code, [1] where, [2] cta
   unsigned long long timeout_ns;
+  int skip_arrival;   // test hook: CTA (skip_arrival-1) leaves at barrier 0 without arriving; 0 = off
+  long long* prof;    // optional [n_stages][grid][4] clock64 stamps: stage start, work done, barrier left
 };
 
 // Everything a launch needs, passed in parameter space: per-call tensor maps (negative map
@@ -88,29 +90,27 @@ __device__ __forceinline__ const void* sel_ptr(int sel, const void* plan, const 
 }
 
 // ------------------------------------------------------------------------------------
-// grid barrier: sense by generation, self-resetting, bounded
+// grid barrier: one monotonic arrival counter per launch, bounded spin
 // ------------------------------------------------------------------------------------
 __device__ bool grid_barrier(const MegaParams& p, const WaitCtl& ctl, int where) {
   __threadfence();
   fence_proxy_async();
   __syncthreads();
   if (threadIdx.x == 0) {
+    if (p.prof) p.prof[((size_t)where * gridDim.x + blockIdx.x) * 4 + 1] = clock64();
+    // The counter only grows during a launch: barrier number `where` is passed once every CTA
+    // has added 1 for it.  (The launch that runs next clears the other counter, see the prologue.)
     unsigned* count = p.sync;
-    unsigned* gen = p.sync + 1;
-    const unsigned g = ld_acquire_u32(gen);
-    const unsigned prev = atom_add_release_u32(count, 1u);
-    if (prev == gridDim.x - 1) {
-      *reinterpret_cast<volatile unsigned*>(count) = 0u;
-      st_release_u32(gen, g + 1u);
-    } else {
-      uint32_t spins = 0;
-      while (ld_acquire_u32(gen) == g) {
-        if (((++spins) & 0x3F) == 0) {
-          if (*ctl.abort_smem) break;
-          if (globaltimer_ns() > ctl.deadline_ns) {
-            record_timeout(ctl, DEV_TIMEOUT_GRID, where);
-            break;
-          }
+    const unsigned target = (unsigned)(where + 1) * gridDim.x;
+    const bool skip = p.skip_arrival > 0 && where == 0 && (int)blockIdx.x == p.skip_arrival - 1;
+    if (skip) *ctl.abort_smem = 1; else atom_add_release_u32(count, 1u);
+    uint32_t spins = 0;
+    while (!skip && ld_acquire_u32(count) < target) {
+      if (((++spins) & 0x3F) == 0) {
+        if (*ctl.abort_smem) break;
+        if (globaltimer_ns() > ctl.deadline_ns) {
+          record_timeout(ctl, DEV_TIMEOUT_GRID, where);
+          break;
         }
       }
     }
@@ -234,7 +234,9 @@ __device__ void gemm_stage(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s,
           const uint32_t fb = full0 + 8 * s;
           mbar_expect_tx(fb, (uint32_t)g.slot_bytes);
           const uint32_t a_dst = ring + s * g.slot_bytes, b_dst = a_dst + kATileBytes;
-          const int k0 = (ks * g.kchunks + kc) * 64;
+          // CTAs start at different K chunks so they do not all pull the same A tile at once
+          const int kk = (kc + (int)blockIdx.x + item) % g.kchunks;
+          const int k0 = (ks * g.kchunks + kk) * 64;
           tma_load_2d(a_dst, tmA, fb, k0, mt * 128);
           if (!st.b_mn_major) {
             tma_load_2d(b_dst, tmB, fb, k0, nt * g.bn);
@@ -507,9 +509,21 @@ __device__ void attn_stage(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, 
 }
 
 // ------------------------------------------------------------------------------------
-// LayerNorm stage: one warp per row; sums split-K partial planes, adds bias and residual
+// LayerNorm stage: a warp normalises R rows at a time (R x NIT x 32-byte loads in flight per
+// lane); sums the split-K partial planes, adds bias and residual, two-pass statistics in fp32.
 // ------------------------------------------------------------------------------------
-__device__ void ln_stage(const Stage& st, const MegaParams& p, int warp, int lane) {
+__device__ __forceinline__ void add_h8(float* z, const uint4& u) {
+  const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __half22float2(h[j]);
+    z[2 * j] += f.x;
+    z[2 * j + 1] += f.y;
+  }
+}
+
+template <int NIT, int R>
+__device__ void ln_rows(const Stage& st, const MegaParams& p, int warp, int lane) {
   const int N = st.N, M = st.M;
   const __half* resid = reinterpret_cast<const __half*>(sel_ptr(st.resid_sel, st.resid, p));
   __half* out = reinterpret_cast<__half*>(const_cast<void*>(sel_ptr(st.out_sel, st.out, p)));
@@ -517,72 +531,102 @@ __device__ void ln_stage(const Stage& st, const MegaParams& p, int warp, int lan
   const __half* gamma = reinterpret_cast<const __half*>(st.gamma);
   const __half* beta = reinterpret_cast<const __half*>(st.beta);
   const int nwarps = kThreads / 32;
-  for (int row = blockIdx.x * nwarps + warp; row < M; row += gridDim.x * nwarps) {
-    float z[4][8];
-    float s1 = 0.0f;
+  const int total = gridDim.x * nwarps;
+  const float inv_n = 1.0f / (float)N;
+  for (int row0 = (blockIdx.x * nwarps + warp) * R; row0 < M; row0 += total * R) {
+    float z[R][NIT][8];
 #pragma unroll
-    for (int it = 0; it < 4; ++it) {
-      const int c = (lane + 32 * it) * 8;
+    for (int r = 0; r < R; ++r)
 #pragma unroll
-      for (int i = 0; i < 8; ++i) z[it][i] = 0.0f;
-      if (c < N) {
-        for (int pl = 0; pl < st.n_partial; ++pl) {
-          const float4* src = reinterpret_cast<const float4*>(st.partial + ((size_t)pl * M + row) * N + c);
-          const float4 a = src[0], b = src[1];
-          z[it][0] += a.x; z[it][1] += a.y; z[it][2] += a.z; z[it][3] += a.w;
-          z[it][4] += b.x; z[it][5] += b.y; z[it][6] += b.z; z[it][7] += b.w;
-        }
-        if (bias) {
-          const uint4 u = __ldg(reinterpret_cast<const uint4*>(bias + c));
-          const __half2* h = reinterpret_cast<const __half2*>(&u);
+      for (int it = 0; it < NIT; ++it)
 #pragma unroll
-          for (int j = 0; j < 4; ++j) { const float2 f = __half22float2(h[j]); z[it][2 * j] += f.x; z[it][2 * j + 1] += f.y; }
-        }
-        if (resid) {
-          const uint4 u = *reinterpret_cast<const uint4*>(resid + (size_t)row * st.ldo + c);
-          const __half2* h = reinterpret_cast<const __half2*>(&u);
+        for (int i = 0; i < 8; ++i) z[r][it][i] = 0.0f;
+#pragma unroll 2
+    for (int pl = 0; pl < st.n_partial; ++pl) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) { const float2 f = __half22float2(h[j]); z[it][2 * j] += f.x; z[it][2 * j + 1] += f.y; }
-        }
+      for (int r = 0; r < R; ++r) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) s1 += z[it][i];
-      }
-    }
-    const float mean = warp_sum(s1) / (float)N;
-    float s2 = 0.0f;
-#pragma unroll
-    for (int it = 0; it < 4; ++it) {
-      const int c = (lane + 32 * it) * 8;
-      if (c < N) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) { const float dlt = z[it][i] - mean; s2 += dlt * dlt; }
-      }
-    }
-    const float rstd = rsqrtf(warp_sum(s2) / (float)N + st.eps);
-#pragma unroll
-    for (int it = 0; it < 4; ++it) {
-      const int c = (lane + 32 * it) * 8;
-      if (c < N) {
-        float y[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) y[i] = (z[it][i] - mean) * rstd;
-        if (gamma) {
-          const uint4 ug = __ldg(reinterpret_cast<const uint4*>(gamma + c));
-          const uint4 ub = __ldg(reinterpret_cast<const uint4*>(beta + c));
-          const __half2* hg = reinterpret_cast<const __half2*>(&ug);
-          const __half2* hb = reinterpret_cast<const __half2*>(&ub);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 fg = __half22float2(hg[j]), fb = __half22float2(hb[j]);
-            y[2 * j] = y[2 * j] * fg.x + fb.x;
-            y[2 * j + 1] = y[2 * j + 1] * fg.y + fb.y;
+        for (int it = 0; it < NIT; ++it) {
+          const int c = (lane + 32 * it) * 8, row = row0 + r;
+          if (c < N && row < M) {
+            const float4* src = reinterpret_cast<const float4*>(st.partial + ((size_t)pl * M + row) * N + c);
+            const float4 a = src[0], b = src[1];
+            z[r][it][0] += a.x; z[r][it][1] += a.y; z[r][it][2] += a.z; z[r][it][3] += a.w;
+            z[r][it][4] += b.x; z[r][it][5] += b.y; z[r][it][6] += b.z; z[r][it][7] += b.w;
           }
         }
-        *reinterpret_cast<uint4*>(out + (size_t)row * st.ldo + c) =
-            make_uint4(pack_h2(y[0], y[1]), pack_h2(y[2], y[3]), pack_h2(y[4], y[5]), pack_h2(y[6], y[7]));
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+#pragma unroll
+      for (int it = 0; it < NIT; ++it) {
+        const int c = (lane + 32 * it) * 8, row = row0 + r;
+        if (c < N && row < M) {
+          if (resid) add_h8(z[r][it], *reinterpret_cast<const uint4*>(resid + (size_t)row * st.ldo + c));
+          if (bias) add_h8(z[r][it], __ldg(reinterpret_cast<const uint4*>(bias + c)));
+        }
+      }
+    }
+    float mean[R], rstd[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float s1 = 0.0f;
+#pragma unroll
+      for (int it = 0; it < NIT; ++it)
+        if ((lane + 32 * it) * 8 < N) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) s1 += z[r][it][i];
+        }
+      mean[r] = warp_sum(s1) * inv_n;
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float s2 = 0.0f;
+#pragma unroll
+      for (int it = 0; it < NIT; ++it)
+        if ((lane + 32 * it) * 8 < N) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { const float dlt = z[r][it][i] - mean[r]; s2 += dlt * dlt; }
+        }
+      rstd[r] = rsqrtf(warp_sum(s2) * inv_n + st.eps);
+    }
+#pragma unroll
+    for (int it = 0; it < NIT; ++it) {
+      const int c = (lane + 32 * it) * 8;
+      if (c < N) {
+        float g[8], bt[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { g[i] = 1.0f; bt[i] = 0.0f; }
+        if (gamma) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) g[i] = 0.0f;
+          add_h8(g, __ldg(reinterpret_cast<const uint4*>(gamma + c)));
+          add_h8(bt, __ldg(reinterpret_cast<const uint4*>(beta + c)));
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const int row = row0 + r;
+          if (row < M) {
+            float y[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) y[i] = (z[r][it][i] - mean[r]) * rstd[r] * g[i] + bt[i];
+            *reinterpret_cast<uint4*>(out + (size_t)row * st.ldo + c) =
+                make_uint4(pack_h2(y[0], y[1]), pack_h2(y[2], y[3]), pack_h2(y[4], y[5]), pack_h2(y[6], y[7]));
+          }
+        }
       }
     }
   }
+}
+
+__device__ void ln_stage(const Stage& st, const MegaParams& p, int warp, int lane) {
+  const int nit = (st.N + 255) / 256;
+  const bool many = st.M > gridDim.x * (kThreads / 32);     // more rows than warps: batch rows per warp
+  if (nit == 1) { if (many) ln_rows<1, 4>(st, p, warp, lane); else ln_rows<1, 1>(st, p, warp, lane); }
+  else if (nit == 2) { if (many) ln_rows<2, 4>(st, p, warp, lane); else ln_rows<2, 1>(st, p, warp, lane); }
+  else if (nit == 3) { if (many) ln_rows<3, 4>(st, p, warp, lane); else ln_rows<3, 1>(st, p, warp, lane); }
+  else { if (many) ln_rows<4, 2>(st, p, warp, lane); else ln_rows<4, 1>(st, p, warp, lane); }
 }
 
 // ------------------------------------------------------------------------------------
@@ -641,6 +685,7 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
       for (int i = threadIdx.x; i < (int)(sizeof(Stage) / 4); i += kThreads) dst[i] = src[i];
     }
     __syncthreads();
+    if (p.prof && threadIdx.x == 0) p.prof[((size_t)si * gridDim.x + blockIdx.x) * 4 + 0] = clock64();
     const Stage& st = cs.stage;
     if (st.type == STAGE_GEMM) {
       gemm_stage(st, ca, cs, ring, rs, ctl, warp, lane);
@@ -653,7 +698,9 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
       if (!grid_barrier(p, ctl, si)) break;
     } else {
       __syncthreads();
+      if (p.prof && threadIdx.x == 0) p.prof[((size_t)si * gridDim.x + blockIdx.x) * 4 + 1] = clock64();
     }
+    if (p.prof && threadIdx.x == 0) p.prof[((size_t)si * gridDim.x + blockIdx.x) * 4 + 2] = clock64();
     if (cs.abort) break;
   }
 

@@ -194,6 +194,7 @@ struct SouffleBertPlan {
   CUtensorMap* d_maps = nullptr;
   unsigned* d_sync = nullptr;   // two (count, generation) pairs
   int* d_status = nullptr;
+  long long* d_prof = nullptr;
   // plan-owned activations
   __half *qkv = nullptr, *ctx = nullptr, *ln1 = nullptr, *fc1 = nullptr, *probs = nullptr, *act[2] = {nullptr, nullptr};
   float* partial = nullptr;
@@ -396,6 +397,11 @@ static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* la
   }
   p->grid = max_items < sms ? max_items : sms;
 
+  if (d.profile) {
+    const size_t pb = p->stages.size() * (size_t)p->grid * 4 * sizeof(long long);
+    if ((rc = plan_alloc(p, (void**)&p->d_prof, pb))) return rc;
+    SF_CUDA(cudaMemset(p->d_prof, 0, pb));
+  }
   if ((rc = plan_alloc(p, (void**)&p->d_stages, p->stages.size() * sizeof(Stage)))) return rc;
   if ((rc = plan_alloc(p, (void**)&p->d_maps, p->maps.size() * sizeof(CUtensorMap)))) return rc;
   SF_CUDA(cudaMemcpy(p->d_stages, p->stages.data(), p->stages.size() * sizeof(Stage), cudaMemcpyHostToDevice));
@@ -476,6 +482,8 @@ int souffle_bert_forward(SouffleBertPlan* plan, const void* x, const int32_t* se
   mp.sync_next = plan->d_sync + 2 * (par ^ 1u);
   mp.status = plan->d_status;
   mp.timeout_ns = (unsigned long long)(d.timeout_ms > 0 ? d.timeout_ms : 2000) * 1000000ull;
+  mp.prof = plan->d_prof;
+  mp.skip_arrival = d.debug_skip_arrival;
   int rc = launch_mega(args, plan->grid, reinterpret_cast<cudaStream_t>(stream));
   if (rc) return rc;
   plan->launch_id++;
@@ -524,6 +532,17 @@ int souffle_bert_plan_buffer(SouffleBertPlan* plan, int which, void** ptr_out, s
   return SOUFFLE_OK;
 }
 
+int souffle_bert_plan_copy_buffer(SouffleBertPlan* plan, int which, void* dst, size_t dst_bytes,
+                                  souffle_stream_t stream) {
+  void* src = nullptr;
+  size_t bytes = 0;
+  int rc = souffle_bert_plan_buffer(plan, which, &src, &bytes);
+  if (rc) return rc;
+  if (!dst || dst_bytes < bytes) return fail(SOUFFLE_BAD_ARGUMENT, "destination holds %zu bytes, buffer has %zu", dst_bytes, bytes);
+  SF_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, reinterpret_cast<cudaStream_t>(stream)));
+  return SOUFFLE_OK;
+}
+
 int souffle_bert_plan_status(SouffleBertPlan* plan) {
   if (!plan) return fail(SOUFFLE_BAD_ARGUMENT, "null plan");
   SF_CUDA(cudaDeviceSynchronize());
@@ -535,6 +554,16 @@ int souffle_bert_plan_status(SouffleBertPlan* plan) {
     cudaMemset(plan->d_sync, 0, 64);
   }
   return decode_status(h, "souffle_bert_forward");
+}
+
+int souffle_bert_plan_read_profile(SouffleBertPlan* plan, int64_t* out, size_t capacity_elems) {
+  if (!plan || !out) return fail(SOUFFLE_BAD_ARGUMENT, "null argument");
+  if (!plan->d_prof) return fail(SOUFFLE_BAD_ARGUMENT, "the plan was created without desc.profile");
+  const size_t n = plan->stages.size() * (size_t)plan->grid * 4;
+  if (capacity_elems < n) return fail(SOUFFLE_BAD_ARGUMENT, "profile needs %zu elements, got %zu", n, capacity_elems);
+  SF_CUDA(cudaDeviceSynchronize());
+  SF_CUDA(cudaMemcpy(out, plan->d_prof, n * sizeof(long long), cudaMemcpyDeviceToHost));
+  return SOUFFLE_OK;
 }
 
 int souffle_bert_plan_info(SouffleBertPlan* plan, int* launches_out, int* grid_out, int* n_stages_out) {
@@ -617,6 +646,104 @@ int souffle_swin_mlp_forward(const void* src, const void* fc1_w, const void* fc2
   const int i2 = stage_items(args.inline_stages[1]);
   if (i2 > items) items = i2;
   return launch_mega(args, items < sms ? items : sms, st);
+}
+
+// ======================================================================================
+// LSTM plan
+// ======================================================================================
+struct SouffleLstmPlan {
+  SouffleLstmDesc desc;
+  __half *w_in = nullptr, *w_state = nullptr;
+  float *bias = nullptr, *h_all = nullptr;
+  unsigned* done = nullptr;   // two sets of [32] counters
+  int* status = nullptr;
+  unsigned launch_id = 0;
+  size_t smem = 0;
+};
+
+int souffle_lstm_plan_create(const SouffleLstmDesc* desc, const void* w_in, const void* w_state, const float* bias,
+                             SouffleLstmPlan** plan_out) {
+  if (!desc || !plan_out) return fail(SOUFFLE_BAD_ARGUMENT, "null argument");
+  *plan_out = nullptr;
+  const SouffleLstmDesc& d = *desc;
+  if (d.layers < 1 || d.layers > 18) return fail(SOUFFLE_BAD_SHAPE, "layers must be in 1..18 (got %d)", d.layers);
+  if (d.hidden != 64 && d.hidden != 128 && d.hidden != 256)
+    return fail(SOUFFLE_BAD_SHAPE, "hidden must be 64, 128 or 256 (got %d)", d.hidden);
+  if (d.steps < 1) return fail(SOUFFLE_BAD_SHAPE, "steps must be >= 1");
+  if (!aligned16(w_in) || !aligned16(w_state)) return fail(SOUFFLE_BAD_POINTER, "weights must be non-null and 16-byte aligned");
+  int dev = 0, cc = 0, sms = 0;
+  SF_CUDA(cudaGetDevice(&dev));
+  SF_CUDA(cudaDeviceGetAttribute(&cc, cudaDevAttrComputeCapabilityMajor, dev));
+  SF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  if (cc != 10) return fail(SOUFFLE_BAD_DEVICE, "device %d is not sm_100", dev);
+  SouffleLstmPlan* p = new SouffleLstmPlan();
+  p->desc = d;
+  const int H = d.hidden, rows = 4 * (H / kLstmParts);
+  p->smem = (size_t)rows * (2 * H * 2 + 64) + (size_t)(2 * H + rows) * 4 + 16;
+  const size_t wbytes = (size_t)4 * d.layers * H * H * 2;
+  cudaError_t e = cudaFuncSetAttribute(souffle_lstm_wavefront, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p->smem);
+  int per_sm = 0;
+  if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, souffle_lstm_wavefront, kLstmThreads, p->smem);
+  if (e == cudaSuccess && per_sm * sms < d.layers * kLstmParts) {
+    delete p;
+    return fail(SOUFFLE_NOT_CORESIDENT, "%d CTAs needed, %d can be resident", d.layers * kLstmParts, per_sm * sms);
+  }
+  if (e == cudaSuccess) e = cudaMalloc((void**)&p->w_in, wbytes);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&p->w_state, wbytes);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&p->h_all, (size_t)d.layers * d.steps * H * 4);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&p->done, 256);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&p->status, 64);
+  if (e == cudaSuccess && bias) e = cudaMalloc((void**)&p->bias, (size_t)d.layers * H * 4);
+  if (e == cudaSuccess) e = cudaMemcpy(p->w_in, w_in, wbytes, cudaMemcpyDeviceToDevice);
+  if (e == cudaSuccess) e = cudaMemcpy(p->w_state, w_state, wbytes, cudaMemcpyDeviceToDevice);
+  if (e == cudaSuccess && bias) e = cudaMemcpy(p->bias, bias, (size_t)d.layers * H * 4, cudaMemcpyDeviceToDevice);
+  if (e == cudaSuccess) e = cudaMemset(p->done, 0, 256);
+  if (e == cudaSuccess) e = cudaMemset(p->status, 0, 64);
+  if (e != cudaSuccess) {
+    souffle_lstm_plan_destroy(p);
+    return fail(SOUFFLE_CUDA_ERROR, "LSTM plan set-up failed: %s", cudaGetErrorString(e));
+  }
+  *plan_out = p;
+  return SOUFFLE_OK;
+}
+
+int souffle_lstm_plan_destroy(SouffleLstmPlan* p) {
+  if (!p) return SOUFFLE_OK;
+  cudaDeviceSynchronize();
+  cudaFree(p->w_in); cudaFree(p->w_state); cudaFree(p->bias); cudaFree(p->h_all); cudaFree(p->done); cudaFree(p->status);
+  delete p;
+  return SOUFFLE_OK;
+}
+
+int souffle_lstm_forward(SouffleLstmPlan* plan, const float* x, float* y, souffle_stream_t stream) {
+  if (!plan) return fail(SOUFFLE_BAD_ARGUMENT, "null plan");
+  if (!aligned16(x) || !aligned16(y)) return fail(SOUFFLE_BAD_POINTER, "x and y must be non-null and 16-byte aligned");
+  const SouffleLstmDesc& d = plan->desc;
+  LstmParams lp;
+  lp.w_in = plan->w_in; lp.w_state = plan->w_state; lp.bias = plan->bias; lp.x = x; lp.y = y; lp.h_all = plan->h_all;
+  const unsigned par = plan->launch_id & 1u;
+  lp.done = plan->done + 32 * par;
+  lp.done_next = plan->done + 32 * (par ^ 1u);
+  lp.status = plan->status;
+  lp.layers = d.layers; lp.hidden = d.hidden; lp.steps = d.steps; lp.ref_input_delay = d.ref_input_delay;
+  lp.timeout_ns = (unsigned long long)(d.timeout_ms > 0 ? d.timeout_ms : 2000) * 1000000ull;
+  void* kargs[] = {&lp};
+  SF_CUDA(cudaLaunchCooperativeKernel((const void*)souffle_lstm_wavefront, dim3(d.layers * kLstmParts), dim3(kLstmThreads),
+                                      kargs, plan->smem, reinterpret_cast<cudaStream_t>(stream)));
+  plan->launch_id++;
+  return SOUFFLE_OK;
+}
+
+int souffle_lstm_plan_status(SouffleLstmPlan* plan) {
+  if (!plan) return fail(SOUFFLE_BAD_ARGUMENT, "null plan");
+  SF_CUDA(cudaDeviceSynchronize());
+  int h[4] = {0, 0, 0, 0};
+  SF_CUDA(cudaMemcpy(h, plan->status, sizeof(h), cudaMemcpyDeviceToHost));
+  if (h[0] != DEV_OK) {
+    cudaMemset(plan->status, 0, 64);
+    cudaMemset(plan->done, 0, 256);
+  }
+  return decode_status(h, "souffle_lstm_forward");
 }
 
 int souffle_workspace_status(void* workspace, souffle_stream_t stream) {

@@ -1,0 +1,82 @@
+"""Host-side mirror of lstm_binding.fused_lstm (cpp/lstm/lstm_binding.cu:30-78) over the C ABI."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, Optional
+
+import torch
+
+from . import _lib
+from .bert import _stream_ptr
+
+
+class LstmStack:
+    """Plan for a stacked LSTM (batch 1): weights [4*layers, H, H] in [out][in] layout."""
+
+    def __init__(self, w_in: torch.Tensor, w_state: torch.Tensor, steps: int, bias: Optional[torch.Tensor] = None,
+                 ref_input_delay: bool = False):
+        lib = _lib.load()
+        if w_in.shape != w_state.shape or w_in.dim() != 3 or w_in.shape[0] % 4 or w_in.shape[1] != w_in.shape[2]:
+            raise ValueError("weights must both be [4*layers, hidden, hidden]")
+        for t in (w_in, w_state):
+            if not t.is_cuda:
+                raise ValueError("weights must be CUDA tensors")
+        self.layers, self.hidden, self.steps = w_in.shape[0] // 4, w_in.shape[1], steps
+        wi = w_in.to(torch.float16).contiguous()
+        ws = w_state.to(torch.float16).contiguous()
+        b = bias.to(torch.float32).contiguous() if bias is not None else None
+        d = _lib.LstmDesc(layers=self.layers, hidden=self.hidden, steps=steps, ref_input_delay=int(ref_input_delay))
+        self._h = C.c_void_p()
+        _lib.check(lib.souffle_lstm_plan_create(C.byref(d), wi.data_ptr(), ws.data_ptr(),
+                                                b.data_ptr() if b is not None else None, C.byref(self._h)))
+        self._lib = lib
+
+    def close(self) -> None:
+        if getattr(self, "_h", None) is not None and self._h.value:
+            self._lib.souffle_lstm_plan_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """x: fp32 CUDA [1, steps, hidden] -> fp32 [1, steps, hidden]; asynchronous."""
+        if not x.is_cuda or x.dtype != torch.float32 or not x.is_contiguous():
+            raise ValueError("x must be a contiguous float32 CUDA tensor")
+        if x.numel() != self.steps * self.hidden:
+            raise ValueError(f"x must hold {self.steps}x{self.hidden} values")
+        y = torch.empty_like(x)
+        _lib.check(self._lib.souffle_lstm_forward(self._h, x.data_ptr(), y.data_ptr(), _stream_ptr()))
+        return y
+
+    def status(self) -> None:
+        _lib.check(self._lib.souffle_lstm_plan_status(self._h))
+
+
+_cache: Dict[tuple, LstmStack] = {}
+
+
+def fused_lstm(input_timestep: torch.Tensor, weight_input_wavefront: torch.Tensor,
+               weight_state_wavefront: torch.Tensor) -> torch.Tensor:
+    """Drop-in for lstm_binding.fused_lstm: fp32 x [1,100,256], fp32 weights [40,256,256] x2 ->
+    fp32 [1,100,256].  Weights are stored as fp16 on the device (exact when they are fp16-valued)
+    and the plan is cached on their addresses and versions.  Inputs are consumed one step late,
+    as the reference kernel does (lstm_reuse_shared_memory.cu:324-326).  Blocking, like the reference."""
+    if not input_timestep.is_cuda:
+        raise ValueError("input_timestep must be a CUDA tensor")
+    if input_timestep.dim() != 3 or input_timestep.shape[0] != 1:
+        raise ValueError("input_timestep must be [1, steps, hidden]")
+    steps = input_timestep.shape[1]
+    key = (steps,) + tuple((t.data_ptr(), t._version, tuple(t.shape)) for t in (weight_input_wavefront, weight_state_wavefront))
+    plan = _cache.get(key)
+    if plan is None:
+        if len(_cache) >= 4:
+            _cache.pop(next(iter(_cache))).close()
+        plan = LstmStack(weight_input_wavefront, weight_state_wavefront, steps, ref_input_delay=True)
+        _cache[key] = plan
+    y = plan.forward(input_timestep.to(torch.float32).contiguous())
+    plan.status()
+    return y

@@ -1,0 +1,74 @@
+"""The C-ABI library loads, exports every symbol the header declares, and rejects bad
+arguments with status codes before touching a device (no GPU needed)."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from souffle_models_b200 import _lib, build
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_functions():
+    text = open(os.path.join(ROOT, "include", "souffle_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(souffle_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_builds_and_loads():
+    path = build.build()
+    assert os.path.exists(path)
+    lib = _lib.load()
+    assert lib.souffle_abi_version() >= 1
+
+
+def test_every_declared_symbol_is_exported_and_bound():
+    lib = _lib.load()
+    names = _declared_functions()
+    assert len(names) >= 15
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in the header but not exported"
+        assert n in _lib.SIGNATURES, f"{n} has no ctypes signature"
+    for n in _lib.SIGNATURES:
+        assert n in names, f"{n} bound in python but not declared in the header"
+
+
+def test_struct_layout_matches_header():
+    assert C.sizeof(_lib.BertDesc) == 4 * 19
+    assert C.sizeof(_lib.BertLayerWeights) == 8 * 12
+    assert C.sizeof(_lib.LstmDesc) == 4 * 5
+
+
+def test_argument_errors_need_no_device():
+    lib = _lib.load()
+    assert lib.souffle_bert_forward(None, None, None, None, None) == 7
+    assert b"null plan" in lib.souffle_last_error()
+    d = _lib.BertDesc(batch=1, seq=100, heads=12, head_dim=64, ffn=3072, n_layers=1)
+    w = (_lib.BertLayerWeights * 1)()
+    h = C.c_void_p()
+    assert lib.souffle_bert_plan_create(C.byref(d), w, C.byref(h)) == 1       # seq not a multiple of 16
+    assert b"seq" in lib.souffle_last_error()
+    d.seq, d.head_dim = 128, 32
+    assert lib.souffle_bert_plan_create(C.byref(d), w, C.byref(h)) == 1
+    d.head_dim, d.n_layers = 64, 13
+    assert lib.souffle_bert_plan_create(C.byref(d), w, C.byref(h)) == 1
+    assert lib.souffle_gemm_f16(None, None, None, 16, 100, 64, None, 0, None) == 1   # N % 64
+    assert lib.souffle_gemm_f16(None, None, None, 16, 128, 64, None, 0, None) == 2   # null pointers
+    assert lib.souffle_swin_mlp_forward(None, None, None, None, None, 256, 500, 2048, None, 0, None) == 1
+    assert lib.souffle_bert_plan_destroy(None) == 0
+    ld = _lib.LstmDesc(layers=0, hidden=256, steps=100)
+    assert lib.souffle_lstm_plan_create(C.byref(ld), None, None, None, C.byref(h)) in (1, 7)
+
+
+def test_python_mirror_validates_before_calling():
+    torch = pytest.importorskip("torch")
+    from souffle_models_b200 import bert, swin
+    x = torch.zeros(1, 128, 768, dtype=torch.float16)
+    with pytest.raises(ValueError):
+        bert.souffle_bert_layer(x, x, x, x, x, 7)           # unsupported opt level
+    with pytest.raises(ValueError):
+        bert.souffle_bert_layer(x, x, x, x, x, 3)           # CPU tensors
+    with pytest.raises(ValueError):
+        swin.swin_ffn(x[0], x[0], 1, 2, 3)
