@@ -177,6 +177,13 @@ int souffle_swin_mlp_forward(const void* src, const void* fc1_w, const void* fc2
                              int32_t M, int32_t C, int32_t F, void* workspace, size_t workspace_bytes,
                              souffle_stream_t stream);
 
+/* out[M][N] (fp16) = LayerNorm(sum_p partial[p][M][N] (fp32) + bias[N] + resid[M][N]) * gamma + beta, statistics
+ * in fp32 over each row; bias, resid, gamma/beta (fp16) may be null.  N % 8 == 0, N <= 1024.  This is the
+ * normalisation stage of the fused layer (cpp/bert/kernels/fused_sqq_bert.cu:3690-3782) as a call of its own. */
+int souffle_layernorm_forward(const float* partial, int32_t n_partial, const void* bias, const void* resid,
+                              const void* gamma, const void* beta, void* out, int32_t M, int32_t N, float eps,
+                              void* workspace, size_t workspace_bytes, souffle_stream_t stream);
+
 /* Blocks until `stream` is idle, then decodes the status words in `workspace`. */
 int souffle_workspace_status(void* workspace, souffle_stream_t stream);
 

@@ -57,6 +57,9 @@ SIGNATURES = {
                                    C.c_void_p, C.c_size_t, C.c_void_p]),
     "souffle_swin_mlp_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
                                            C.c_int32, C.c_int32, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "souffle_layernorm_forward": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                            C.c_void_p, C.c_int32, C.c_int32, C.c_float, C.c_void_p, C.c_size_t,
+                                            C.c_void_p]),
     "souffle_workspace_status": (C.c_int, [C.c_void_p, C.c_void_p]),
 }
 

@@ -535,14 +535,23 @@ __device__ void ln_rows(const Stage& st, const MegaParams& p, int warp, int lane
   const float inv_n = 1.0f / (float)N;
   for (int row0 = (blockIdx.x * nwarps + warp) * R; row0 < M; row0 += total * R) {
     float z[R][NIT][8];
+    // first partial plane: plain loads (all in flight together), further planes are added
 #pragma unroll
-    for (int r = 0; r < R; ++r)
+    for (int r = 0; r < R; ++r) {
 #pragma unroll
-      for (int it = 0; it < NIT; ++it)
-#pragma unroll
-        for (int i = 0; i < 8; ++i) z[r][it][i] = 0.0f;
-#pragma unroll 2
-    for (int pl = 0; pl < st.n_partial; ++pl) {
+      for (int it = 0; it < NIT; ++it) {
+        const int c = (lane + 32 * it) * 8, row = row0 + r;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+        if (c < N && row < M) {
+          const float4* src = reinterpret_cast<const float4*>(st.partial + (size_t)row * N + c);
+          a = __ldcs(src);
+          b = __ldcs(src + 1);
+        }
+        z[r][it][0] = a.x; z[r][it][1] = a.y; z[r][it][2] = a.z; z[r][it][3] = a.w;
+        z[r][it][4] = b.x; z[r][it][5] = b.y; z[r][it][6] = b.z; z[r][it][7] = b.w;
+      }
+    }
+    for (int pl = 1; pl < st.n_partial; ++pl) {
 #pragma unroll
       for (int r = 0; r < R; ++r) {
 #pragma unroll
@@ -550,7 +559,7 @@ __device__ void ln_rows(const Stage& st, const MegaParams& p, int warp, int lane
           const int c = (lane + 32 * it) * 8, row = row0 + r;
           if (c < N && row < M) {
             const float4* src = reinterpret_cast<const float4*>(st.partial + ((size_t)pl * M + row) * N + c);
-            const float4 a = src[0], b = src[1];
+            const float4 a = __ldcs(src), b = __ldcs(src + 1);
             z[r][it][0] += a.x; z[r][it][1] += a.y; z[r][it][2] += a.z; z[r][it][3] += a.w;
             z[r][it][4] += b.x; z[r][it][5] += b.y; z[r][it][6] += b.z; z[r][it][7] += b.w;
           }

@@ -648,6 +648,32 @@ int souffle_swin_mlp_forward(const void* src, const void* fc1_w, const void* fc2
   return launch_mega(args, items < sms ? items : sms, st);
 }
 
+int souffle_layernorm_forward(const float* partial, int32_t n_partial, const void* bias, const void* resid,
+                              const void* gamma, const void* beta, void* out, int32_t M, int32_t N, float eps,
+                              void* workspace, size_t workspace_bytes, souffle_stream_t stream) {
+  if (M < 1 || N < 8 || N % 8 || N > 1024 || n_partial < 1)
+    return fail(SOUFFLE_BAD_SHAPE, "LayerNorm needs M >= 1, N %% 8 == 0, N <= 1024, n_partial >= 1 (got %d, %d, %d)", M, N, n_partial);
+  if (!aligned16(partial) || !aligned16(out) || (bias && !aligned16(bias)) || (resid && !aligned16(resid)) ||
+      (gamma && !aligned16(gamma)) || (beta && !aligned16(beta)))
+    return fail(SOUFFLE_BAD_POINTER, "operands must be 16-byte aligned");
+  if ((gamma == nullptr) != (beta == nullptr)) return fail(SOUFFLE_BAD_ARGUMENT, "gamma and beta must be given together");
+  DeviceInfo* di = nullptr;
+  int rc = device_info(&di);
+  if (rc) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  CallArgs args;
+  memset(&args, 0, sizeof(args));
+  if ((rc = ws_prepare(workspace, workspace_bytes, st, &args.p))) return rc;
+  Stage& s = args.inline_stages[0];
+  s = blank_stage(STAGE_LN);
+  s.M = M; s.N = N; s.ldo = N; s.partial = const_cast<float*>(partial); s.n_partial = n_partial; s.bias = bias;
+  s.resid = resid; s.out = out; s.gamma = gamma; s.beta = beta; s.eps = eps;
+  args.p.n_stages = 1;
+  const int sms = di->sms < di->max_ctas ? di->sms : di->max_ctas;
+  const int items = stage_items(s);
+  return launch_mega(args, items < sms ? items : sms, st);
+}
+
 // ======================================================================================
 // LSTM plan
 // ======================================================================================

@@ -105,3 +105,20 @@ def bench_swin_fused_feed_mlp(num_warmup: int, num_bench: int, repeat: int, M: i
     w1 = (torch.rand(C_, F, device="cuda") * 0.05).half()
     w2 = (torch.rand(F, C_, device="cuda") * 0.05).half()
     return _bench(lambda: swin_fused_feed_mlp(src, w1, w2, check=False), num_warmup, num_bench, repeat)
+
+
+def layernorm(partial: torch.Tensor, resid=None, bias=None, gamma=None, beta=None, eps: float = 1e-5,
+              check: bool = True) -> torch.Tensor:
+    """out = LayerNorm(sum over planes of partial[P,M,N] (fp32) + bias + resid) * gamma + beta -> fp16 [M,N]."""
+    if partial.dtype != torch.float32 or not partial.is_cuda or partial.dim() != 3:
+        raise ValueError("partial must be a float32 CUDA tensor [P, M, N]")
+    P, M, N = partial.shape
+    out = torch.empty(M, N, dtype=torch.float16, device=partial.device)
+    ws = _workspace()
+    lib = _lib.load()
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    _lib.check(lib.souffle_layernorm_forward(partial.data_ptr(), P, ptr(bias), ptr(resid), ptr(gamma), ptr(beta),
+                                             out.data_ptr(), M, N, eps, ws.data_ptr(), ws.numel(), _stream_ptr()))
+    if check:
+        _lib.check(lib.souffle_workspace_status(ws.data_ptr(), _stream_ptr()))
+    return out

@@ -74,3 +74,15 @@ def test_fused_lstm_drop_in_signature():
     y = lstm.fused_lstm(x.float().cuda(), w_in.float().cuda(), w_st.float().cuda())
     assert y.shape == (1, 100, 256) and y.dtype == torch.float32
     assert (y.cpu() - so.lstm_forward(x, w_in, w_st, ref_input_delay=True)).abs().max() < 5e-3
+
+
+@pytest.mark.parametrize("P,M,N", [(1, 300, 768), (3, 64, 512), (2, 1000, 1024), (1, 5, 128)])
+def test_layernorm_entry_point(P, M, N):
+    from souffle_models_b200 import swin
+    g = torch.Generator().manual_seed(4)
+    part = torch.randn(P, M, N, generator=g)
+    resid, bias = _rand((M, N), 5), _rand((N,), 6, 0.1)
+    gamma, beta = (1 + torch.randn(N, generator=g) * 0.1).half(), _rand((N,), 7, 0.1)
+    out = swin.layernorm(part.cuda(), resid.cuda(), bias.cuda(), gamma.cuda(), beta.cuda(), eps=1e-12)
+    want = so.layer_norm(part.sum(0) + bias.float() + resid.float(), gamma, beta, 1e-12)
+    assert (out.float().cpu() - want).abs().max() < 5e-3
