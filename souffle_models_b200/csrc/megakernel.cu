@@ -40,6 +40,7 @@ struct MegaParams {
   const Stage* stages;        // plan-owned stage list, or null to use the inline stages
   int n_stages;
   const CUtensorMap* maps;    // plan-owned tensor maps (indices >= 0)
+  int n_maps;
   const void* x;
   void* y;
   const int* lens;
@@ -70,6 +71,7 @@ struct __align__(8) SmemCtl {
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint64_t qk_full, qk_empty, v_full, v_empty, s_full, p_full, o_full;
+  uint64_t ln_full[4];
   uint32_t tmem_base;
   int abort;
   Stage stage;        // current stage, copied once per stage
@@ -83,6 +85,7 @@ struct RoleState {
   uint32_t acc = 0;        // next accumulator buffer
   uint32_t acc_bits = 0;   // phase bit per accumulator buffer
   uint32_t attn_bit = 0;   // phase bit of the attention barriers
+  uint32_t ln_bits = 0;    // phase bit per LayerNorm batch buffer
 };
 
 __device__ __forceinline__ const void* sel_ptr(int sel, const void* plan, const MegaParams& p) {
@@ -509,133 +512,144 @@ __device__ void attn_stage(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, 
 }
 
 // ------------------------------------------------------------------------------------
-// LayerNorm stage: a warp normalises R rows at a time (R x NIT x 32-byte loads in flight per
-// lane); sums the split-K partial planes, adds bias and residual, two-pass statistics in fp32.
+// LayerNorm stage.  Rows stream through shared memory in batches fetched by bulk copies (all
+// split-K planes plus the residual of a batch are in flight together, several batches deep), so
+// the stage is bound by memory bandwidth rather than by per-warp load latency.  A warp owns a
+// row: z = sum of planes + bias + residual, two-pass statistics in fp32, fp16 output.
 // ------------------------------------------------------------------------------------
-__device__ __forceinline__ void add_h8(float* z, const uint4& u) {
-  const __half2* h = reinterpret_cast<const __half2*>(&u);
+constexpr int kLnMaxBufs = 4;
+
+template <int NJ>
+__device__ __forceinline__ void ln_row(const float* pl0, int n_partial, int plane_stride, const __half* res_row,
+                                       const __half* bias, const __half* gamma, const __half* beta, float eps,
+                                       __half* out_row, int lane) {
+  float z[NJ][4];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const float2 f = __half22float2(h[j]);
-    z[2 * j] += f.x;
-    z[2 * j + 1] += f.y;
+  for (int j = 0; j < NJ; ++j) {
+    const float4 a = *reinterpret_cast<const float4*>(pl0 + (lane + 32 * j) * 4);
+    z[j][0] = a.x; z[j][1] = a.y; z[j][2] = a.z; z[j][3] = a.w;
+  }
+  for (int pl = 1; pl < n_partial; ++pl) {
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+      const float4 a = *reinterpret_cast<const float4*>(pl0 + (size_t)pl * plane_stride + (lane + 32 * j) * 4);
+      z[j][0] += a.x; z[j][1] += a.y; z[j][2] += a.z; z[j][3] += a.w;
+    }
+  }
+  if (res_row) {
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+      const uint2 u = *reinterpret_cast<const uint2*>(res_row + (lane + 32 * j) * 4);
+      const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
+      const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+      z[j][0] += f0.x; z[j][1] += f0.y; z[j][2] += f1.x; z[j][3] += f1.y;
+    }
+  }
+  if (bias) {
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+      const uint2 u = __ldg(reinterpret_cast<const uint2*>(bias + (lane + 32 * j) * 4));
+      const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
+      const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+      z[j][0] += f0.x; z[j][1] += f0.y; z[j][2] += f1.x; z[j][3] += f1.y;
+    }
+  }
+  const float inv_n = 1.0f / (float)(NJ * 128);
+  float s1 = 0.0f;
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) s1 += (z[j][0] + z[j][1]) + (z[j][2] + z[j][3]);
+  const float mean = warp_sum(s1) * inv_n;
+  float s2 = 0.0f;
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float d = z[j][i] - mean; s2 = fmaf(d, d, s2); }
+  }
+  const float rstd = rsqrtf(warp_sum(s2) * inv_n + eps);
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) {
+    float y[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) y[i] = (z[j][i] - mean) * rstd;
+    if (gamma) {
+      const uint2 ug = __ldg(reinterpret_cast<const uint2*>(gamma + (lane + 32 * j) * 4));
+      const uint2 ub = __ldg(reinterpret_cast<const uint2*>(beta + (lane + 32 * j) * 4));
+      const float2 g0 = __half22float2(*reinterpret_cast<const __half2*>(&ug.x));
+      const float2 g1 = __half22float2(*reinterpret_cast<const __half2*>(&ug.y));
+      const float2 b0 = __half22float2(*reinterpret_cast<const __half2*>(&ub.x));
+      const float2 b1 = __half22float2(*reinterpret_cast<const __half2*>(&ub.y));
+      y[0] = fmaf(y[0], g0.x, b0.x); y[1] = fmaf(y[1], g0.y, b0.y);
+      y[2] = fmaf(y[2], g1.x, b1.x); y[3] = fmaf(y[3], g1.y, b1.y);
+    }
+    *reinterpret_cast<uint2*>(out_row + (lane + 32 * j) * 4) = make_uint2(pack_h2(y[0], y[1]), pack_h2(y[2], y[3]));
   }
 }
 
-template <int NIT, int R>
-__device__ void ln_rows(const Stage& st, const MegaParams& p, int warp, int lane) {
-  const int N = st.N, M = st.M;
+__device__ void ln_stage(const Stage& st, const MegaParams& p, SmemCtl& cs, uint32_t ring, uint8_t* ring_ptr,
+                         RoleState& rs, const WaitCtl& ctl, int warp, int lane) {
+  const int N = st.N, M = st.M, P = st.n_partial;
   const __half* resid = reinterpret_cast<const __half*>(sel_ptr(st.resid_sel, st.resid, p));
   __half* out = reinterpret_cast<__half*>(const_cast<void*>(sel_ptr(st.out_sel, st.out, p)));
   const __half* bias = reinterpret_cast<const __half*>(st.bias);
   const __half* gamma = reinterpret_cast<const __half*>(st.gamma);
   const __half* beta = reinterpret_cast<const __half*>(st.beta);
+  const int row_bytes = (P * 4 + (resid ? 2 : 0)) * N;
+  // rows per batch: about 52 KB per batch, at most 12 rows, and few enough that every CTA gets work
+  int rb = 53248 / row_bytes;
+  rb = rb > 12 ? 12 : (rb < 1 ? 1 : rb);
+  const int per_cta = (M + (int)gridDim.x - 1) / (int)gridDim.x;
+  if (rb > per_cta) rb = per_cta;
+  const int batch_bytes = rb * row_bytes;
+  int nbuf = kRingBytes / batch_bytes;
+  nbuf = nbuf > kLnMaxBufs ? kLnMaxBufs : nbuf;
+  const int n_batches = (M + rb - 1) / rb;
   const int nwarps = kThreads / 32;
-  const int total = gridDim.x * nwarps;
-  const float inv_n = 1.0f / (float)N;
-  for (int row0 = (blockIdx.x * nwarps + warp) * R; row0 < M; row0 += total * R) {
-    float z[R][NIT][8];
-    // first partial plane: plain loads (all in flight together), further planes are added
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-#pragma unroll
-      for (int it = 0; it < NIT; ++it) {
-        const int c = (lane + 32 * it) * 8, row = row0 + r;
-        float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
-        if (c < N && row < M) {
-          const float4* src = reinterpret_cast<const float4*>(st.partial + (size_t)row * N + c);
-          a = __ldcs(src);
-          b = __ldcs(src + 1);
-        }
-        z[r][it][0] = a.x; z[r][it][1] = a.y; z[r][it][2] = a.z; z[r][it][3] = a.w;
-        z[r][it][4] = b.x; z[r][it][5] = b.y; z[r][it][6] = b.z; z[r][it][7] = b.w;
-      }
-    }
-    for (int pl = 1; pl < st.n_partial; ++pl) {
-#pragma unroll
-      for (int r = 0; r < R; ++r) {
-#pragma unroll
-        for (int it = 0; it < NIT; ++it) {
-          const int c = (lane + 32 * it) * 8, row = row0 + r;
-          if (c < N && row < M) {
-            const float4* src = reinterpret_cast<const float4*>(st.partial + ((size_t)pl * M + row) * N + c);
-            const float4 a = __ldcs(src), b = __ldcs(src + 1);
-            z[r][it][0] += a.x; z[r][it][1] += a.y; z[r][it][2] += a.z; z[r][it][3] += a.w;
-            z[r][it][4] += b.x; z[r][it][5] += b.y; z[r][it][6] += b.z; z[r][it][7] += b.w;
-          }
-        }
-      }
-    }
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-#pragma unroll
-      for (int it = 0; it < NIT; ++it) {
-        const int c = (lane + 32 * it) * 8, row = row0 + r;
-        if (c < N && row < M) {
-          if (resid) add_h8(z[r][it], *reinterpret_cast<const uint4*>(resid + (size_t)row * st.ldo + c));
-          if (bias) add_h8(z[r][it], __ldg(reinterpret_cast<const uint4*>(bias + c)));
-        }
-      }
-    }
-    float mean[R], rstd[R];
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      float s1 = 0.0f;
-#pragma unroll
-      for (int it = 0; it < NIT; ++it)
-        if ((lane + 32 * it) * 8 < N) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) s1 += z[r][it][i];
-        }
-      mean[r] = warp_sum(s1) * inv_n;
-    }
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      float s2 = 0.0f;
-#pragma unroll
-      for (int it = 0; it < NIT; ++it)
-        if ((lane + 32 * it) * 8 < N) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) { const float dlt = z[r][it][i] - mean[r]; s2 += dlt * dlt; }
-        }
-      rstd[r] = rsqrtf(warp_sum(s2) * inv_n + st.eps);
-    }
-#pragma unroll
-    for (int it = 0; it < NIT; ++it) {
-      const int c = (lane + 32 * it) * 8;
-      if (c < N) {
-        float g[8], bt[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) { g[i] = 1.0f; bt[i] = 0.0f; }
-        if (gamma) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) g[i] = 0.0f;
-          add_h8(g, __ldg(reinterpret_cast<const uint4*>(gamma + c)));
-          add_h8(bt, __ldg(reinterpret_cast<const uint4*>(beta + c)));
-        }
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-          const int row = row0 + r;
-          if (row < M) {
-            float y[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) y[i] = (z[r][it][i] - mean[r]) * rstd[r] * g[i] + bt[i];
-            *reinterpret_cast<uint4*>(out + (size_t)row * st.ldo + c) =
-                make_uint4(pack_h2(y[0], y[1]), pack_h2(y[2], y[3]), pack_h2(y[4], y[5]), pack_h2(y[6], y[7]));
-          }
-        }
-      }
-    }
-  }
-}
 
-__device__ void ln_stage(const Stage& st, const MegaParams& p, int warp, int lane) {
-  const int nit = (st.N + 255) / 256;
-  const bool many = st.M > gridDim.x * (kThreads / 32);     // more rows than warps: batch rows per warp
-  if (nit == 1) { if (many) ln_rows<1, 4>(st, p, warp, lane); else ln_rows<1, 1>(st, p, warp, lane); }
-  else if (nit == 2) { if (many) ln_rows<2, 4>(st, p, warp, lane); else ln_rows<2, 1>(st, p, warp, lane); }
-  else if (nit == 3) { if (many) ln_rows<3, 4>(st, p, warp, lane); else ln_rows<3, 1>(st, p, warp, lane); }
-  else { if (many) ln_rows<4, 2>(st, p, warp, lane); else ln_rows<4, 1>(st, p, warp, lane); }
+  auto issue = [&](int batch, int buf) {
+    const int row0 = batch * rb;
+    const int rows = (M - row0) < rb ? (M - row0) : rb;
+    const uint32_t bar = smem_u32(&cs.ln_full[buf]);
+    const uint32_t dst = ring + buf * batch_bytes;
+    mbar_expect_tx(bar, (uint32_t)(rows * row_bytes));
+    for (int pl = 0; pl < P; ++pl)
+      bulk_load(dst + pl * rb * N * 4, st.partial + ((size_t)pl * M + row0) * N, (uint32_t)(rows * N * 4), bar);
+    if (resid) bulk_load(dst + P * rb * N * 4, resid + (size_t)row0 * N, (uint32_t)(rows * N * 2), bar);
+  };
+
+  if (threadIdx.x == 0) {
+    int b = blockIdx.x;
+    for (int j = 0; j < nbuf && b < n_batches; ++j, b += gridDim.x) issue(b, j);
+  }
+  int k = 0;
+  for (int batch = blockIdx.x; batch < n_batches; batch += gridDim.x, ++k) {
+    const int buf = k % nbuf;
+    bool ok = mbar_wait(smem_u32(&cs.ln_full[buf]), (rs.ln_bits >> buf) & 1u, ctl, 600 + buf);
+    ok = __all_sync(0xffffffffu, ok);
+    rs.ln_bits ^= 1u << buf;
+    if (!ok) break;
+    const int row0 = batch * rb;
+    const int rows = (M - row0) < rb ? (M - row0) : rb;
+    const float* base = reinterpret_cast<const float*>(ring_ptr + buf * batch_bytes);
+    const __half* rbase = reinterpret_cast<const __half*>(ring_ptr + buf * batch_bytes + P * rb * N * 4);
+    for (int r = warp; r < rows; r += nwarps) {
+      const float* pl0 = base + (size_t)r * N;
+      const __half* rr = resid ? rbase + (size_t)r * N : nullptr;
+      __half* orow = out + (size_t)(row0 + r) * N;
+      switch (N >> 7) {
+        case 1: ln_row<1>(pl0, P, rb * N, rr, bias, gamma, beta, st.eps, orow, lane); break;
+        case 2: ln_row<2>(pl0, P, rb * N, rr, bias, gamma, beta, st.eps, orow, lane); break;
+        case 3: ln_row<3>(pl0, P, rb * N, rr, bias, gamma, beta, st.eps, orow, lane); break;
+        case 4: ln_row<4>(pl0, P, rb * N, rr, bias, gamma, beta, st.eps, orow, lane); break;
+        case 5: ln_row<5>(pl0, P, rb * N, rr, bias, gamma, beta, st.eps, orow, lane); break;
+        case 6: ln_row<6>(pl0, P, rb * N, rr, bias, gamma, beta, st.eps, orow, lane); break;
+        case 7: ln_row<7>(pl0, P, rb * N, rr, bias, gamma, beta, st.eps, orow, lane); break;
+        default: ln_row<8>(pl0, P, rb * N, rr, bias, gamma, beta, st.eps, orow, lane); break;
+      }
+    }
+    __syncthreads();                       // every warp is done with this buffer before it is refilled
+    const int next = batch + nbuf * (int)gridDim.x;
+    if (threadIdx.x == 0 && next < n_batches) issue(next, buf);
+  }
 }
 
 // ------------------------------------------------------------------------------------
@@ -668,6 +682,7 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
     mbar_init(smem_u32(&cs.s_full), 1);
     mbar_init(smem_u32(&cs.p_full), 128);
     mbar_init(smem_u32(&cs.o_full), 1);
+    for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&cs.ln_full[i]), 1);
     cs.abort = 0;
     fence_mbar_init();
     if (blockIdx.x == 0) {          // the other launch parity's barrier words start clean
@@ -676,6 +691,9 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
     }
   }
   if (warp == 1) tmem_alloc(smem_u32(&cs.tmem_base), kTmemCols);
+  if (warp >= 2 && p.maps) {               // warm the descriptor cache while the CTA sets up
+    for (int i = (int)threadIdx.x - 64; i < p.n_maps; i += kThreads - 64) tma_prefetch_desc(p.maps + i);
+  }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -701,7 +719,7 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
     } else if (st.type == STAGE_ATTN) {
       attn_stage(st, ca, cs, ring, ring_ptr, rs, ctl, warp, lane);
     } else {
-      ln_stage(st, p, warp, lane);
+      ln_stage(st, p, cs, ring, ring_ptr, rs, ctl, warp, lane);
     }
     if (si + 1 < p.n_stages) {
       if (!grid_barrier(p, ctl, si)) break;
