@@ -116,7 +116,7 @@ static void choose_tiles(int M, int N, int K, int sms, bool allow_split, bool b_
       const long items = (long)tiles_m * (N / bn) * split;
       const long waves = (items + sms - 1) / sms;
       double cost = (double)waves * (kch / split) * (128.0 + 1.5 * bn) + (double)waves * 40.0;
-      if (allow_split) cost += (double)split * M * N * 8.0 / sms / 128.0;
+      if (allow_split) cost += 3.0 * (double)split * M * N * 8.0 / sms / 128.0;   // fp32 planes written, then re-read
       if (cost < best - 1e-9) {
         best = cost;
         best_bn = bn;
