@@ -159,6 +159,24 @@ int souffle_lstm_plan_destroy(SouffleLstmPlan* plan);
 int souffle_lstm_forward(SouffleLstmPlan* plan, const float* x, float* y, souffle_stream_t stream);
 int souffle_lstm_plan_status(SouffleLstmPlan* plan);
 
+/* Has no counterpart in the reference.  The same stacked-LSTM forward for callers that must not allocate
+ * device memory (a server whose memory pool owns the whole GPU, a plugin inside someone else's process, a
+ * loop that cannot take the device-wide synchronisation cudaMalloc/cudaFree imply): no plan, no cudaMalloc,
+ * cudaFree or other allocating call.  The kernel's scratch -- every published hidden state, the per-layer
+ * arrival counters, the status words -- sits in a fixed array inside the library image (about 1.5 MB held
+ * by every GPU that loads the library, until the process exits), so layers * steps * hidden must not exceed
+ * 12 * 128 * 256 = 393,216; larger shapes are rejected with SOUFFLE_BAD_SHAPE (use a plan for those).
+ * w_in / w_state (fp16 [4*layers][hidden][hidden]), bias (fp32 [layers][hidden] or null), x and y (fp32
+ * [steps][hidden]) are device pointers and are used in place, so they must stay valid until the work on
+ * `stream` has run.  `device_status` is optional: 4 device ints that receive {code, where, cta, 0}, code 0
+ * meaning every bounded wait was satisfied.  The first call on a device also looks up the array's device
+ * address and sets the kernel's attributes; make that first call before any stream capture begins.
+ * All calls share the one array and it keeps the previous call's contents: the counters and status words
+ * are cleared on `stream` at the start of each call, and two calls that overlap on the GPU (different
+ * streams, or different host threads) would race on it -- serialise them. */
+int souffle_lstm_forward_static(const SouffleLstmDesc* desc, const void* w_in, const void* w_state, const float* bias,
+                                const float* x, float* y, int32_t* device_status, souffle_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------
  * Plain fp16 GEMM with fp32 accumulation: c[M][N] = a[M][K] . w[K][N].
  * Replaces swin_ffn (swin_transformer_binding.cu:62-100, shapes (256,2048,512),(256,512,2048))

@@ -18,6 +18,7 @@
 #include "../../include/souffle_b200.h"
 #include "megakernel.cu"
 #include "lstm_kernel.cu"
+#include "lstm_static.cu"
 
 namespace souffle {
 
@@ -771,6 +772,64 @@ int souffle_lstm_plan_status(SouffleLstmPlan* plan) {
     cudaMemset(plan->done, 0, 256);
   }
   return decode_status(h, "souffle_lstm_forward");
+}
+
+// Allocation-free variant (see lstm_static.cu).  The first call on a device looks up the scratch
+// array's device address and sets the kernel attributes; make that call before any stream capture.
+int souffle_lstm_forward_static(const SouffleLstmDesc* desc, const void* w_in, const void* w_state, const float* bias,
+                                const float* x, float* y, int32_t* device_status, souffle_stream_t stream) {
+  if (!desc) return fail(SOUFFLE_BAD_ARGUMENT, "null descriptor");
+  const SouffleLstmDesc& d = *desc;
+  if (d.layers < 1 || d.layers > 18) return fail(SOUFFLE_BAD_SHAPE, "layers must be in 1..18 (got %d)", d.layers);
+  if (d.hidden != 64 && d.hidden != 128 && d.hidden != 256)
+    return fail(SOUFFLE_BAD_SHAPE, "hidden must be 64, 128 or 256 (got %d)", d.hidden);
+  if (d.steps < 1) return fail(SOUFFLE_BAD_SHAPE, "steps must be >= 1");
+  if ((size_t)d.layers * d.steps * d.hidden > kStaticHiddenFloats)
+    return fail(SOUFFLE_BAD_SHAPE, "layers*steps*hidden = %zu exceeds the built-in scratch of %zu values; use a plan",
+                (size_t)d.layers * d.steps * d.hidden, kStaticHiddenFloats);
+  if (!aligned16(w_in) || !aligned16(w_state) || !aligned16(x) || !aligned16(y))
+    return fail(SOUFFLE_BAD_POINTER, "w_in, w_state, x and y must be non-null and 16-byte aligned");
+  int dev = 0;
+  SF_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 16) return fail(SOUFFLE_BAD_DEVICE, "device index %d out of range", dev);
+  const int H = d.hidden, rows = 4 * (H / kLstmParts);
+  const size_t smem = (size_t)rows * (2 * H * 2 + 64) + (size_t)(2 * H + rows) * 4 + 16;
+  StaticLstmDevice& sd = g_static_lstm[dev];
+  if (!sd.ready) {
+    int cc = 0;
+    SF_CUDA(cudaDeviceGetAttribute(&cc, cudaDevAttrComputeCapabilityMajor, dev));
+    if (cc != 10) return fail(SOUFFLE_BAD_DEVICE, "device %d is not sm_100", dev);
+    SF_CUDA(cudaDeviceGetAttribute(&sd.sms, cudaDevAttrMultiProcessorCount, dev));
+    void* ptr = nullptr;
+    SF_CUDA(cudaGetSymbolAddress(&ptr, g_lstm_static_scratch));
+    sd.scratch = static_cast<unsigned char*>(ptr);
+    sd.ready = true;
+  }
+  // allow the largest shared-memory request any shape makes (a plan may have lowered the limit since)
+  SF_CUDA(cudaFuncSetAttribute(souffle_lstm_wavefront, cudaFuncAttributeMaxDynamicSharedMemorySize, 141840));
+  int per_sm = 0;
+  SF_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, souffle_lstm_wavefront, kLstmThreads, smem));
+  if (per_sm * sd.sms < d.layers * kLstmParts)
+    return fail(SOUFFLE_NOT_CORESIDENT, "%d CTAs needed, %d can be resident", d.layers * kLstmParts, per_sm * sd.sms);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  unsigned char* ctl = sd.scratch + kStaticHiddenFloats * 4;
+  // counters and status must start at zero; the hidden-state slots are all written before they are read
+  SF_CUDA(cudaMemsetAsync(ctl, 0, kStaticCtlBytes, st));
+  if (device_status) SF_CUDA(cudaMemsetAsync(device_status, 0, 16, st));
+  LstmParams lp;
+  lp.w_in = reinterpret_cast<const __half*>(w_in);
+  lp.w_state = reinterpret_cast<const __half*>(w_state);
+  lp.bias = bias; lp.x = x; lp.y = y;
+  lp.h_all = reinterpret_cast<float*>(sd.scratch);
+  lp.done = reinterpret_cast<unsigned*>(ctl);
+  lp.done_next = reinterpret_cast<unsigned*>(ctl + 128);
+  lp.status = device_status ? reinterpret_cast<int*>(device_status) : reinterpret_cast<int*>(ctl + 256);
+  lp.layers = d.layers; lp.hidden = d.hidden; lp.steps = d.steps; lp.ref_input_delay = d.ref_input_delay;
+  lp.timeout_ns = (unsigned long long)(d.timeout_ms > 0 ? d.timeout_ms : 2000) * 1000000ull;
+  void* kargs[] = {&lp};
+  SF_CUDA(cudaLaunchCooperativeKernel((const void*)souffle_lstm_wavefront, dim3(d.layers * kLstmParts), dim3(kLstmThreads),
+                                      kargs, smem, st));
+  return SOUFFLE_OK;
 }
 
 int souffle_workspace_status(void* workspace, souffle_stream_t stream) {
