@@ -69,6 +69,8 @@ typedef struct SouffleBertDesc {
   int32_t max_ctas;   /* 0 = one CTA per SM */
   int32_t timeout_ms; /* device-side wait limit, 0 = 2000 ms */
   int32_t profile;    /* 1: record per-stage, per-CTA SM clock stamps (souffle_bert_plan_read_profile) */
+  int32_t bm_qkv, bm_fc1, bm_proj, bm_fc2; /* tile heights (128 or 256), 0 = choose automatically */
+  int32_t debug_max_slots;    /* experiment knob: cap on operand ring slots per CTA, 0 = as many as fit */
   int32_t debug_skip_arrival; /* failure-detection test hook, 0 = off: CTA (value-1) leaves at the first grid
                                  barrier without arriving, so the others run into the wait limit and the
                                  launch ends with SOUFFLE_DEVICE_TIMEOUT (nothing is in flight at that point) */
@@ -128,8 +130,10 @@ int souffle_bert_plan_copy_buffer(SouffleBertPlan* plan, int which, void* dst, s
 /* Synchronises the plan's device and reports the device-side status of the last launch:
  * SOUFFLE_OK, or SOUFFLE_DEVICE_TIMEOUT with the stage/CTA in souffle_last_error(). */
 int souffle_bert_plan_status(SouffleBertPlan* plan);
-/* Per-stage stamps of the last launch (desc.profile=1): out[stage][cta][4] int64 SM-clock values
- * {stage start, this CTA's work done, barrier left, 0}; differences within one CTA are cycles.
+/* Per-stage stamps of the last launch (desc.profile=1): out[stage][cta][8] int64 SM-clock values
+ * {stage start, this CTA's work done, barrier left} and, for GEMM stages, cycle totals {MMA issuer waiting
+ * for operands, MMA issuer waiting for a free accumulator, producer waiting for a free ring slot, epilogue
+ * waiting for an accumulator, epilogue busy}; differences within one CTA are cycles.
  * The in-kernel counterpart of the reference's profile_grid_clock buffers
  * (cpp/bert/kernels/fused_sqq_bert.cu:2330,2770; cpp/bert/bert_binding.cu:67-76).  Synchronises. */
 int souffle_bert_plan_read_profile(SouffleBertPlan* plan, int64_t* out, size_t capacity_elems);

@@ -106,9 +106,10 @@ class BertEncoder:
         return dict(launches=a.value, grid=b.value, stages=c.value)
 
     def read_profile(self) -> torch.Tensor:
-        """[stages, grid, 4] int64 SM-clock stamps of the last launch (needs tuning={'profile': 1})."""
+        """[stages, grid, 8] int64 SM-clock stamps / role cycle totals of the last launch
+        (needs tuning={'profile': 1}; layout in include/souffle_b200.h)."""
         i = self.info()
-        out = torch.zeros(i["stages"], i["grid"], 4, dtype=torch.int64)
+        out = torch.zeros(i["stages"], i["grid"], 8, dtype=torch.int64)
         _lib.check(self._lib.souffle_bert_plan_read_profile(self._h, out.data_ptr(), out.numel()))
         return out
 

@@ -12,8 +12,9 @@
 //   cpp/swin_transformer/kernels/swin_fused_ffn_m256n2048k512_m256n512k2048.cu:9-769 fc1 -> fc2
 //   cpp/swin_transformer/kernels/gemm_three_stages.h:8-379 and kernels/gemm_k6.cu:9-339 single GEMMs
 //
-// Warp roles (192 threads): warp 0 = TMA producer (one elected lane), warp 1 = MMA issuer and
-// TMEM owner, warps 2..5 = epilogue / softmax (warp w reads TMEM lanes 32*(w%4) .. +31).
+// Warp roles (320 threads): warp 0 = TMA producer (one elected lane), warp 1 = MMA issuer and
+// TMEM owner, warps 2..9 = epilogue (warp w reads TMEM lanes 32*(w%4) .. +31; two warps share a
+// lane quarter and take alternate 32-column chunks); warps 2..5 are the attention softmax warps.
 // Every wait (mbarrier, grid barrier) is bounded by a wall-clock deadline; on expiry the CTA
 // records a status word, drains and returns, so a fault never leaves the GPU spinning.
 #include <cuda.h>
@@ -26,10 +27,16 @@
 
 namespace souffle {
 
-constexpr int kThreads = 192;
-constexpr int kRingBytes = 212992;          // 208 KiB operand ring (4 x 48 KiB or 6 x 32 KiB slots)
+constexpr int kThreads = 320;               // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
+constexpr int kRingBytes = 196608;          // 192 KiB operand ring (4 x 48 KiB, 3 x 64 KiB or 6 x 32 KiB slots)
 constexpr int kCtlBytes = 1024;             // barriers + control words
-constexpr int kSmemBytes = kCtlBytes + kRingBytes + 1024;  // + alignment slack
+constexpr int kVecBytes = 8192;              // per-stage bias vector staged in shared memory
+constexpr int kStageRow = 80;                // bytes per staged row: 64 B of payload + 16 B against bank conflicts
+constexpr int kStageWarp = 32 * kStageRow;   // one epilogue warp's transpose buffer
+constexpr int kStageBytes = 8 * kStageWarp;  // 20 KiB
+// Layout after the control block: ring | bias vector | store staging.  The attention stage with three
+// key blocks needs 208 KiB and simply runs over all three regions (it uses neither of the other two).
+constexpr int kSmemBytes = kCtlBytes + kRingBytes + kVecBytes + kStageBytes + 1024;  // + alignment slack
 constexpr int kMaxSlots = 8;
 constexpr uint32_t kTmemCols = 512;
 constexpr int kATileBytes = 128 * 64 * 2;   // 128 rows x 64 halves
@@ -48,8 +55,12 @@ struct MegaParams {
   unsigned* sync_next;  // the pair the next launch will use; cleared by this launch
   int* status;        // [0] code, [1] where, [2] cta
   unsigned long long timeout_ns;
+  int dbg_flags;      // experiment knob: 1 = epilogue does not store, 2 = epilogue does not read TMEM either
+  int max_slots;      // experiment knob: cap on operand ring slots, 0 = as many as fit
   int skip_arrival;   // test hook: CTA (skip_arrival-1) leaves at barrier 0 without arriving; 0 = off
-  long long* prof;    // optional [n_stages][grid][4] clock64 stamps: stage start, work done, barrier left
+  long long* prof;    // optional [n_stages][grid][8]: clock64 at stage start, work done, barrier left, then GEMM
+                      // role cycles: MMA waiting for operands, MMA waiting for a free accumulator, producer
+                      // waiting for a free slot, epilogue waiting for an accumulator, epilogue busy
 };
 
 // Everything a launch needs, passed in parameter space: per-call tensor maps (negative map
@@ -100,7 +111,7 @@ __device__ bool grid_barrier(const MegaParams& p, const WaitCtl& ctl, int where)
   fence_proxy_async();
   __syncthreads();
   if (threadIdx.x == 0) {
-    if (p.prof) p.prof[((size_t)where * gridDim.x + blockIdx.x) * 4 + 1] = clock64();
+    if (p.prof) p.prof[((size_t)where * gridDim.x + blockIdx.x) * 8 + 1] = clock64();
     // The counter only grows during a launch: barrier number `where` is passed once every CTA
     // has added 1 for it.  (The launch that runs next clears the other counter, see the prologue.)
     unsigned* count = p.sync;
@@ -127,42 +138,82 @@ __device__ bool grid_barrier(const MegaParams& p, const WaitCtl& ctl, int where)
 // GEMM stage
 // ------------------------------------------------------------------------------------
 struct GemmGeom {
-  int tiles_n, splitk, items, kchunks, bn, slot_bytes, nslots;
+  int tiles_n, splitk, items, kchunks, bn, bm, nh, slot_bytes, nslots;
 };
-__device__ __forceinline__ GemmGeom gemm_geom(const Stage& st) {
+__device__ __forceinline__ GemmGeom gemm_geom(const Stage& st, int max_slots) {
   GemmGeom g;
   g.bn = st.bn;
+  g.bm = st.bm == 256 ? 256 : 128;
+  g.nh = g.bm / 128;                       // 128-row halves per tile, each with its own accumulator
   g.tiles_n = st.N / st.bn;
   g.splitk = st.splitk;
-  g.items = ((st.M + 127) / 128) * g.tiles_n * g.splitk;
+  g.items = ((st.M + g.bm - 1) / g.bm) * g.tiles_n * g.splitk;
   g.kchunks = st.K / 64 / st.splitk;
-  g.slot_bytes = kATileBytes + st.bn * 128;
+  g.slot_bytes = g.nh * kATileBytes + st.bn * 128;
   int n = kRingBytes / g.slot_bytes;
   g.nslots = n > kMaxSlots ? kMaxSlots : n;
+  if (max_slots > 0 && g.nslots > max_slots) g.nslots = max_slots;
   return g;
 }
 
-template <int NC>
-__device__ __forceinline__ void epilogue_chunk(const Stage& st, const MegaParams& p, const uint32_t* r, int row,
-                                               int col, int ks, bool valid) {
-  if (st.epi == EPI_PARTIAL) {
-    if (valid) {
-      float4* dst = reinterpret_cast<float4*>(st.partial + ((size_t)ks * st.M + row) * st.N + col);
+// Epilogue parameters of a stage, copied into registers once (the stage record itself lives in
+// shared memory and would otherwise be re-read around every asm statement).
+struct EpiCtx {
+  int epi, act, M, N, ldo, heads, head_dim, seq;
+  size_t head_plane;       // seq * head_dim
+  size_t qkv_plane;        // batch * heads * seq * head_dim
+  const __half* bias_s;    // bias staged in shared memory, or null
+  const __half* resid;
+  __half* out;
+  float* partial;
+};
+
+// A thread that owns one row of a 32-row block holds 64 bytes of that row.  Written straight to global
+// memory, one store instruction would touch 32 different lines with 16 bytes each.  Going through the
+// warp's staging buffer turns that around: afterwards lanes 4j..4j+3 hold the 64 bytes of row j (+8, +16,
+// +24), so every store instruction writes eight rows with 64 contiguous bytes each.
+// `rowptr[i]` is the global byte address of row (8*i + lane/4) at this chunk's first column, or null.
+__device__ __forceinline__ void staged_store_64B(uint8_t* sbuf, const uint32_t (&w)[16], uint8_t* const (&rowptr)[4], int lane) {
+  uint4* mine = reinterpret_cast<uint4*>(sbuf + lane * kStageRow);
 #pragma unroll
-      for (int i = 0; i < NC / 4; ++i)
-        dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
-                             __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+  for (int i = 0; i < 4; ++i) mine[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint4 v = *reinterpret_cast<const uint4*>(sbuf + (8 * i + (lane >> 2)) * kStageRow + (lane & 3) * 16);
+    if (rowptr[i]) *reinterpret_cast<uint4*>(rowptr[i] + (lane & 3) * 16) = v;
+  }
+  __syncwarp();
+}
+
+// One 32-column chunk of the accumulator block: r[i] = column col+i of this thread's row `row`.
+// `trow[i]` = global row index of row (8*i + lane/4) of the same 32-row block (for the staged stores).
+__device__ __forceinline__ void epilogue_chunk32(const EpiCtx& e, uint8_t* sbuf, const uint32_t (&r)[32], int row,
+                                                 const int (&trow)[4], int col, int ks, int lane) {
+  uint8_t* rowptr[4];
+  if (e.epi == EPI_PARTIAL) {
+    // fp32 planes: two halves of 16 columns = 64 bytes per row each
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        rowptr[i] = trow[i] < e.M ? reinterpret_cast<uint8_t*>(e.partial + ((size_t)ks * e.M + trow[i]) * e.N + col + 16 * half)
+                                  : nullptr;
+      uint32_t w[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) w[i] = r[16 * half + i];
+      staged_store_64B(sbuf, w, rowptr, lane);
     }
     return;
   }
-  float v[NC];
+  float v[32];
 #pragma unroll
-  for (int i = 0; i < NC; ++i) v[i] = __uint_as_float(r[i]);
-  if (st.bias) {
-    const uint4* b4 = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(st.bias) + col);
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+  if (e.bias_s) {
+    const uint4* b4 = reinterpret_cast<const uint4*>(e.bias_s + col);
 #pragma unroll
-    for (int i = 0; i < NC / 8; ++i) {
-      const uint4 u = __ldg(b4 + i);
+    for (int i = 0; i < 4; ++i) {
+      const uint4 u = b4[i];
       const __half2* h = reinterpret_cast<const __half2*>(&u);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -172,19 +223,17 @@ __device__ __forceinline__ void epilogue_chunk(const Stage& st, const MegaParams
       }
     }
   }
-  if (st.act == ACT_RELU) {
+  if (e.act == ACT_RELU) {
 #pragma unroll
-    for (int i = 0; i < NC; ++i) v[i] = fmaxf(v[i], 0.0f);
-  } else if (st.act == ACT_GELU) {
+    for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.0f);
+  } else if (e.act == ACT_GELU) {
 #pragma unroll
-    for (int i = 0; i < NC; ++i) v[i] = gelu_tanh(v[i]);
+    for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
   }
-  if (!valid) return;
-  const __half* resid = reinterpret_cast<const __half*>(sel_ptr(st.resid_sel, st.resid, p));
-  if (resid) {
-    const uint4* r4 = reinterpret_cast<const uint4*>(resid + (size_t)row * st.ldo + col);
+  if (e.resid && row < e.M) {
+    const uint4* r4 = reinterpret_cast<const uint4*>(e.resid + (size_t)row * e.ldo + col);
 #pragma unroll
-    for (int i = 0; i < NC / 8; ++i) {
+    for (int i = 0; i < 4; ++i) {
       const uint4 u = r4[i];
       const __half2* h = reinterpret_cast<const __half2*>(&u);
 #pragma unroll
@@ -195,31 +244,98 @@ __device__ __forceinline__ void epilogue_chunk(const Stage& st, const MegaParams
       }
     }
   }
-  __half* out = reinterpret_cast<__half*>(const_cast<void*>(sel_ptr(st.out_sel, st.out, p)));
-  __half* dst;
-  if (st.epi == EPI_QKV) {
-    const int hidden = st.heads * st.head_dim;
-    const int j = col / hidden, rem = col - j * hidden;
-    const int hh = rem / st.head_dim, dd = rem - hh * st.head_dim;
-    const int b = row / st.seq, s = row - b * st.seq;
-    dst = out + ((((size_t)j * st.batch + b) * st.heads + hh) * st.seq + s) * st.head_dim + dd;
-  } else {
-    dst = out + (size_t)row * st.ldo + col;
-  }
-  uint4* d4 = reinterpret_cast<uint4*>(dst);
+  if (e.epi == EPI_QKV) {
+    // [3][B][heads][S][d]: column -> (which of q/k/v, head, offset in head); row -> (sequence, token)
+    const int g = col / e.head_dim, dd = col - g * e.head_dim;      // g = which * heads + head
+    const int which = g / e.heads, hh = g - which * e.heads;
+    const size_t coloff = (size_t)which * e.qkv_plane + (size_t)hh * e.head_plane + dd;
 #pragma unroll
-  for (int i = 0; i < NC / 8; ++i)
-    d4[i] = make_uint4(pack_h2(v[8 * i], v[8 * i + 1]), pack_h2(v[8 * i + 2], v[8 * i + 3]),
-                       pack_h2(v[8 * i + 4], v[8 * i + 5]), pack_h2(v[8 * i + 6], v[8 * i + 7]));
+    for (int i = 0; i < 4; ++i) {
+      const int b = trow[i] / e.seq, sq = trow[i] - b * e.seq;
+      rowptr[i] = trow[i] < e.M ? reinterpret_cast<uint8_t*>(e.out + coloff + (size_t)b * e.heads * e.head_plane + (size_t)sq * e.head_dim)
+                                : nullptr;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      rowptr[i] = trow[i] < e.M ? reinterpret_cast<uint8_t*>(e.out + (size_t)trow[i] * e.ldo + col) : nullptr;
+  }
+  uint32_t w[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) w[i] = pack_h2(v[2 * i], v[2 * i + 1]);
+  staged_store_64B(sbuf, w, rowptr, lane);
 }
 
-__device__ void gemm_stage(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s,
-                           uint32_t ring, RoleState& rs, const WaitCtl& ctl, int warp, int lane) {
+// 16-column tail chunk (tile widths that are an odd multiple of 16): direct stores.
+__device__ __forceinline__ void epilogue_chunk16(const EpiCtx& e, const uint32_t (&r)[16], int row, int col, int ks) {
+  if (row >= e.M) return;
+  if (e.epi == EPI_PARTIAL) {
+    float4* dst = reinterpret_cast<float4*>(e.partial + ((size_t)ks * e.M + row) * e.N + col);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]),
+                           __uint_as_float(r[4 * i + 3]));
+    return;
+  }
+  float v[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+  if (e.bias_s) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(e.bias_s + col + 2 * i));
+      v[2 * i] += f.x;
+      v[2 * i + 1] += f.y;
+    }
+  }
+  if (e.act == ACT_RELU) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = fmaxf(v[i], 0.0f);
+  } else if (e.act == ACT_GELU) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = gelu_tanh(v[i]);
+  }
+  if (e.resid) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(e.resid + (size_t)row * e.ldo + col + 2 * i));
+      v[2 * i] += f.x;
+      v[2 * i + 1] += f.y;
+    }
+  }
+  __half* dst;
+  if (e.epi == EPI_QKV) {
+    const int g = col / e.head_dim, dd = col - g * e.head_dim;
+    const int which = g / e.heads, hh = g - which * e.heads;
+    const int b = row / e.seq, sq = row - b * e.seq;
+    dst = e.out + (size_t)which * e.qkv_plane + ((size_t)b * e.heads + hh) * e.head_plane + (size_t)sq * e.head_dim + dd;
+  } else {
+    dst = e.out + (size_t)row * e.ldo + col;
+  }
+  uint4* d4 = reinterpret_cast<uint4*>(dst);
+  d4[0] = make_uint4(pack_h2(v[0], v[1]), pack_h2(v[2], v[3]), pack_h2(v[4], v[5]), pack_h2(v[6], v[7]));
+  d4[1] = make_uint4(pack_h2(v[8], v[9]), pack_h2(v[10], v[11]), pack_h2(v[12], v[13]), pack_h2(v[14], v[15]));
+}
+
+// Tiles are bm x bn with bm = 128 (two accumulators used alternately, so the epilogue of one tile
+// overlaps the main loop of the next) or bm = 256 (two 128-row halves share every B tile, which
+// halves the B traffic per FLOP; each half has its own accumulator and hand-shake).
+__device__ void gemm_stage(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, uint32_t ring, __half* vec_s,
+                           uint8_t* stage_s, RoleState& rs, const WaitCtl& ctl, int warp, int lane) {
   const MegaParams& p = ca.p;
-  const GemmGeom g = gemm_geom(st);
+  const GemmGeom g = gemm_geom(st, p.max_slots);
   if (rs.slot >= (uint32_t)g.nslots) rs.slot = 0;
   const uint32_t full0 = smem_u32(&ctl_s.full[0]), empty0 = smem_u32(&ctl_s.empty[0]);
   const uint32_t tfull0 = smem_u32(&ctl_s.tmem_full[0]), tempty0 = smem_u32(&ctl_s.tmem_empty[0]);
+  const uint32_t a_bytes = (uint32_t)(g.nh * kATileBytes);
+  // the stage's bias vector -> shared memory (one global read per CTA instead of one per tile chunk)
+  const __half* bias_s = nullptr;
+  if (st.bias && st.epi != EPI_PARTIAL && st.N * 2 <= kVecBytes) {
+    const uint4* src = reinterpret_cast<const uint4*>(st.bias);
+    for (int i = threadIdx.x; i < st.N / 8; i += kThreads) reinterpret_cast<uint4*>(vec_s)[i] = __ldg(src + i);
+    bias_s = vec_s;
+    __syncthreads();
+  }
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -227,29 +343,38 @@ __device__ void gemm_stage(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s,
       const CUtensorMap* tmA = map_ptr(ca, st.tm_a);
       const CUtensorMap* tmB = map_ptr(ca, st.tm_b);
       bool ok = true;
+      long long t_wait = 0;
+      const bool prof = p.prof != nullptr;
+      uint32_t s = rs.slot, bits = rs.slot_bits;
       for (int item = blockIdx.x; ok && item < g.items; item += gridDim.x) {
         const int ks = item % g.splitk;
         const int nt = (item / g.splitk) % g.tiles_n;
         const int mt = item / (g.splitk * g.tiles_n);
+        const int m0 = mt * g.bm, n0 = nt * g.bn, kbase = ks * g.kchunks;
+        // CTAs start at different K chunks so they do not all pull the same A tile at once
+        int kk = (int)((blockIdx.x + (unsigned)item) % (unsigned)g.kchunks);
         for (int kc = 0; kc < g.kchunks; ++kc) {
-          const uint32_t s = rs.slot;
-          if (!mbar_wait(empty0 + 8 * s, ((rs.slot_bits >> s) & 1u) ^ 1u, ctl, 100 + (int)s)) { ok = false; break; }
+          const long long tw = prof ? clock64() : 0;
+          if (!mbar_wait(empty0 + 8 * s, ((bits >> s) & 1u) ^ 1u, ctl, 100 + (int)s)) { ok = false; break; }
+          if (prof) t_wait += clock64() - tw;
           const uint32_t fb = full0 + 8 * s;
           mbar_expect_tx(fb, (uint32_t)g.slot_bytes);
-          const uint32_t a_dst = ring + s * g.slot_bytes, b_dst = a_dst + kATileBytes;
-          // CTAs start at different K chunks so they do not all pull the same A tile at once
-          const int kk = (kc + (int)blockIdx.x + item) % g.kchunks;
-          const int k0 = (ks * g.kchunks + kk) * 64;
-          tma_load_2d(a_dst, tmA, fb, k0, mt * 128);
+          const uint32_t a_dst = ring + s * g.slot_bytes, b_dst = a_dst + a_bytes;
+          const int k0 = (kbase + kk) * 64;
+          tma_load_2d(a_dst, tmA, fb, k0, m0);                  // box rows = bm: both halves in one copy
           if (!st.b_mn_major) {
-            tma_load_2d(b_dst, tmB, fb, k0, nt * g.bn);
+            tma_load_2d(b_dst, tmB, fb, k0, n0);
           } else {
-            for (int j = 0; j < g.bn / 64; ++j) tma_load_2d(b_dst + j * 8192, tmB, fb, nt * g.bn + j * 64, k0);
+            for (int j = 0; j < g.bn / 64; ++j) tma_load_2d(b_dst + j * 8192, tmB, fb, n0 + j * 64, k0);
           }
-          rs.slot_bits ^= 1u << s;
-          rs.slot = (s + 1 == (uint32_t)g.nslots) ? 0 : s + 1;
+          bits ^= 1u << s;
+          s = (s + 1 == (uint32_t)g.nslots) ? 0 : s + 1;
+          kk = (kk + 1 == g.kchunks) ? 0 : kk + 1;
         }
       }
+      rs.slot = s;
+      rs.slot_bits = bits;
+      if (p.prof) p.prof[((size_t)st.prof_index * gridDim.x + blockIdx.x) * 8 + 5] = t_wait;
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -257,67 +382,127 @@ __device__ void gemm_stage(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s,
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_f16((uint32_t)g.bn, (uint32_t)st.b_mn_major);
       const uint32_t tmem = ctl_s.tmem_base;
+      // descriptor low words of slot 0; a slot further on adds slot_bytes/16 to both
+      const uint32_t a_lo0 = umma_desc_lo(ring, 16);
+      const uint32_t b_lo0 = umma_desc_lo(ring + a_bytes, st.b_mn_major ? 8192u : 16u);
+      const uint32_t slot16 = (uint32_t)g.slot_bytes >> 4;
+      const uint32_t bstep = st.b_mn_major ? 128u : 2u;       // 16 K-rows = 2048 B, or 16 halves = 32 B
+      const bool prof = p.prof != nullptr;
       bool ok = true;
+      long long t_full = 0, t_acc = 0;
       for (int item = blockIdx.x; ok && item < g.items; item += gridDim.x) {
-        const uint32_t acc = rs.acc;
-        if (!mbar_wait(tempty0 + 8 * acc, ((rs.acc_bits >> acc) & 1u) ^ 1u, ctl, 200 + (int)acc)) break;
-        tc_fence_after_sync();
-        const uint32_t d = tmem + acc * kAccStride;
-        for (int kc = 0; kc < g.kchunks; ++kc) {
-          const uint32_t s = rs.slot;
-          if (!mbar_wait(full0 + 8 * s, (rs.slot_bits >> s) & 1u, ctl, 300 + (int)s)) { ok = false; break; }
+        const uint32_t acc0 = g.nh == 2 ? 0u : rs.acc;       // accumulator of half 0; half 1 uses buffer 1
+        const uint32_t d0 = tmem + acc0 * kAccStride, d1 = d0 + kAccStride;
+        {                                                      // the epilogue must have drained the buffers
+          const long long ta = prof ? clock64() : 0;
+          for (int h = 0; h < g.nh; ++h) {
+            const uint32_t acc = acc0 + (uint32_t)h;
+            if (!mbar_wait(tempty0 + 8 * acc, ((rs.acc_bits >> acc) & 1u) ^ 1u, ctl, 200 + (int)acc)) { ok = false; break; }
+          }
           tc_fence_after_sync();
-          const uint32_t a_addr = ring + s * g.slot_bytes, b_addr = a_addr + kATileBytes;
-          const uint64_t ad = umma_desc_sw128(a_addr, 16, 1024);
-          const uint64_t bd = st.b_mn_major ? umma_desc_sw128(b_addr, 8192, 1024) : umma_desc_sw128(b_addr, 16, 1024);
-          const uint32_t bstep = st.b_mn_major ? 128u : 2u;   // 16 K-rows = 2048 B, or 16 halves = 32 B
-#pragma unroll
-          for (uint32_t k = 0; k < 4; ++k)
-            umma_f16(d, ad + 2u * k, bd + bstep * k, idesc, (uint32_t)((kc | (int)k) != 0));
+          if (prof) t_acc += clock64() - ta;
+        }
+        for (int kc = 0; ok && kc < g.kchunks; ++kc) {
+          const uint32_t s = rs.slot;
+          const long long tw = prof ? clock64() : 0;
+          if (!mbar_wait(full0 + 8 * s, (rs.slot_bits >> s) & 1u, ctl, 300 + (int)s)) { ok = false; break; }
+          if (prof) t_full += clock64() - tw;
+          tc_fence_after_sync();
+          const uint32_t a_lo = a_lo0 + s * slot16, b_lo = b_lo0 + s * slot16;
+          if (g.nh == 2) umma_f16_k64_x2(d0, d1, a_lo, b_lo, bstep, idesc, (uint32_t)(kc != 0));
+          else umma_f16_k64(d0, a_lo, b_lo, bstep, idesc, (uint32_t)(kc != 0));
           umma_commit(empty0 + 8 * s);
           rs.slot_bits ^= 1u << s;
           rs.slot = (s + 1 == (uint32_t)g.nslots) ? 0 : s + 1;
         }
         if (!ok) break;
-        umma_commit(tfull0 + 8 * acc);
-        rs.acc_bits ^= 1u << acc;
-        rs.acc ^= 1u;
+        for (int h = 0; h < g.nh; ++h) {
+          const uint32_t acc = acc0 + (uint32_t)h;
+          umma_commit(tfull0 + 8 * acc);
+          rs.acc_bits ^= 1u << acc;
+        }
+        if (g.nh == 1) rs.acc ^= 1u;
+      }
+      if (p.prof) {
+        long long* pr = p.prof + ((size_t)st.prof_index * gridDim.x + blockIdx.x) * 8;
+        pr[3] = t_full;
+        pr[4] = t_acc;
       }
     }
     __syncwarp();
   } else {
-    // ---------------- epilogue: TMEM -> registers -> global ----------------
-    const int q = warp & 3;
+    // ---------------- epilogue: TMEM -> registers -> global (8 warps: lane quarter x column parity) --
+    const int q = warp & 3, cpar = (warp - 2) >> 2;
     const uint32_t tmem = ctl_s.tmem_base + ((uint32_t)(q * 32) << 16);
+    const int full_chunks = g.bn >> 5;
+    EpiCtx e;
+    e.epi = st.epi; e.act = st.act; e.M = st.M; e.N = st.N; e.ldo = st.ldo;
+    e.heads = st.heads; e.head_dim = st.head_dim; e.seq = st.seq;
+    e.head_plane = (size_t)st.seq * st.head_dim;
+    e.qkv_plane = (size_t)st.batch * st.heads * e.head_plane;
+    e.bias_s = bias_s;
+    e.resid = reinterpret_cast<const __half*>(sel_ptr(st.resid_sel, st.resid, p));
+    e.out = reinterpret_cast<__half*>(const_cast<void*>(sel_ptr(st.out_sel, st.out, p)));
+    e.partial = st.partial;
+    const bool prof = p.prof != nullptr;
+    uint8_t* sbuf = stage_s + (warp - 2) * kStageWarp;
+    long long t_wait = 0, t_busy = 0;
     for (int item = blockIdx.x; item < g.items; item += gridDim.x) {
       const int ks = item % g.splitk;
       const int nt = (item / g.splitk) % g.tiles_n;
       const int mt = item / (g.splitk * g.tiles_n);
-      const uint32_t acc = rs.acc;
-      bool ok = mbar_wait(tfull0 + 8 * acc, (rs.acc_bits >> acc) & 1u, ctl, 400 + (int)acc);
-      ok = __all_sync(0xffffffffu, ok);
+      const uint32_t acc0 = g.nh == 2 ? 0u : rs.acc;
+      bool ok = true;
+      for (int h = 0; h < g.nh; ++h) {
+        const uint32_t acc = acc0 + (uint32_t)h;
+        const long long tw = prof ? clock64() : 0;
+        ok = mbar_wait(tfull0 + 8 * acc, (rs.acc_bits >> acc) & 1u, ctl, 400 + (int)acc);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const long long tb = prof ? clock64() : 0;
+        t_wait += tb - tw;
+        tc_fence_after_sync();
+        const int row0 = mt * g.bm + h * 128 + q * 32;
+        const int row = row0 + lane;
+        int trow[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) trow[i] = (p.dbg_flags & 1) ? 0x7fffffff : row0 + 8 * i + (lane >> 2);
+        const uint32_t t0 = tmem + acc * kAccStride;
+        const int colbase = nt * g.bn;
+        // this warp takes chunks cpar, cpar+2, ...; the load of the next chunk is in flight while
+        // the current one is converted and stored
+        uint32_t ra[32], rb[32];
+        int c = (p.dbg_flags & 2) ? full_chunks : cpar;
+        if (c < full_chunks) tmem_ld32(t0 + c * 32, ra);
+        while (c < full_chunks) {
+          tmem_ld_wait(ra);
+          if (c + 2 < full_chunks) tmem_ld32(t0 + (c + 2) * 32, rb);
+          epilogue_chunk32(e, sbuf, ra, row, trow, colbase + c * 32, ks, lane);
+          c += 2;
+          if (c >= full_chunks) break;
+          tmem_ld_wait(rb);
+          if (c + 2 < full_chunks) tmem_ld32(t0 + (c + 2) * 32, ra);
+          epilogue_chunk32(e, sbuf, rb, row, trow, colbase + c * 32, ks, lane);
+          c += 2;
+        }
+        if ((g.bn & 16) && (full_chunks & 1) == cpar) {
+          uint32_t r[16];
+          tmem_ld16(t0 + full_chunks * 32, r);
+          tmem_ld_wait(r);
+          epilogue_chunk16(e, r, row, colbase + full_chunks * 32, ks);
+        }
+        tc_fence_before_sync();
+        mbar_arrive(tempty0 + 8 * acc);
+        rs.acc_bits ^= 1u << acc;
+        if (prof) t_busy += clock64() - tb;
+      }
       if (!ok) break;
-      tc_fence_after_sync();
-      const int row = mt * 128 + q * 32 + lane;
-      const bool valid = row < st.M;
-      const uint32_t t0 = tmem + acc * kAccStride;
-      int c0 = 0;
-      for (; c0 + 32 <= g.bn; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(t0 + c0, r);
-        tmem_ld_wait();
-        epilogue_chunk<32>(st, p, r, row, nt * g.bn + c0, ks, valid);
-      }
-      if (c0 < g.bn) {
-        uint32_t r[16];
-        tmem_ld16(t0 + c0, r);
-        tmem_ld_wait();
-        epilogue_chunk<16>(st, p, r, row, nt * g.bn + c0, ks, valid);
-      }
-      tc_fence_before_sync();
-      mbar_arrive(tempty0 + 8 * acc);
-      rs.acc_bits ^= 1u << acc;
-      rs.acc ^= 1u;
+      if (g.nh == 1) rs.acc ^= 1u;
+    }
+    if (p.prof && warp == 2 && lane == 0) {
+      long long* pr = p.prof + ((size_t)st.prof_index * gridDim.x + blockIdx.x) * 8;
+      pr[6] = t_wait;
+      pr[7] = t_busy;
     }
   }
 }
@@ -385,7 +570,7 @@ __device__ void attn_stage(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, 
       }
     }
     __syncwarp();
-  } else {
+  } else if (warp < 6) {
     const int q = warp & 3;
     const int r_in = q * 32 + lane;
     const uint32_t tmem = ctl_s.tmem_base + ((uint32_t)(q * 32) << 16);
@@ -663,6 +848,8 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
   const uint32_t pad = ((raw + 1023u) & ~1023u) - raw;      // 1024-byte alignment for swizzled tiles
   SmemCtl& cs = *reinterpret_cast<SmemCtl*>(smem_raw + pad);
   uint8_t* ring_ptr = smem_raw + pad + kCtlBytes;
+  __half* vec_s = reinterpret_cast<__half*>(ring_ptr + kRingBytes);
+  uint8_t* stage_s = ring_ptr + kRingBytes + kVecBytes;
   const uint32_t ring = raw + pad + kCtlBytes;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -673,7 +860,7 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&cs.tmem_full[i]), 1);
-      mbar_init(smem_u32(&cs.tmem_empty[i]), 128);
+      mbar_init(smem_u32(&cs.tmem_empty[i]), kThreads - 64);
     }
     mbar_init(smem_u32(&cs.qk_full), 1);
     mbar_init(smem_u32(&cs.qk_empty), 1);
@@ -711,11 +898,12 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
       uint32_t* dst = reinterpret_cast<uint32_t*>(&cs.stage);
       for (int i = threadIdx.x; i < (int)(sizeof(Stage) / 4); i += kThreads) dst[i] = src[i];
     }
+    if (threadIdx.x == 0) cs.stage.prof_index = si;
     __syncthreads();
-    if (p.prof && threadIdx.x == 0) p.prof[((size_t)si * gridDim.x + blockIdx.x) * 4 + 0] = clock64();
+    if (p.prof && threadIdx.x == 0) p.prof[((size_t)si * gridDim.x + blockIdx.x) * 8 + 0] = clock64();
     const Stage& st = cs.stage;
     if (st.type == STAGE_GEMM) {
-      gemm_stage(st, ca, cs, ring, rs, ctl, warp, lane);
+      gemm_stage(st, ca, cs, ring, vec_s, stage_s, rs, ctl, warp, lane);
     } else if (st.type == STAGE_ATTN) {
       attn_stage(st, ca, cs, ring, ring_ptr, rs, ctl, warp, lane);
     } else {
@@ -725,9 +913,9 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
       if (!grid_barrier(p, ctl, si)) break;
     } else {
       __syncthreads();
-      if (p.prof && threadIdx.x == 0) p.prof[((size_t)si * gridDim.x + blockIdx.x) * 4 + 1] = clock64();
+      if (p.prof && threadIdx.x == 0) p.prof[((size_t)si * gridDim.x + blockIdx.x) * 8 + 1] = clock64();
     }
-    if (p.prof && threadIdx.x == 0) p.prof[((size_t)si * gridDim.x + blockIdx.x) * 4 + 2] = clock64();
+    if (p.prof && threadIdx.x == 0) p.prof[((size_t)si * gridDim.x + blockIdx.x) * 8 + 2] = clock64();
     if (cs.abort) break;
   }
 

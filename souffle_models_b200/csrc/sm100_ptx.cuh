@@ -159,12 +159,64 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// High word of a SW128 descriptor (stride byte offset 1024, version 1, layout SWIZZLE_128B) and the
+// low word for a tile at `smem_addr` with leading byte offset `lbo_bytes`.
+constexpr uint32_t kDescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
+  return ((smem_addr >> 4) & 0x3FFFu) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+// One K chunk of 64 (four K=16 steps) in a single instruction sequence.  The issuing thread is a
+// lone lane whose every dependent instruction costs several cycles, so the descriptor arithmetic is
+// kept to one 32-bit add per operand and step.  `acc0` = 0 makes the first step overwrite D.
+__device__ __forceinline__ void umma_f16_k64(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t bstep,
+                                             uint32_t idesc, uint32_t acc0) {
+  asm volatile(
+      "{\n\t.reg .pred p, pt;\n\t.reg .b64 da, db;\n\t.reg .b32 al, bl;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
+      "mov.b64 da, {%1, %6};\n\tmov.b64 db, {%2, %6};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t"
+      "add.u32 al, %1, 2;\n\tadd.u32 bl, %2, %3;\n\tmov.b64 da, {al, %6};\n\tmov.b64 db, {bl, %6};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, pt;\n\t"
+      "add.u32 al, al, 2;\n\tadd.u32 bl, bl, %3;\n\tmov.b64 da, {al, %6};\n\tmov.b64 db, {bl, %6};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, pt;\n\t"
+      "add.u32 al, al, 2;\n\tadd.u32 bl, bl, %3;\n\tmov.b64 da, {al, %6};\n\tmov.b64 db, {bl, %6};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, pt;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(bstep), "r"(idesc), "r"(acc0), "r"(kDescHiSw128)
+      : "memory");
+}
+// Same for a 256-row tile: two accumulators (d0, d1) and two A tiles 16 KB apart share every B step.
+__device__ __forceinline__ void umma_f16_k64_x2(uint32_t d0, uint32_t d1, uint32_t a_lo, uint32_t b_lo, uint32_t bstep,
+                                                uint32_t idesc, uint32_t acc0) {
+  asm volatile(
+      "{\n\t.reg .pred p, pt;\n\t.reg .b64 da, da2, db;\n\t.reg .b32 al, al2, bl;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
+      "add.u32 al2, %2, 1024;\n\t"
+      "mov.b64 da, {%2, %7};\n\tmov.b64 da2, {al2, %7};\n\tmov.b64 db, {%3, %7};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], da2, db, %5, p;\n\t"
+      "add.u32 al, %2, 2;\n\tadd.u32 al2, al2, 2;\n\tadd.u32 bl, %3, %4;\n\t"
+      "mov.b64 da, {al, %7};\n\tmov.b64 da2, {al2, %7};\n\tmov.b64 db, {bl, %7};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], da2, db, %5, pt;\n\t"
+      "add.u32 al, al, 2;\n\tadd.u32 al2, al2, 2;\n\tadd.u32 bl, bl, %4;\n\t"
+      "mov.b64 da, {al, %7};\n\tmov.b64 da2, {al2, %7};\n\tmov.b64 db, {bl, %7};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], da2, db, %5, pt;\n\t"
+      "add.u32 al, al, 2;\n\tadd.u32 al2, al2, 2;\n\tadd.u32 bl, bl, %4;\n\t"
+      "mov.b64 da, {al, %7};\n\tmov.b64 da2, {al2, %7};\n\tmov.b64 db, {bl, %7};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], da2, db, %5, pt;\n\t}"
+      ::"r"(d0), "r"(d1), "r"(a_lo), "r"(b_lo), "r"(bstep), "r"(idesc), "r"(acc0), "r"(kDescHiSw128)
+      : "memory");
+}
 // Arrives on the mbarrier once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
 // 32 lanes x 32 columns of fp32: thread i of the warp receives lane (base+i), columns [col, col+32).
+// The loads carry no memory clobber (they only write registers); the matching wait names the same
+// registers as read-write operands so the compiler cannot move their uses above it.
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -174,8 +226,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
         "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
         "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
+      : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
@@ -183,10 +234,21 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
         "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
+      : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                 "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                 "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31]));
+}
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]));
+}
 
 // ------------------------------------------------------------------------------------
 // global-memory release/acquire for the grid barrier and dataflow flags

@@ -100,33 +100,47 @@ __global__ void transpose_kn_to_nk(const __half* __restrict__ src, __half* __res
 }
 
 // ------------------------------------------------------------------------------------
-// tiling choice.  Cost unit: one 128-byte row moved L2 -> shared memory by one CTA.
+// tiling choice: a small cycle model of one CTA, fitted to the in-kernel stage profile on a B200.
+// A K chunk costs the larger of its tensor-core time (bm*bn/64 cycles) and its shared-memory traffic
+// (operands written once by TMA and read by the tensor core, B once per 128-row half, at 128 B/clk).
+// The epilogue of a 128-row tile overlaps the next tile's main loop but competes with it; with
+// 256-row tiles it is exposed.  Tiles run in waves over the SMs; split-K pays for its fp32 planes
+// (written by the GEMM, re-read by the LayerNorm stage).
 // ------------------------------------------------------------------------------------
-static void choose_tiles(int M, int N, int K, int sms, bool allow_split, bool b_mn, int* bn_out, int* split_out) {
-  const int tiles_m = (M + 127) / 128;
+struct TileChoice {
+  int bm = 128, bn = 0, split = 1;
+};
+static TileChoice choose_tiles(int M, int N, int K, int sms, bool allow_split, bool b_mn, bool head_split = false) {
   const int kch = K / 64;
   double best = 1e300;
-  int best_bn = 0, best_split = 1;
-  const int cands[5] = {256, 128, 64, 32, 16};
-  for (int ci = 0; ci < 5; ++ci) {
-    const int bn = cands[ci];
-    if (N % bn) continue;
-    if (b_mn && bn % 64) continue;
-    for (int split = 1; split <= (allow_split ? 16 : 1); ++split) {
-      if (kch % split) continue;
-      const long items = (long)tiles_m * (N / bn) * split;
-      const long waves = (items + sms - 1) / sms;
-      double cost = (double)waves * (kch / split) * (128.0 + 1.5 * bn) + (double)waves * 40.0;
-      if (allow_split) cost += 3.0 * (double)split * M * N * 8.0 / sms / 128.0;   // fp32 planes written, then re-read
-      if (cost < best - 1e-9) {
-        best = cost;
-        best_bn = bn;
-        best_split = split;
+  TileChoice bt;
+  const int cands[8] = {256, 192, 128, 96, 64, 48, 32, 16};
+  for (int bm = 128; bm <= 256; bm += 128) {
+    if (bm == 256 && M <= 128) continue;
+    for (int ci = 0; ci < 8; ++ci) {
+      const int bn = cands[ci];
+      if (N % bn) continue;
+      if (b_mn && bn % 64) continue;
+      if (head_split && bn != 16 && bn % 32) continue;   // 32-column epilogue chunks must not straddle a head
+      if (196608 / ((bm + bn) * 128) < 2) continue;
+      for (int split = 1; split <= (allow_split ? 16 : 1); ++split) {
+        if (kch % split) continue;
+        const long items = (long)((M + bm - 1) / bm) * (N / bn) * split;
+        const long waves = (items + sms - 1) / sms;
+        const double smem = 2.0 * bm + (bm / 128 + 1.0) * bn, mma = bm * bn / 64.0;
+        const double chunk = 1.1 * (smem > mma ? smem : mma);
+        const double epilogue = bm * bn * (allow_split ? 0.2 : 0.35);      // fp32 planes need no math
+        const double tile = (kch / split) * chunk + (bm == 256 ? 0.7 : 0.45) * epilogue + 1500.0;
+        double cost = waves * tile;
+        if (allow_split) cost += (double)split * M * N * 8.0 / sms / 12.0;
+        if (cost < best - 1e-9) {
+          best = cost;
+          bt.bm = bm; bt.bn = bn; bt.split = split;
+        }
       }
     }
   }
-  *bn_out = best_bn;
-  *split_out = best_split;
+  return bt;
 }
 
 // ------------------------------------------------------------------------------------
@@ -167,9 +181,9 @@ static int launch_mega(const CallArgs& args, int grid, cudaStream_t stream) {
 }
 
 static int stage_items(const Stage& s) {
-  if (s.type == STAGE_GEMM) return ((s.M + 127) / 128) * (s.N / s.bn) * s.splitk;
+  if (s.type == STAGE_GEMM) return ((s.M + s.bm - 1) / s.bm) * (s.N / s.bn) * s.splitk;
   if (s.type == STAGE_ATTN) return s.batch * s.heads * ((s.seq + 127) / 128);
-  return (s.M + 5) / 6;
+  return (s.M + kThreads / 32 - 1) / (kThreads / 32);
 }
 
 static int decode_status(const int* h, const char* what) {
@@ -205,6 +219,7 @@ struct SouffleBertPlan {
   // per-call map cache for x
   const void* last_x = nullptr;
   CUtensorMap x_map;
+  int x_box_rows = 128;
 };
 
 namespace souffle {
@@ -230,6 +245,7 @@ static Stage blank_stage(int type) {
   memset(&s, 0, sizeof(s));
   s.type = type;
   s.splitk = 1;
+  s.bm = 128;
   s.n_partial = 0;
   return s;
 }
@@ -265,36 +281,42 @@ static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* la
   SF_CUDA(cudaMemset(p->d_status, 0, 64));
 
   // ---- tiling ----
-  int bn_qkv = d.bn_qkv, bn_fc1 = d.bn_fc1, bn_proj = d.bn_proj, sp_proj = d.split_proj, bn_fc2 = d.bn_fc2,
-      sp_fc2 = d.split_fc2, one = 1;
-  if (!bn_qkv) choose_tiles(M, 3 * H, H, sms, false, false, &bn_qkv, &one);
-  if (!bn_fc1) choose_tiles(M, F, H, sms, false, false, &bn_fc1, &one);
-  if (!bn_proj || !sp_proj) {
-    int a, b;
-    choose_tiles(M, H, H, sms, true, false, &a, &b);
-    if (!bn_proj) bn_proj = a;
-    if (!sp_proj) sp_proj = b;
-  }
-  if (!bn_fc2 || !sp_fc2) {
-    int a, b;
-    choose_tiles(M, H, F, sms, true, false, &a, &b);
-    if (!bn_fc2) bn_fc2 = a;
-    if (!sp_fc2) sp_fc2 = b;
-  }
-  auto bad_bn = [](int bn, int N) { return bn < 16 || bn > 256 || bn % 16 || N % bn; };
-  if (bad_bn(bn_qkv, 3 * H) || bad_bn(bn_fc1, F) || bad_bn(bn_proj, H) || bad_bn(bn_fc2, H))
-    return fail(SOUFFLE_BAD_SHAPE, "tile widths (%d,%d,%d,%d) do not divide the layer's widths", bn_qkv, bn_fc1, bn_proj, bn_fc2);
-  if ((H / 64) % sp_proj || (F / 64) % sp_fc2) return fail(SOUFFLE_BAD_SHAPE, "split-K factors must divide K/64");
+  TileChoice t_qkv = choose_tiles(M, 3 * H, H, sms, false, false, true), t_fc1 = choose_tiles(M, F, H, sms, false, false),
+             t_proj = choose_tiles(M, H, H, sms, true, false), t_fc2 = choose_tiles(M, H, F, sms, true, false);
+  if (d.bm_qkv) t_qkv.bm = d.bm_qkv;
+  if (d.bn_qkv) t_qkv.bn = d.bn_qkv;
+  if (d.bm_fc1) t_fc1.bm = d.bm_fc1;
+  if (d.bn_fc1) t_fc1.bn = d.bn_fc1;
+  if (d.bm_proj) t_proj.bm = d.bm_proj;
+  if (d.bn_proj) t_proj.bn = d.bn_proj;
+  if (d.split_proj) t_proj.split = d.split_proj;
+  if (d.bm_fc2) t_fc2.bm = d.bm_fc2;
+  if (d.bn_fc2) t_fc2.bn = d.bn_fc2;
+  if (d.split_fc2) t_fc2.split = d.split_fc2;
+  auto bad_tile = [](const TileChoice& t, int N) {
+    return (t.bm != 128 && t.bm != 256) || t.bn < 16 || t.bn > 256 || t.bn % 16 || N % t.bn ||
+           196608 / ((t.bm + t.bn) * 128) < 2;
+  };
+  if (t_qkv.bn != 16 && t_qkv.bn % 32) return fail(SOUFFLE_BAD_SHAPE, "bn_qkv must be 16 or a multiple of 32");
+  if (bad_tile(t_qkv, 3 * H) || bad_tile(t_fc1, F) || bad_tile(t_proj, H) || bad_tile(t_fc2, H))
+    return fail(SOUFFLE_BAD_SHAPE, "tile shapes (%dx%d, %dx%d, %dx%d, %dx%d) do not fit the layer", t_qkv.bm, t_qkv.bn,
+                t_fc1.bm, t_fc1.bn, t_proj.bm, t_proj.bn, t_fc2.bm, t_fc2.bn);
+  if (t_proj.split < 1 || t_fc2.split < 1 || t_proj.split > 16 || t_fc2.split > 16 || (H / 64) % t_proj.split ||
+      (F / 64) % t_fc2.split)
+    return fail(SOUFFLE_BAD_SHAPE, "split-K factors must be in 1..16 and divide K/64");
+  const int bn_qkv = t_qkv.bn, bn_fc1 = t_fc1.bn, bn_proj = t_proj.bn, sp_proj = t_proj.split, bn_fc2 = t_fc2.bn,
+            sp_fc2 = t_fc2.split;
   const int max_split = sp_proj > sp_fc2 ? sp_proj : sp_fc2;
   if ((rc = plan_alloc(p, (void**)&p->partial, (size_t)max_split * M * H * 4))) return rc;
+  p->x_box_rows = t_qkv.bm;
 
   // ---- activation maps (A operands, box 64 x 128) ----
   int m_ctx, m_ln1, m_fc1, m_act[2] = {-1, -1}, m_qkv;
-  if ((rc = add_map(p, p->ctx, M, H, 128, &m_ctx))) return rc;
-  if ((rc = add_map(p, p->ln1, M, H, 128, &m_ln1))) return rc;
-  if ((rc = add_map(p, p->fc1, M, F, 128, &m_fc1))) return rc;
+  if ((rc = add_map(p, p->ctx, M, H, t_proj.bm, &m_ctx))) return rc;
+  if ((rc = add_map(p, p->ln1, M, H, t_fc1.bm, &m_ln1))) return rc;
+  if ((rc = add_map(p, p->fc1, M, F, t_fc2.bm, &m_fc1))) return rc;
   for (int i = 0; i < 2; ++i)
-    if (p->act[i] && (rc = add_map(p, p->act[i], M, H, 128, &m_act[i]))) return rc;
+    if (p->act[i] && (rc = add_map(p, p->act[i], M, H, t_qkv.bm, &m_act[i]))) return rc;
   if ((rc = add_map(p, p->qkv, (uint64_t)3 * B * Hh * S, hd, 128, &m_qkv))) return rc;
 
   // ---- per layer: repack weights, maps, stages ----
@@ -354,7 +376,7 @@ static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* la
     const int out_sel = last ? PTR_CALL_Y : PTR_PLAN;
 
     Stage s = blank_stage(STAGE_GEMM);                 // QKV projection, head-split store
-    s.tm_a = in_map; s.tm_b = m_wqkv; s.M = M; s.N = 3 * H; s.K = H; s.bn = bn_qkv;
+    s.tm_a = in_map; s.tm_b = m_wqkv; s.M = M; s.N = 3 * H; s.K = H; s.bm = t_qkv.bm; s.bn = bn_qkv;
     s.epi = EPI_QKV; s.bias = qkv_b; s.out = p->qkv; s.batch = B; s.heads = Hh; s.seq = S; s.head_dim = hd;
     p->stages.push_back(s);
 
@@ -364,7 +386,7 @@ static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* la
     p->stages.push_back(s);
 
     s = blank_stage(STAGE_GEMM);                       // output projection -> fp32 partials
-    s.tm_a = m_ctx; s.tm_b = m_wo; s.M = M; s.N = H; s.K = H; s.bn = bn_proj; s.splitk = sp_proj;
+    s.tm_a = m_ctx; s.tm_b = m_wo; s.M = M; s.N = H; s.K = H; s.bm = t_proj.bm; s.bn = bn_proj; s.splitk = sp_proj;
     s.epi = EPI_PARTIAL; s.partial = p->partial;
     p->stages.push_back(s);
 
@@ -374,12 +396,12 @@ static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* la
     p->stages.push_back(s);
 
     s = blank_stage(STAGE_GEMM);                       // FC1 + bias + activation
-    s.tm_a = m_ln1; s.tm_b = m_w1; s.M = M; s.N = F; s.K = H; s.bn = bn_fc1;
+    s.tm_a = m_ln1; s.tm_b = m_w1; s.M = M; s.N = F; s.K = H; s.bm = t_fc1.bm; s.bn = bn_fc1;
     s.epi = EPI_F16; s.act = std_variant ? ACT_GELU : ACT_RELU; s.bias = fc1_b; s.out = p->fc1; s.ldo = F;
     p->stages.push_back(s);
 
     s = blank_stage(STAGE_GEMM);                       // FC2 -> fp32 partials
-    s.tm_a = m_fc1; s.tm_b = m_w2; s.M = M; s.N = H; s.K = F; s.bn = bn_fc2; s.splitk = sp_fc2;
+    s.tm_a = m_fc1; s.tm_b = m_w2; s.M = M; s.N = H; s.K = F; s.bm = t_fc2.bm; s.bn = bn_fc2; s.splitk = sp_fc2;
     s.epi = EPI_PARTIAL; s.partial = p->partial;
     p->stages.push_back(s);
 
@@ -399,7 +421,7 @@ static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* la
   p->grid = max_items < sms ? max_items : sms;
 
   if (d.profile) {
-    const size_t pb = p->stages.size() * (size_t)p->grid * 4 * sizeof(long long);
+    const size_t pb = p->stages.size() * (size_t)p->grid * 8 * sizeof(long long);
     if ((rc = plan_alloc(p, (void**)&p->d_prof, pb))) return rc;
     SF_CUDA(cudaMemset(p->d_prof, 0, pb));
   }
@@ -464,7 +486,7 @@ int souffle_bert_forward(SouffleBertPlan* plan, const void* x, const int32_t* se
   const SouffleBertDesc& d = plan->desc;
   const int M = d.batch * d.seq, H = d.heads * d.head_dim;
   if (x != plan->last_x) {
-    int rc = make_map(&plan->x_map, x, M, H, 128);
+    int rc = make_map(&plan->x_map, x, M, H, (uint32_t)plan->x_box_rows);
     if (rc) return rc;
     plan->last_x = x;
   }
@@ -486,6 +508,8 @@ int souffle_bert_forward(SouffleBertPlan* plan, const void* x, const int32_t* se
   mp.timeout_ns = (unsigned long long)(d.timeout_ms > 0 ? d.timeout_ms : 2000) * 1000000ull;
   mp.prof = plan->d_prof;
   mp.skip_arrival = d.debug_skip_arrival;
+  mp.max_slots = d.debug_max_slots & 0xFF;
+  mp.dbg_flags = d.debug_max_slots >> 8;
   int rc = launch_mega(args, plan->grid, reinterpret_cast<cudaStream_t>(stream));
   if (rc) return rc;
   plan->launch_id++;
@@ -561,7 +585,7 @@ int souffle_bert_plan_status(SouffleBertPlan* plan) {
 int souffle_bert_plan_read_profile(SouffleBertPlan* plan, int64_t* out, size_t capacity_elems) {
   if (!plan || !out) return fail(SOUFFLE_BAD_ARGUMENT, "null argument");
   if (!plan->d_prof) return fail(SOUFFLE_BAD_ARGUMENT, "the plan was created without desc.profile");
-  const size_t n = plan->stages.size() * (size_t)plan->grid * 4;
+  const size_t n = plan->stages.size() * (size_t)plan->grid * 8;
   if (capacity_elems < n) return fail(SOUFFLE_BAD_ARGUMENT, "profile needs %zu elements, got %zu", n, capacity_elems);
   SF_CUDA(cudaDeviceSynchronize());
   SF_CUDA(cudaMemcpy(out, plan->d_prof, n * sizeof(long long), cudaMemcpyDeviceToHost));
@@ -594,10 +618,9 @@ static int ws_prepare(void* workspace, size_t ws_bytes, cudaStream_t st, MegaPar
 
 static int fill_gemm_stage(Stage* s, int tm_a, int tm_b, const void* out, int M, int N, int K, int sms) {
   *s = blank_stage(STAGE_GEMM);
-  int bn = 0, split = 1;
-  choose_tiles(M, N, K, sms, false, true, &bn, &split);
-  if (!bn) return fail(SOUFFLE_BAD_SHAPE, "N=%d must be a multiple of 64", N);
-  s->tm_a = tm_a; s->tm_b = tm_b; s->M = M; s->N = N; s->K = K; s->bn = bn; s->b_mn_major = 1;
+  const TileChoice t = choose_tiles(M, N, K, sms, false, true);
+  if (!t.bn) return fail(SOUFFLE_BAD_SHAPE, "N=%d must be a multiple of 64", N);
+  s->tm_a = tm_a; s->tm_b = tm_b; s->M = M; s->N = N; s->K = K; s->bm = t.bm; s->bn = t.bn; s->b_mn_major = 1;
   s->epi = EPI_F16; s->out = const_cast<void*>(out); s->ldo = N;
   return SOUFFLE_OK;
 }
@@ -614,10 +637,10 @@ int souffle_gemm_f16(const void* a, const void* w_kn, void* c, int32_t M, int32_
   CallArgs args;
   memset(&args, 0, sizeof(args));
   if ((rc = ws_prepare(workspace, workspace_bytes, st, &args.p))) return rc;
-  if ((rc = make_map(&args.call_maps[0], a, M, K, 128))) return rc;
-  if ((rc = make_map(&args.call_maps[1], w_kn, K, N, 64))) return rc;     // [K][N]: box 64 (N) x 64 (K rows)
   const int sms = di->sms < di->max_ctas ? di->sms : di->max_ctas;
   if ((rc = fill_gemm_stage(&args.inline_stages[0], -1, -2, c, M, N, K, sms))) return rc;
+  if ((rc = make_map(&args.call_maps[0], a, M, K, (uint32_t)args.inline_stages[0].bm))) return rc;
+  if ((rc = make_map(&args.call_maps[1], w_kn, K, N, 64))) return rc;     // [K][N]: box 64 (N) x 64 (K rows)
   args.p.n_stages = 1;
   const int items = stage_items(args.inline_stages[0]);
   return launch_mega(args, items < sms ? items : sms, st);
@@ -636,13 +659,13 @@ int souffle_swin_mlp_forward(const void* src, const void* fc1_w, const void* fc2
   CallArgs args;
   memset(&args, 0, sizeof(args));
   if ((rc = ws_prepare(workspace, workspace_bytes, st, &args.p))) return rc;
-  if ((rc = make_map(&args.call_maps[0], src, M, C, 128))) return rc;
-  if ((rc = make_map(&args.call_maps[1], fc1_w, C, F, 64))) return rc;
-  if ((rc = make_map(&args.call_maps[2], hidden, M, F, 128))) return rc;
-  if ((rc = make_map(&args.call_maps[3], fc2_w, F, C, 64))) return rc;
   const int sms = di->sms < di->max_ctas ? di->sms : di->max_ctas;
   if ((rc = fill_gemm_stage(&args.inline_stages[0], -1, -2, hidden, M, F, C, sms))) return rc;
   if ((rc = fill_gemm_stage(&args.inline_stages[1], -3, -4, out, M, C, F, sms))) return rc;
+  if ((rc = make_map(&args.call_maps[0], src, M, C, (uint32_t)args.inline_stages[0].bm))) return rc;
+  if ((rc = make_map(&args.call_maps[1], fc1_w, C, F, 64))) return rc;
+  if ((rc = make_map(&args.call_maps[2], hidden, M, F, (uint32_t)args.inline_stages[1].bm))) return rc;
+  if ((rc = make_map(&args.call_maps[3], fc2_w, F, C, 64))) return rc;
   args.p.n_stages = 2;
   int items = stage_items(args.inline_stages[0]);
   const int i2 = stage_items(args.inline_stages[1]);

@@ -30,9 +30,10 @@ enum PtrSel : int { PTR_PLAN = 0, PTR_CALL_X = 1, PTR_CALL_Y = 2 };
 struct Stage {
   int type;
   // ---- GEMM ----
-  int tm_a;          // tensor-map index of the A operand ([M][K], box 64 x 128); -1 = per-call x map
+  int tm_a;          // tensor-map index of the A operand ([M][K], box 64 x bm); negative = per-call map
   int tm_b;          // tensor-map index of the B operand
   int M, N, K;
+  int bm;            // tile height: 128, or 256 (two 128-row halves that share each B tile)
   int bn;            // tile width in N (multiple of 16, <= 256, divides N)
   int splitk;        // K is cut into this many independent partial products
   int b_mn_major;    // 0: B stored [N][K] (K contiguous); 1: B stored [K][N] (N contiguous, bn % 64 == 0)
@@ -57,7 +58,7 @@ struct Stage {
   const void* beta;  // fp16 [N] or null
   float eps;
   int n_partial;     // number of fp32 partial planes to sum
-  int pad_;
+  int prof_index;    // filled in by the kernel: position of this stage in the program
 };
 
 constexpr int kMaxTensorMaps = 80;
