@@ -58,5 +58,32 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB_PATH
 
 
+def resource_usage() -> dict:
+    """Compiles without linking and returns {kernel: (registers, spill_store_bytes, spill_load_bytes)} from
+    `ptxas -v`.  The persistent kernels must not spill: a spilling epilogue cost 10-25% end to end."""
+    import re
+    import tempfile
+    with tempfile.TemporaryDirectory() as tmp:
+        cmd = [_nvcc(), "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-Xptxas", "-v", "-c",
+               "-o", os.path.join(tmp, "x.o"), os.path.join(CSRC, "souffle_b200.cu")]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
+    out, name = {}, None
+    spills = (0, 0)
+    for line in res.stderr.splitlines():
+        m = re.search(r"Compiling entry function '(\w+)'", line)
+        if m:
+            name = m.group(1)
+        m = re.search(r"(\d+) bytes spill stores, (\d+) bytes spill loads", line)
+        if m:
+            spills = (int(m.group(1)), int(m.group(2)))
+        m = re.search(r"Used (\d+) registers", line)
+        if m and name:
+            out[name] = (int(m.group(1)),) + spills
+            name = None
+    return out
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

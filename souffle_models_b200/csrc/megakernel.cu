@@ -81,7 +81,8 @@ struct __align__(8) SmemCtl {
   uint64_t empty[kMaxSlots];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
-  uint64_t qk_full, qk_empty, v_full, v_empty, s_full, p_full, o_full;
+  uint64_t qk_full, qk_empty, v_full, v_empty, s_full, p_full, o_full;   // attention, pipeline 0
+  uint64_t attn1[7];                                                     // attention, pipeline 1 (same order)
   uint64_t ln_full[4];
   uint32_t tmem_base;
   int abort;
@@ -95,7 +96,8 @@ struct RoleState {
   uint32_t slot_bits = 0;  // phase bit per ring slot
   uint32_t acc = 0;        // next accumulator buffer
   uint32_t acc_bits = 0;   // phase bit per accumulator buffer
-  uint32_t attn_bit = 0;   // phase bit of the attention barriers
+  uint32_t attn_bit = 0;   // phase bit of the attention barriers, pipeline 0
+  uint32_t attn_bit1 = 0;  // phase bit of the attention barriers, pipeline 1
   uint32_t ln_bits = 0;    // phase bit per LayerNorm batch buffer
 };
 
@@ -107,10 +109,12 @@ __device__ __forceinline__ const void* sel_ptr(int sel, const void* plan, const 
 // grid barrier: one monotonic arrival counter per launch, bounded spin
 // ------------------------------------------------------------------------------------
 __device__ bool grid_barrier(const MegaParams& p, const WaitCtl& ctl, int where) {
-  __threadfence();
+  // Every thread orders its generic-proxy writes before async-proxy reads; the CTA barrier then orders all
+  // of them before thread 0, whose gpu-scope release (cumulative) publishes them to the other CTAs.
   fence_proxy_async();
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence();
     if (p.prof) p.prof[((size_t)where * gridDim.x + blockIdx.x) * 8 + 1] = clock64();
     // The counter only grows during a launch: barrier number `where` is passed once every CTA
     // has added 1 for it.  (The launch that runs next clears the other counter, see the prologue.)
@@ -329,12 +333,13 @@ __device__ void gemm_stage(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, 
   const uint32_t tfull0 = smem_u32(&ctl_s.tmem_full[0]), tempty0 = smem_u32(&ctl_s.tmem_empty[0]);
   const uint32_t a_bytes = (uint32_t)(g.nh * kATileBytes);
   // the stage's bias vector -> shared memory (one global read per CTA instead of one per tile chunk)
+  // (done by the epilogue warps alone; the producer and MMA warps start the main loop meanwhile)
   const __half* bias_s = nullptr;
-  if (st.bias && st.epi != EPI_PARTIAL && st.N * 2 <= kVecBytes) {
+  if (warp >= 2 && st.bias && st.epi != EPI_PARTIAL && st.N * 2 <= kVecBytes) {
     const uint4* src = reinterpret_cast<const uint4*>(st.bias);
-    for (int i = threadIdx.x; i < st.N / 8; i += kThreads) reinterpret_cast<uint4*>(vec_s)[i] = __ldg(src + i);
+    for (int i = threadIdx.x - 64; i < st.N / 8; i += kThreads - 64) reinterpret_cast<uint4*>(vec_s)[i] = __ldg(src + i);
     bias_s = vec_s;
-    __syncthreads();
+    named_barrier_sync(1, kThreads - 64);
   }
 
   if (warp == 0) {
@@ -456,8 +461,7 @@ __device__ void gemm_stage(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, 
       for (int h = 0; h < g.nh; ++h) {
         const uint32_t acc = acc0 + (uint32_t)h;
         const long long tw = prof ? clock64() : 0;
-        ok = mbar_wait(tfull0 + 8 * acc, (rs.acc_bits >> acc) & 1u, ctl, 400 + (int)acc);
-        ok = __all_sync(0xffffffffu, ok);
+        ok = mbar_wait_warp(tfull0 + 8 * acc, (rs.acc_bits >> acc) & 1u, ctl, 400 + (int)acc, lane);
         if (!ok) break;
         const long long tb = prof ? clock64() : 0;
         t_wait += tb - tw;
@@ -469,21 +473,12 @@ __device__ void gemm_stage(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, 
         for (int i = 0; i < 4; ++i) trow[i] = (p.dbg_flags & 1) ? 0x7fffffff : row0 + 8 * i + (lane >> 2);
         const uint32_t t0 = tmem + acc * kAccStride;
         const int colbase = nt * g.bn;
-        // this warp takes chunks cpar, cpar+2, ...; the load of the next chunk is in flight while
-        // the current one is converted and stored
-        uint32_t ra[32], rb[32];
-        int c = (p.dbg_flags & 2) ? full_chunks : cpar;
-        if (c < full_chunks) tmem_ld32(t0 + c * 32, ra);
-        while (c < full_chunks) {
-          tmem_ld_wait(ra);
-          if (c + 2 < full_chunks) tmem_ld32(t0 + (c + 2) * 32, rb);
-          epilogue_chunk32(e, sbuf, ra, row, trow, colbase + c * 32, ks, lane);
-          c += 2;
-          if (c >= full_chunks) break;
-          tmem_ld_wait(rb);
-          if (c + 2 < full_chunks) tmem_ld32(t0 + (c + 2) * 32, ra);
-          epilogue_chunk32(e, sbuf, rb, row, trow, colbase + c * 32, ks, lane);
-          c += 2;
+        // this warp takes chunks cpar, cpar+2, ... (its partner warp on the same lane quarter the others)
+        for (int c = (p.dbg_flags & 2) ? full_chunks : cpar; c < full_chunks; c += 2) {
+          uint32_t r[32];
+          tmem_ld32(t0 + c * 32, r);
+          tmem_ld_wait(r);
+          epilogue_chunk32(e, sbuf, r, row, trow, colbase + c * 32, ks, lane);
         }
         if ((g.bn & 16) && (full_chunks & 1) == cpar) {
           uint32_t r[16];
@@ -583,8 +578,7 @@ __device__ void attn_stage(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, 
     for (int item = blockIdx.x; item < items; item += gridDim.x) {
       const int qt = item % n_kb, h = (item / n_kb) % H, b = item / (n_kb * H);
       const int kv_len = lens ? lens[b] : S;
-      bool ok = mbar_wait(s_full, rs.attn_bit, ctl, 520);
-      ok = __all_sync(0xffffffffu, ok);
+      bool ok = mbar_wait_warp(s_full, rs.attn_bit, ctl, 520, lane);
       if (!ok) break;
       tc_fence_after_sync();
       const int n_chunks = n_kb * 4;
@@ -665,8 +659,7 @@ __device__ void attn_stage(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, 
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(p_full);
-      ok = mbar_wait(o_full, rs.attn_bit, ctl, 521);
-      ok = __all_sync(0xffffffffu, ok);
+      ok = mbar_wait_warp(o_full, rs.attn_bit, ctl, 521, lane);
       if (!ok) break;
       tc_fence_after_sync();
       {
@@ -693,6 +686,217 @@ __device__ void attn_stage(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, 
       tc_fence_before_sync();
       rs.attn_bit ^= 1u;
     }
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// attention stage for S <= 128: two independent pipelines ("ping" and "pong").  The CTA's work items
+// alternate between them; each pipeline has its own Q/K/V/P tiles in shared memory, its own score and
+// output accumulators in TMEM, its own barriers and its own group of four softmax warps (warps 2..5
+// and 6..9).  While one group runs the softmax of item i, the tensor core already holds the scores of
+// item i+1 for the other group, and the loads of item i+2 are in flight.
+// ------------------------------------------------------------------------------------
+enum AttnBar : int { AB_QK_FULL = 0, AB_QK_EMPTY, AB_V_FULL, AB_V_EMPTY, AB_S_FULL, AB_P_FULL, AB_O_FULL };
+constexpr int kPipeBytes = 5 * kATileBytes;      // Q 16 KiB, K 16, V 16, P 32
+constexpr int kPipeOCol = 256;                   // TMEM: scores at 0 / 128, outputs at 256 / 320
+
+__device__ void attn_stage_pp(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, uint32_t ring, uint8_t* ring_ptr,
+                              uint8_t* stage_s, RoleState& rs, const WaitCtl& ctl, int warp, int lane) {
+  const MegaParams& p = ca.p;
+  const int S = st.seq, B = st.batch, H = st.heads;
+  const int items = B * H;
+  const int my_items = items > (int)blockIdx.x ? (items - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  const uint32_t bar0 = smem_u32(&ctl_s.qk_full), bar1 = smem_u32(&ctl_s.attn1[0]);
+  auto bar = [&](int g, int which) -> uint32_t { return (g ? bar1 : bar0) + 8u * (uint32_t)which; };
+  const CUtensorMap* tm = map_ptr(ca, st.tm_qkv);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t bits = rs.attn_bit | (rs.attn_bit1 << 1);
+      for (int k = 0; k < my_items; ++k) {
+        const int item = blockIdx.x + k * gridDim.x, g = k & 1;
+        const int h = item % H, b = item / H;
+        const int rq = ((0 * B + b) * H + h) * S, rk = ((1 * B + b) * H + h) * S, rv = ((2 * B + b) * H + h) * S;
+        const uint32_t base = ring + g * kPipeBytes, bit = (bits >> g) & 1u;
+        if (!mbar_wait(bar(g, AB_QK_EMPTY), bit ^ 1u, ctl, 500 + g)) break;
+        mbar_expect_tx(bar(g, AB_QK_FULL), 2u * kATileBytes);
+        tma_load_2d(base, tm, bar(g, AB_QK_FULL), 0, rq);
+        tma_load_2d(base + kATileBytes, tm, bar(g, AB_QK_FULL), 0, rk);
+        if (!mbar_wait(bar(g, AB_V_EMPTY), bit ^ 1u, ctl, 502 + g)) break;
+        mbar_expect_tx(bar(g, AB_V_FULL), (uint32_t)kATileBytes);
+        tma_load_2d(base + 2 * kATileBytes, tm, bar(g, AB_V_FULL), 0, rv);
+        bits ^= 1u << g;
+      }
+      rs.attn_bit = bits & 1u;
+      rs.attn_bit1 = (bits >> 1) & 1u;
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = umma_idesc_f16(128u, 0u), idesc_o = umma_idesc_f16(64u, 1u);
+      const uint32_t tmem = ctl_s.tmem_base;
+      uint32_t bits = rs.attn_bit | (rs.attn_bit1 << 1);
+      bool ok = true;
+      auto issue_s = [&](int k) {                              // scores of item k: S = Q K^T
+        const int g = k & 1;
+        const uint32_t base = ring + g * kPipeBytes;
+        if (!mbar_wait(bar(g, AB_QK_FULL), (bits >> g) & 1u, ctl, 510 + g)) { ok = false; return; }
+        tc_fence_after_sync();
+        umma_f16_k64(tmem + g * 128, umma_desc_lo(base, 16), umma_desc_lo(base + kATileBytes, 16), 2u, idesc_s, 0u);
+        umma_commit(bar(g, AB_S_FULL));
+        umma_commit(bar(g, AB_QK_EMPTY));
+      };
+      if (my_items > 0) issue_s(0);
+      if (ok && my_items > 1) issue_s(1);
+      for (int k = 0; ok && k < my_items; ++k) {
+        const int g = k & 1;
+        const uint32_t base = ring + g * kPipeBytes, bit = (bits >> g) & 1u;
+        if (!mbar_wait(bar(g, AB_P_FULL), bit, ctl, 512 + g)) break;
+        if (!mbar_wait(bar(g, AB_V_FULL), bit, ctl, 514 + g)) break;
+        tc_fence_after_sync();
+        // O = P V: K = 128 keys = two chunks of 64; V is an MN-major B operand (16 keys = 2048 B per step)
+        const uint32_t d = tmem + kPipeOCol + g * 64;
+        umma_f16_k64(d, umma_desc_lo(base + 3 * kATileBytes, 16), umma_desc_lo(base + 2 * kATileBytes, 8192), 128u, idesc_o, 0u);
+        umma_f16_k64(d, umma_desc_lo(base + 4 * kATileBytes, 16), umma_desc_lo(base + 2 * kATileBytes + 8192, 8192), 128u,
+                     idesc_o, 1u);
+        umma_commit(bar(g, AB_O_FULL));
+        umma_commit(bar(g, AB_V_EMPTY));
+        bits ^= 1u << g;
+        if (k + 2 < my_items) issue_s(k + 2);
+      }
+      rs.attn_bit = bits & 1u;
+      rs.attn_bit1 = (bits >> 1) & 1u;
+    }
+    __syncwarp();
+  } else {
+    const int g = (warp - 2) >> 2, q = warp & 3;
+    const int r_in = q * 32 + lane;
+    const uint32_t tmem = ctl_s.tmem_base + ((uint32_t)(q * 32) << 16);
+    const float sl2 = st.scale * 1.4426950408889634f;
+    const float mask_l2 = -10000.0f * 1.4426950408889634f;
+    const int* lens = st.lens_from_call ? p.lens : st.lens;
+    __half* ctx = reinterpret_cast<__half*>(st.out);
+    __half* probs = reinterpret_cast<__half*>(st.probs);
+    const int hd = st.head_dim, hidden = H * hd;
+    uint8_t* sbuf = stage_s + (warp - 2) * kStageWarp;
+    uint8_t* pbase = ring_ptr + g * kPipeBytes + 3 * kATileBytes + r_in * 128;
+    uint32_t bit = g ? rs.attn_bit1 : rs.attn_bit;
+    const int n_chunks = (S + 31) >> 5;
+    for (int k = g; k < my_items; k += 2) {
+      const int item = blockIdx.x + k * gridDim.x;
+      const int h = item % H, b = item / H;
+      const int kv_len = lens ? lens[b] : S;
+      if (!mbar_wait_warp(bar(g, AB_S_FULL), bit, ctl, 520 + g, lane)) break;
+      tc_fence_after_sync();
+      const uint32_t ts = tmem + g * 128;
+      // ---- pass 1: row maximum of the scaled, masked scores (base-2 domain), four running maxima ----
+      float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+      for (int c = 0; c < n_chunks; ++c) {
+        uint32_t r[32];
+        tmem_ld32(ts + c * 32, r);
+        tmem_ld_wait(r);
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          const int key = c * 32 + i;
+          float t0 = __uint_as_float(r[i]) * sl2, t1 = __uint_as_float(r[i + 1]) * sl2,
+                t2 = __uint_as_float(r[i + 2]) * sl2, t3 = __uint_as_float(r[i + 3]) * sl2;
+          if (key + 3 >= kv_len) {
+            t0 = key < S ? t0 + (key >= kv_len ? mask_l2 : 0.f) : -INFINITY;
+            t1 = key + 1 < S ? t1 + (key + 1 >= kv_len ? mask_l2 : 0.f) : -INFINITY;
+            t2 = key + 2 < S ? t2 + (key + 2 >= kv_len ? mask_l2 : 0.f) : -INFINITY;
+            t3 = key + 3 < S ? t3 + (key + 3 >= kv_len ? mask_l2 : 0.f) : -INFINITY;
+          }
+          m0 = fmaxf(m0, t0); m1 = fmaxf(m1, t1); m2 = fmaxf(m2, t2); m3 = fmaxf(m3, t3);
+        }
+      }
+      const float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+      // ---- pass 2: unnormalised probabilities -> fp16 A-operand tile (128B-swizzled rows) ----
+      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+      for (int c = 0; c < 4; ++c) {
+        uint32_t w[16];
+        if (c >= n_chunks) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) w[i] = 0u;
+        } else {
+          uint32_t r[32];
+          tmem_ld32(ts + c * 32, r);
+          tmem_ld_wait(r);
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const int key = c * 32 + i;
+            float t0 = __uint_as_float(r[i]) * sl2, t1 = __uint_as_float(r[i + 1]) * sl2,
+                  t2 = __uint_as_float(r[i + 2]) * sl2, t3 = __uint_as_float(r[i + 3]) * sl2;
+            float p0, p1, p2, p3;
+            if (key + 3 >= kv_len) {
+              p0 = key < S ? ex2_fast(t0 + (key >= kv_len ? mask_l2 : 0.f) - mx) : 0.f;
+              p1 = key + 1 < S ? ex2_fast(t1 + (key + 1 >= kv_len ? mask_l2 : 0.f) - mx) : 0.f;
+              p2 = key + 2 < S ? ex2_fast(t2 + (key + 2 >= kv_len ? mask_l2 : 0.f) - mx) : 0.f;
+              p3 = key + 3 < S ? ex2_fast(t3 + (key + 3 >= kv_len ? mask_l2 : 0.f) - mx) : 0.f;
+            } else {
+              p0 = ex2_fast(t0 - mx); p1 = ex2_fast(t1 - mx); p2 = ex2_fast(t2 - mx); p3 = ex2_fast(t3 - mx);
+            }
+            s0 += p0; s1 += p1; s2 += p2; s3 += p3;
+            w[i >> 1] = pack_h2(p0, p1);
+            w[(i >> 1) + 1] = pack_h2(p2, p3);
+          }
+        }
+        uint8_t* base = pbase + (c >> 1) * kATileBytes;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int j = (c & 1) * 4 + i;
+          *reinterpret_cast<uint4*>(base + ((j ^ (r_in & 7)) << 4)) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+        }
+      }
+      const float inv = 1.0f / ((s0 + s1) + (s2 + s3));
+      if (probs) {                                            // parity output: normalised probabilities
+        for (int c = 0; c < n_chunks; ++c) {
+          uint32_t r[32];
+          tmem_ld32(ts + c * 32, r);
+          tmem_ld_wait(r);
+          if (r_in < S) {
+            __half* dst = probs + ((size_t)(b * H + h) * S + r_in) * S + c * 32;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int key = c * 32 + i;
+              const float t = __uint_as_float(r[i]) * sl2 + (key >= kv_len ? mask_l2 : 0.0f);
+              if (key < S) dst[i] = __float2half_rn(ex2_fast(t - mx) * inv);
+            }
+          }
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(bar(g, AB_P_FULL));
+      if (!mbar_wait_warp(bar(g, AB_O_FULL), bit, ctl, 522 + g, lane)) break;
+      tc_fence_after_sync();
+      {
+        // O rows are 128 bytes: two staged stores of 64 bytes per row
+        const int row0 = q * 32;
+        uint8_t* rowptr[4];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t r[32];
+          tmem_ld32(tmem + kPipeOCol + g * 64 + half * 32, r);
+          tmem_ld_wait(r);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int rr = row0 + 8 * i + (lane >> 2);
+            rowptr[i] = rr < S ? reinterpret_cast<uint8_t*>(ctx + ((size_t)b * S + rr) * hidden + h * hd + half * 32) : nullptr;
+          }
+          uint32_t w[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) w[i] = pack_h2(__uint_as_float(r[2 * i]) * inv, __uint_as_float(r[2 * i + 1]) * inv);
+          staged_store_64B(sbuf, w, rowptr, lane);
+        }
+      }
+      tc_fence_before_sync();
+      bit ^= 1u;
+    }
+    if (q == 0 && lane == 0) { /* phase bookkeeping is per thread; nothing shared to update */ }
+    if (g) rs.attn_bit1 = bit; else rs.attn_bit = bit;
+    // the other pipeline's bit advances with that pipeline's item count
+    const int n_other = (my_items + (g ? 1 : 0)) >> 1;        // items handled by pipeline 1-g
+    if (g) rs.attn_bit ^= (uint32_t)(n_other & 1); else rs.attn_bit1 ^= (uint32_t)(n_other & 1);
   }
 }
 
@@ -808,8 +1012,7 @@ __device__ void ln_stage(const Stage& st, const MegaParams& p, SmemCtl& cs, uint
   int k = 0;
   for (int batch = blockIdx.x; batch < n_batches; batch += gridDim.x, ++k) {
     const int buf = k % nbuf;
-    bool ok = mbar_wait(smem_u32(&cs.ln_full[buf]), (rs.ln_bits >> buf) & 1u, ctl, 600 + buf);
-    ok = __all_sync(0xffffffffu, ok);
+    const bool ok = mbar_wait_warp(smem_u32(&cs.ln_full[buf]), (rs.ln_bits >> buf) & 1u, ctl, 600 + buf, lane);
     rs.ln_bits ^= 1u << buf;
     if (!ok) break;
     const int row0 = batch * rb;
@@ -840,6 +1043,8 @@ __device__ void ln_stage(const Stage& st, const MegaParams& p, SmemCtl& cs, uint
 // ------------------------------------------------------------------------------------
 // the kernel
 // ------------------------------------------------------------------------------------
+// 320 threads leave 168 registers per thread (the register file is handed out per four warps); the
+// epilogue is written to stay below that without spilling.
 __global__ void __launch_bounds__(kThreads, 1)
 souffle_megakernel(const __grid_constant__ CallArgs ca) {
   const MegaParams& p = ca.p;
@@ -869,6 +1074,7 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
     mbar_init(smem_u32(&cs.s_full), 1);
     mbar_init(smem_u32(&cs.p_full), 128);
     mbar_init(smem_u32(&cs.o_full), 1);
+    for (int i = 0; i < 7; ++i) mbar_init(smem_u32(&cs.attn1[i]), i == 5 ? 128 : 1);
     for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&cs.ln_full[i]), 1);
     cs.abort = 0;
     fence_mbar_init();
@@ -905,7 +1111,8 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
     if (st.type == STAGE_GEMM) {
       gemm_stage(st, ca, cs, ring, vec_s, stage_s, rs, ctl, warp, lane);
     } else if (st.type == STAGE_ATTN) {
-      attn_stage(st, ca, cs, ring, ring_ptr, rs, ctl, warp, lane);
+      if (st.seq <= 128) attn_stage_pp(st, ca, cs, ring, ring_ptr, stage_s, rs, ctl, warp, lane);
+      else attn_stage(st, ca, cs, ring, ring_ptr, rs, ctl, warp, lane);
     } else {
       ln_stage(st, p, cs, ring, ring_ptr, rs, ctl, warp, lane);
     }

@@ -84,6 +84,18 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
   return true;
 }
 
+// Warp-collective bounded wait: one lane polls, the verdict is broadcast.  Keeps 31 lanes per warp
+// from hammering the barrier word while the producer and MMA lanes work on its neighbours.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, const WaitCtl& c, int where, int lane) {
+  int ok = 1;
+  if (lane == 0) ok = mbar_wait(bar, parity, c, where) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+// Named barrier among a subset of warps (id 1..15, thread count a multiple of 32).
+__device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
 // ------------------------------------------------------------------------------------
 // proxies and fences
 // ------------------------------------------------------------------------------------

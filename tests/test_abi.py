@@ -72,3 +72,13 @@ def test_python_mirror_validates_before_calling():
         bert.souffle_bert_layer(x, x, x, x, x, 3)           # CPU tensors
     with pytest.raises(ValueError):
         swin.swin_ffn(x[0], x[0], 1, 2, 3)
+
+
+def test_persistent_kernels_do_not_spill():
+    usage = build.resource_usage()
+    mega = [v for k, v in usage.items() if "souffle_megakernel" in k]
+    lstm = [v for k, v in usage.items() if "souffle_lstm_wavefront" in k]
+    assert mega and lstm
+    for regs, st, ld in mega + lstm:
+        assert st == 0 and ld == 0, f"kernel spills ({st} B stores, {ld} B loads, {regs} registers)"
+    assert mega[0][0] <= 168          # 320 threads per CTA leave 168 registers per thread
