@@ -57,7 +57,7 @@ typedef enum SouffleBertVariant {
 typedef struct SouffleBertDesc {
   int32_t batch;      /* sequences per call */
   int32_t seq;        /* tokens per sequence: multiple of 16, <= 128, or 256 / 384 */
-  int32_t heads;      /* even, heads * head_dim <= 1024 */
+  int32_t heads;      /* 2, 4, 8, 12 or 16 (hidden = heads * 64 in {128, 256, 512, 768, 1024}) */
   int32_t head_dim;   /* 64 */
   int32_t ffn;        /* intermediate size, multiple of 64 */
   int32_t n_layers;   /* >= 1: layers chained inside one launch */
@@ -200,7 +200,7 @@ int souffle_swin_mlp_forward(const void* src, const void* fc1_w, const void* fc2
                              souffle_stream_t stream);
 
 /* out[M][N] (fp16) = LayerNorm(sum_p partial[p][M][N] (fp32) + bias[N] + resid[M][N]) * gamma + beta, statistics
- * in fp32 over each row; bias, resid, gamma/beta (fp16) may be null.  N % 128 == 0, N <= 1024.  This is the
+ * in fp32 over each row; bias, resid, gamma/beta (fp16) may be null.  N in {128, 256, 512, 768, 1024}.  This is the
  * normalisation stage of the fused layer (cpp/bert/kernels/fused_sqq_bert.cu:3690-3782) as a call of its own. */
 int souffle_layernorm_forward(const float* partial, int32_t n_partial, const void* bias, const void* resid,
                               const void* gamma, const void* beta, void* out, int32_t M, int32_t N, float eps,

@@ -782,11 +782,15 @@ __device__ void attn_stage_pp(const Stage& st, const CallArgs& ca, SmemCtl& ctl_
     uint8_t* pbase = ring_ptr + g * kPipeBytes + 3 * kATileBytes + r_in * 128;
     uint32_t bit = g ? rs.attn_bit1 : rs.attn_bit;
     const int n_chunks = (S + 31) >> 5;
+    const bool prof = p.prof != nullptr;
+    long long t_ws = 0, t_sm = 0, t_wo = 0, t_ep = 0, t_p1 = 0;
     for (int k = g; k < my_items; k += 2) {
       const int item = blockIdx.x + k * gridDim.x;
       const int h = item % H, b = item / H;
       const int kv_len = lens ? lens[b] : S;
+      const long long c0 = prof ? clock64() : 0;
       if (!mbar_wait_warp(bar(g, AB_S_FULL), bit, ctl, 520 + g, lane)) break;
+      const long long c1 = prof ? clock64() : 0;
       tc_fence_after_sync();
       const uint32_t ts = tmem + g * 128;
       // ---- pass 1: row maximum of the scaled, masked scores (base-2 domain), four running maxima ----
@@ -810,6 +814,7 @@ __device__ void attn_stage_pp(const Stage& st, const CallArgs& ca, SmemCtl& ctl_
         }
       }
       const float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+      const long long c1a = prof ? clock64() : 0;
       // ---- pass 2: unnormalised probabilities -> fp16 A-operand tile (128B-swizzled rows) ----
       float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
       for (int c = 0; c < 4; ++c) {
@@ -867,7 +872,9 @@ __device__ void attn_stage_pp(const Stage& st, const CallArgs& ca, SmemCtl& ctl_
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(bar(g, AB_P_FULL));
+      const long long c2 = prof ? clock64() : 0;
       if (!mbar_wait_warp(bar(g, AB_O_FULL), bit, ctl, 522 + g, lane)) break;
+      const long long c3 = prof ? clock64() : 0;
       tc_fence_after_sync();
       {
         // O rows are 128 bytes: two staged stores of 64 bytes per row
@@ -891,8 +898,12 @@ __device__ void attn_stage_pp(const Stage& st, const CallArgs& ca, SmemCtl& ctl_
       }
       tc_fence_before_sync();
       bit ^= 1u;
+      if (prof) { const long long c4 = clock64(); t_ws += c1 - c0; t_sm += c2 - c1; t_wo += c3 - c2; t_ep += c4 - c3; t_p1 += c1a - c1; }
     }
-    if (q == 0 && lane == 0) { /* phase bookkeeping is per thread; nothing shared to update */ }
+    if (prof && warp == 2 && lane == 0) {  // [3] waiting for scores, [4] softmax, [5] waiting for P.V, [6] output
+      long long* pr = p.prof + ((size_t)st.prof_index * gridDim.x + blockIdx.x) * 8;
+      pr[3] = t_ws; pr[4] = t_sm; pr[5] = t_wo; pr[6] = t_ep; pr[7] = t_p1;
+    }
     if (g) rs.attn_bit1 = bit; else rs.attn_bit = bit;
     // the other pipeline's bit advances with that pipeline's item count
     const int n_other = (my_items + (g ? 1 : 0)) >> 1;        // items handled by pipeline 1-g
@@ -908,58 +919,88 @@ __device__ void attn_stage_pp(const Stage& st, const CallArgs& ca, SmemCtl& ctl_
 // ------------------------------------------------------------------------------------
 constexpr int kLnMaxBufs = 4;
 
+// Two rows per call (the second optional): their instruction streams interleave, which hides the
+// shared-memory, shuffle and MUFU latencies a single row's dependent chain exposes.
 template <int NJ>
-__device__ __forceinline__ void ln_row(const float* pl0, int n_partial, int plane_stride, const __half* res_row,
-                                       const __half* bias, const __half* gamma, const __half* beta, float eps,
-                                       __half* out_row, int lane) {
-  float z[NJ][4];
+__device__ __forceinline__ void ln_rows2(const float* pl0, const float* pl1, int n_partial, int plane_stride,
+                                         const __half* res0, const __half* res1, const __half* bias,
+                                         const __half* gamma, const __half* beta, float eps, __half* out0, __half* out1,
+                                         int lane) {
+  const bool two = pl1 != nullptr;
+  float z[2][NJ][4];
 #pragma unroll
   for (int j = 0; j < NJ; ++j) {
     const float4 a = *reinterpret_cast<const float4*>(pl0 + (lane + 32 * j) * 4);
-    z[j][0] = a.x; z[j][1] = a.y; z[j][2] = a.z; z[j][3] = a.w;
+    const float4 b = two ? *reinterpret_cast<const float4*>(pl1 + (lane + 32 * j) * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    z[0][j][0] = a.x; z[0][j][1] = a.y; z[0][j][2] = a.z; z[0][j][3] = a.w;
+    z[1][j][0] = b.x; z[1][j][1] = b.y; z[1][j][2] = b.z; z[1][j][3] = b.w;
   }
   for (int pl = 1; pl < n_partial; ++pl) {
 #pragma unroll
     for (int j = 0; j < NJ; ++j) {
       const float4 a = *reinterpret_cast<const float4*>(pl0 + (size_t)pl * plane_stride + (lane + 32 * j) * 4);
-      z[j][0] += a.x; z[j][1] += a.y; z[j][2] += a.z; z[j][3] += a.w;
+      z[0][j][0] += a.x; z[0][j][1] += a.y; z[0][j][2] += a.z; z[0][j][3] += a.w;
+      if (two) {
+        const float4 b = *reinterpret_cast<const float4*>(pl1 + (size_t)pl * plane_stride + (lane + 32 * j) * 4);
+        z[1][j][0] += b.x; z[1][j][1] += b.y; z[1][j][2] += b.z; z[1][j][3] += b.w;
+      }
     }
   }
-  if (res_row) {
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) {
-      const uint2 u = *reinterpret_cast<const uint2*>(res_row + (lane + 32 * j) * 4);
-      const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
-      const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
-      z[j][0] += f0.x; z[j][1] += f0.y; z[j][2] += f1.x; z[j][3] += f1.y;
-    }
-  }
-  if (bias) {
-#pragma unroll
-    for (int j = 0; j < NJ; ++j) {
+  for (int j = 0; j < NJ; ++j) {
+    float add[4] = {0.f, 0.f, 0.f, 0.f};
+    if (bias) {
       const uint2 u = __ldg(reinterpret_cast<const uint2*>(bias + (lane + 32 * j) * 4));
       const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
       const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
-      z[j][0] += f0.x; z[j][1] += f0.y; z[j][2] += f1.x; z[j][3] += f1.y;
+      add[0] = f0.x; add[1] = f0.y; add[2] = f1.x; add[3] = f1.y;
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const __half* res = r ? res1 : res0;
+      float rr[4] = {0.f, 0.f, 0.f, 0.f};
+      if (res && (r == 0 || two)) {
+        const uint2 u = *reinterpret_cast<const uint2*>(res + (lane + 32 * j) * 4);
+        const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
+        const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+        rr[0] = f0.x; rr[1] = f0.y; rr[2] = f1.x; rr[3] = f1.y;
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) z[r][j][i] += add[i] + rr[i];
     }
   }
   const float inv_n = 1.0f / (float)(NJ * 128);
-  float s1 = 0.0f;
-#pragma unroll
-  for (int j = 0; j < NJ; ++j) s1 += (z[j][0] + z[j][1]) + (z[j][2] + z[j][3]);
-  const float mean = warp_sum(s1) * inv_n;
-  float s2 = 0.0f;
+  float sa = 0.0f, sb = 0.0f;
 #pragma unroll
   for (int j = 0; j < NJ; ++j) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) { const float d = z[j][i] - mean; s2 = fmaf(d, d, s2); }
+    sa += (z[0][j][0] + z[0][j][1]) + (z[0][j][2] + z[0][j][3]);
+    sb += (z[1][j][0] + z[1][j][1]) + (z[1][j][2] + z[1][j][3]);
   }
-  const float rstd = rsqrtf(warp_sum(s2) * inv_n + eps);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    sa += __shfl_xor_sync(0xffffffffu, sa, o);
+    sb += __shfl_xor_sync(0xffffffffu, sb, o);
+  }
+  const float mean0 = sa * inv_n, mean1 = sb * inv_n;
+  float va = 0.0f, vb = 0.0f;
 #pragma unroll
   for (int j = 0; j < NJ; ++j) {
-    float y[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) y[i] = (z[j][i] - mean) * rstd;
+    for (int i = 0; i < 4; ++i) {
+      const float d0 = z[0][j][i] - mean0, d1 = z[1][j][i] - mean1;
+      va = fmaf(d0, d0, va);
+      vb = fmaf(d1, d1, vb);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    va += __shfl_xor_sync(0xffffffffu, va, o);
+    vb += __shfl_xor_sync(0xffffffffu, vb, o);
+  }
+  const float rstd0 = rsqrtf(va * inv_n + eps), rstd1 = rsqrtf(vb * inv_n + eps);
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) {
+    float g[4] = {1.f, 1.f, 1.f, 1.f}, bt[4] = {0.f, 0.f, 0.f, 0.f};
     if (gamma) {
       const uint2 ug = __ldg(reinterpret_cast<const uint2*>(gamma + (lane + 32 * j) * 4));
       const uint2 ub = __ldg(reinterpret_cast<const uint2*>(beta + (lane + 32 * j) * 4));
@@ -967,10 +1008,18 @@ __device__ __forceinline__ void ln_row(const float* pl0, int n_partial, int plan
       const float2 g1 = __half22float2(*reinterpret_cast<const __half2*>(&ug.y));
       const float2 b0 = __half22float2(*reinterpret_cast<const __half2*>(&ub.x));
       const float2 b1 = __half22float2(*reinterpret_cast<const __half2*>(&ub.y));
-      y[0] = fmaf(y[0], g0.x, b0.x); y[1] = fmaf(y[1], g0.y, b0.y);
-      y[2] = fmaf(y[2], g1.x, b1.x); y[3] = fmaf(y[3], g1.y, b1.y);
+      g[0] = g0.x; g[1] = g0.y; g[2] = g1.x; g[3] = g1.y;
+      bt[0] = b0.x; bt[1] = b0.y; bt[2] = b1.x; bt[3] = b1.y;
     }
-    *reinterpret_cast<uint2*>(out_row + (lane + 32 * j) * 4) = make_uint2(pack_h2(y[0], y[1]), pack_h2(y[2], y[3]));
+    float y[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) y[i] = fmaf((z[0][j][i] - mean0) * rstd0, g[i], bt[i]);
+    *reinterpret_cast<uint2*>(out0 + (lane + 32 * j) * 4) = make_uint2(pack_h2(y[0], y[1]), pack_h2(y[2], y[3]));
+    if (two) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) y[i] = fmaf((z[1][j][i] - mean1) * rstd1, g[i], bt[i]);
+      *reinterpret_cast<uint2*>(out1 + (lane + 32 * j) * 4) = make_uint2(pack_h2(y[0], y[1]), pack_h2(y[2], y[3]));
+    }
   }
 }
 
@@ -983,11 +1032,12 @@ __device__ void ln_stage(const Stage& st, const MegaParams& p, SmemCtl& cs, uint
   const __half* gamma = reinterpret_cast<const __half*>(st.gamma);
   const __half* beta = reinterpret_cast<const __half*>(st.beta);
   const int row_bytes = (P * 4 + (resid ? 2 : 0)) * N;
-  // rows per batch: about 52 KB per batch, at most 12 rows, and few enough that every CTA gets work
-  int rb = 53248 / row_bytes;
-  rb = rb > 12 ? 12 : (rb < 1 ? 1 : rb);
+  // rows per batch: up to 96 KB (two batches in flight), at most 20 rows, and few enough that every CTA gets work
+  int rb = 98304 / row_bytes;
+  rb = rb > 20 ? 20 : (rb < 1 ? 1 : rb);
   const int per_cta = (M + (int)gridDim.x - 1) / (int)gridDim.x;
   if (rb > per_cta) rb = per_cta;
+  if (rb > kThreads / 32) rb -= rb % (kThreads / 32);        // whole rounds of one or two rows per warp
   const int batch_bytes = rb * row_bytes;
   int nbuf = kRingBytes / batch_bytes;
   nbuf = nbuf > kLnMaxBufs ? kLnMaxBufs : nbuf;
@@ -1010,33 +1060,48 @@ __device__ void ln_stage(const Stage& st, const MegaParams& p, SmemCtl& cs, uint
     for (int j = 0; j < nbuf && b < n_batches; ++j, b += gridDim.x) issue(b, j);
   }
   int k = 0;
+  const bool prof = p.prof != nullptr;
+  long long t_wait = 0, t_sync = 0;
   for (int batch = blockIdx.x; batch < n_batches; batch += gridDim.x, ++k) {
     const int buf = k % nbuf;
+    const long long tw = prof ? clock64() : 0;
     const bool ok = mbar_wait_warp(smem_u32(&cs.ln_full[buf]), (rs.ln_bits >> buf) & 1u, ctl, 600 + buf, lane);
+    if (prof) t_wait += clock64() - tw;
     rs.ln_bits ^= 1u << buf;
     if (!ok) break;
     const int row0 = batch * rb;
     const int rows = (M - row0) < rb ? (M - row0) : rb;
     const float* base = reinterpret_cast<const float*>(ring_ptr + buf * batch_bytes);
     const __half* rbase = reinterpret_cast<const __half*>(ring_ptr + buf * batch_bytes + P * rb * N * 4);
-    for (int r = warp; r < rows; r += nwarps) {
+    for (int r = warp; r < rows; r += 2 * nwarps) {
+      const int r2 = r + nwarps;
+      const bool two = r2 < rows;
       const float* pl0 = base + (size_t)r * N;
-      const __half* rr = resid ? rbase + (size_t)r * N : nullptr;
-      __half* orow = out + (size_t)(row0 + r) * N;
+      const float* pl1 = two ? base + (size_t)r2 * N : nullptr;
+      const __half* ra = resid ? rbase + (size_t)r * N : nullptr;
+      const __half* rb2 = (resid && two) ? rbase + (size_t)r2 * N : nullptr;
+      __half* o0 = out + (size_t)(row0 + r) * N;
+      __half* o1 = out + (size_t)(row0 + r2) * N;
       switch (N >> 7) {
-        case 1: ln_row<1>(pl0, P, rb * N, rr, bias, gamma, beta, st.eps, orow, lane); break;
-        case 2: ln_row<2>(pl0, P, rb * N, rr, bias, gamma, beta, st.eps, orow, lane); break;
-        case 3: ln_row<3>(pl0, P, rb * N, rr, bias, gamma, beta, st.eps, orow, lane); break;
-        case 4: ln_row<4>(pl0, P, rb * N, rr, bias, gamma, beta, st.eps, orow, lane); break;
-        case 5: ln_row<5>(pl0, P, rb * N, rr, bias, gamma, beta, st.eps, orow, lane); break;
-        case 6: ln_row<6>(pl0, P, rb * N, rr, bias, gamma, beta, st.eps, orow, lane); break;
-        case 7: ln_row<7>(pl0, P, rb * N, rr, bias, gamma, beta, st.eps, orow, lane); break;
-        default: ln_row<8>(pl0, P, rb * N, rr, bias, gamma, beta, st.eps, orow, lane); break;
+        case 1: ln_rows2<1>(pl0, pl1, P, rb * N, ra, rb2, bias, gamma, beta, st.eps, o0, o1, lane); break;
+        case 2: ln_rows2<2>(pl0, pl1, P, rb * N, ra, rb2, bias, gamma, beta, st.eps, o0, o1, lane); break;
+        case 4: ln_rows2<4>(pl0, pl1, P, rb * N, ra, rb2, bias, gamma, beta, st.eps, o0, o1, lane); break;
+        case 6: ln_rows2<6>(pl0, pl1, P, rb * N, ra, rb2, bias, gamma, beta, st.eps, o0, o1, lane); break;
+        default: ln_rows2<8>(pl0, pl1, P, rb * N, ra, rb2, bias, gamma, beta, st.eps, o0, o1, lane); break;
       }
     }
+    const long long ts = prof ? clock64() : 0;
     __syncthreads();                       // every warp is done with this buffer before it is refilled
+    if (prof) t_sync += clock64() - ts;
     const int next = batch + nbuf * (int)gridDim.x;
     if (threadIdx.x == 0 && next < n_batches) issue(next, buf);
+  }
+  if (prof && warp == 2 && lane == 0) {    // [3] waiting for a batch, [4] waiting for the other warps
+    long long* pr = p.prof + ((size_t)st.prof_index * gridDim.x + blockIdx.x) * 8;
+    pr[3] = t_wait;
+    pr[4] = t_sync;
+    pr[5] = rb;
+    pr[6] = nbuf;
   }
 }
 

@@ -451,7 +451,8 @@ int souffle_bert_plan_create(const SouffleBertDesc* desc, const SouffleBertLayer
   const bool seq_ok = (d.seq >= 16 && d.seq <= 128 && d.seq % 16 == 0) || d.seq == 256 || d.seq == 384;
   if (!seq_ok) return fail(SOUFFLE_BAD_SHAPE, "seq must be a multiple of 16 up to 128, or 256, or 384 (got %d)", d.seq);
   const int H = d.heads * d.head_dim;
-  if (H > 1024 || H % 128) return fail(SOUFFLE_BAD_SHAPE, "hidden size %d must be a multiple of 128 up to 1024", H);
+  if (H != 128 && H != 256 && H != 512 && H != 768 && H != 1024)
+    return fail(SOUFFLE_BAD_SHAPE, "hidden size %d must be 128, 256, 512, 768 or 1024", H);
   if (d.ffn < 64 || d.ffn % 64) return fail(SOUFFLE_BAD_SHAPE, "ffn must be a positive multiple of 64 (got %d)", d.ffn);
   if (d.variant != SOUFFLE_BERT_STD && d.variant != SOUFFLE_BERT_REF_COMPAT)
     return fail(SOUFFLE_BAD_ARGUMENT, "unknown variant %d", d.variant);
@@ -676,8 +677,8 @@ int souffle_swin_mlp_forward(const void* src, const void* fc1_w, const void* fc2
 int souffle_layernorm_forward(const float* partial, int32_t n_partial, const void* bias, const void* resid,
                               const void* gamma, const void* beta, void* out, int32_t M, int32_t N, float eps,
                               void* workspace, size_t workspace_bytes, souffle_stream_t stream) {
-  if (M < 1 || N < 128 || N % 128 || N > 1024 || n_partial < 1 || n_partial > 16)
-    return fail(SOUFFLE_BAD_SHAPE, "LayerNorm needs M >= 1, N a multiple of 128 up to 1024, 1 <= n_partial <= 16 (got %d, %d, %d)", M, N, n_partial);
+  if (M < 1 || (N != 128 && N != 256 && N != 512 && N != 768 && N != 1024) || n_partial < 1 || n_partial > 16)
+    return fail(SOUFFLE_BAD_SHAPE, "LayerNorm needs M >= 1, N in {128, 256, 512, 768, 1024}, 1 <= n_partial <= 16 (got %d, %d, %d)", M, N, n_partial);
   if (!aligned16(partial) || !aligned16(out) || (bias && !aligned16(bias)) || (resid && !aligned16(resid)) ||
       (gamma && !aligned16(gamma)) || (beta && !aligned16(beta)))
     return fail(SOUFFLE_BAD_POINTER, "operands must be 16-byte aligned");
