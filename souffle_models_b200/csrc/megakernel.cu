@@ -163,7 +163,7 @@ __device__ __forceinline__ GemmGeom gemm_geom(const Stage& st, int max_slots) {
 // Epilogue parameters of a stage, copied into registers once (the stage record itself lives in
 // shared memory and would otherwise be re-read around every asm statement).
 struct EpiCtx {
-  int epi, act, M, N, ldo, heads, head_dim, seq;
+  int epi, act, M, N, ldo, heads, head_dim, seq, win, shift;
   size_t head_plane;       // seq * head_dim
   size_t qkv_plane;        // batch * heads * seq * head_dim
   const __half* bias_s;    // bias staged in shared memory, or null
@@ -188,6 +188,30 @@ __device__ __forceinline__ void staged_store_64B(uint8_t* sbuf, const uint32_t (
     if (rowptr[i]) *reinterpret_cast<uint4*>(rowptr[i] + (lane & 3) * 16) = v;
   }
   __syncwarp();
+}
+
+// Swin row maps.  Tokens of an R x R grid are rolled by -shift and cut into (R/win)^2 windows of win*win
+// tokens; the window-major buffers give every window 64 row slots (49 used for win = 7).
+// token row (b*R*R + ty*R + tx)  ->  window-major row (global window)*64 + position
+__device__ __forceinline__ int swin_token_to_slot(int row, int R, int win, int shift) {
+  const int img = row / (R * R), t = row - img * R * R;
+  const int ty = t / R, tx = t - ty * R;
+  int sy = ty - shift, sx = tx - shift;
+  if (sy < 0) sy += R;
+  if (sx < 0) sx += R;
+  const int nwr = R / win;
+  const int w = (sy / win) * nwr + sx / win, pos = (sy % win) * win + sx % win;
+  return (img * nwr * nwr + w) * 64 + pos;
+}
+// window-major row -> token row, or -1 for a padding slot
+__device__ __forceinline__ int swin_slot_to_token(int slot, int R, int win, int shift, int n_windows) {
+  const int wg = slot >> 6, pos = slot & 63;
+  if (pos >= win * win || wg >= n_windows) return -1;
+  const int nwr = R / win, img = wg / (nwr * nwr), w = wg - img * nwr * nwr;
+  int ty = (w / nwr) * win + pos / win + shift, tx = (w % nwr) * win + pos % win + shift;
+  if (ty >= R) ty -= R;
+  if (tx >= R) tx -= R;
+  return img * R * R + ty * R + tx;
 }
 
 // One 32-column chunk of the accumulator block: r[i] = column col+i of this thread's row `row`.
@@ -234,8 +258,10 @@ __device__ __forceinline__ void epilogue_chunk32(const EpiCtx& e, uint8_t* sbuf,
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
   }
-  if (e.resid && row < e.M) {
-    const uint4* r4 = reinterpret_cast<const uint4*>(e.resid + (size_t)row * e.ldo + col);
+  int resid_row = row < e.M ? row : -1;
+  if (e.epi == EPI_SWIN_PROJ) resid_row = swin_slot_to_token(row, e.seq, e.win, e.shift, e.M >> 6);
+  if (e.resid && resid_row >= 0) {
+    const uint4* r4 = reinterpret_cast<const uint4*>(e.resid + (size_t)resid_row * e.ldo + col);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const uint4 u = r4[i];
@@ -258,6 +284,21 @@ __device__ __forceinline__ void epilogue_chunk32(const EpiCtx& e, uint8_t* sbuf,
       const int b = trow[i] / e.seq, sq = trow[i] - b * e.seq;
       rowptr[i] = trow[i] < e.M ? reinterpret_cast<uint8_t*>(e.out + coloff + (size_t)b * e.heads * e.head_plane + (size_t)sq * e.head_dim)
                                 : nullptr;
+    }
+  } else if (e.epi == EPI_SWIN_QKV) {
+    // [3][windows][64][C]: the column picks q/k/v and the channel, the row its window slot
+    const int which = col / e.ldo, ch = col - which * e.ldo;
+    const size_t plane = (size_t)((e.M + e.seq * e.seq - 1) / (e.seq * e.seq)) * (e.seq / e.win) * (e.seq / e.win) * 64 * e.ldo;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      rowptr[i] = trow[i] < e.M ? reinterpret_cast<uint8_t*>(e.out + (size_t)which * plane +
+                                                              (size_t)swin_token_to_slot(trow[i], e.seq, e.win, e.shift) * e.ldo + ch)
+                                : nullptr;
+  } else if (e.epi == EPI_SWIN_PROJ) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int t = trow[i] < e.M ? swin_slot_to_token(trow[i], e.seq, e.win, e.shift, e.M >> 6) : -1;
+      rowptr[i] = t >= 0 ? reinterpret_cast<uint8_t*>(e.out + (size_t)t * e.ldo + col) : nullptr;
     }
   } else {
 #pragma unroll
@@ -324,7 +365,7 @@ __device__ __forceinline__ void epilogue_chunk16(const EpiCtx& e, const uint32_t
 // Tiles are bm x bn with bm = 128 (two accumulators used alternately, so the epilogue of one tile
 // overlaps the main loop of the next) or bm = 256 (two 128-row halves share every B tile, which
 // halves the B traffic per FLOP; each half has its own accumulator and hand-shake).
-__device__ void gemm_stage(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, uint32_t ring, __half* vec_s,
+__device__ __noinline__ void gemm_stage(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, uint32_t ring, __half* vec_s,
                            uint8_t* stage_s, RoleState& rs, const WaitCtl& ctl, int warp, int lane) {
   const MegaParams& p = ca.p;
   const GemmGeom g = gemm_geom(st, p.max_slots);
@@ -442,7 +483,7 @@ __device__ void gemm_stage(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, 
     const int full_chunks = g.bn >> 5;
     EpiCtx e;
     e.epi = st.epi; e.act = st.act; e.M = st.M; e.N = st.N; e.ldo = st.ldo;
-    e.heads = st.heads; e.head_dim = st.head_dim; e.seq = st.seq;
+    e.heads = st.heads; e.head_dim = st.head_dim; e.seq = st.seq; e.win = st.win; e.shift = st.shift;
     e.head_plane = (size_t)st.seq * st.head_dim;
     e.qkv_plane = (size_t)st.batch * st.heads * e.head_plane;
     e.bias_s = bias_s;
@@ -505,7 +546,7 @@ __device__ void gemm_stage(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, 
 // ------------------------------------------------------------------------------------
 // attention stage: one work item = (sequence, head, 128-query tile); S <= 384, head_dim 64
 // ------------------------------------------------------------------------------------
-__device__ void attn_stage(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, uint32_t ring, uint8_t* ring_ptr,
+__device__ __noinline__ void attn_stage(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, uint32_t ring, uint8_t* ring_ptr,
                            RoleState& rs, const WaitCtl& ctl, int warp, int lane) {
   const MegaParams& p = ca.p;
   const int S = st.seq, B = st.batch, H = st.heads;
@@ -700,7 +741,7 @@ enum AttnBar : int { AB_QK_FULL = 0, AB_QK_EMPTY, AB_V_FULL, AB_V_EMPTY, AB_S_FU
 constexpr int kPipeBytes = 5 * kATileBytes;      // Q 16 KiB, K 16, V 16, P 32
 constexpr int kPipeOCol = 256;                   // TMEM: scores at 0 / 128, outputs at 256 / 320
 
-__device__ void attn_stage_pp(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, uint32_t ring, uint8_t* ring_ptr,
+__device__ __noinline__ void attn_stage_pp(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, uint32_t ring, uint8_t* ring_ptr,
                               uint8_t* stage_s, RoleState& rs, const WaitCtl& ctl, int warp, int lane) {
   const MegaParams& p = ca.p;
   const int S = st.seq, B = st.batch, H = st.heads;
@@ -912,6 +953,177 @@ __device__ void attn_stage_pp(const Stage& st, const CallArgs& ca, SmemCtl& ctl_
 }
 
 // ------------------------------------------------------------------------------------
+// Swin window attention: one work item = (window, head).  Q/K/V live window-major as [3][windows][64][C]
+// with the heads side by side in C, so one 64-column TMA box holds a PAIR of 32-wide heads; the MMAs of
+// head h read their half of every 128-byte row (K-major operands: descriptor start +64 B for odd heads)
+// or their half of the output columns (P.V is computed for the pair, the other half is dropped).
+// Scores get the relative-position bias of the (query, key) offset and, for shifted windows, -100 where
+// query and key come from different sides of the wrap-around.  Slots >= win*win are padding.
+// ------------------------------------------------------------------------------------
+// Softmax of one query row of a WS x WS window (thread = row): reads the 64 score columns from TMEM,
+// adds bias and shift mask, writes the unnormalised probabilities as an fp16 A-operand row (128B swizzle)
+// and returns their sum.  Rows and keys >= WS*WS are padding (probability 0).
+template <int WS>
+__device__ __forceinline__ float swin_softmax_row(uint32_t tmem, const float* bias_s, uint8_t* prow, int r_in, int wy, int wx,
+                                                  int R, int shift, float sl2) {
+  constexpr int NT = WS * WS, TBL = 2 * WS - 1;
+  const bool rowok = r_in < NT;
+  const int qy = rowok ? r_in / WS : 0, qx = rowok ? r_in - qy * WS : 0;
+  // region of a shifted coordinate along one axis: 0 | 1 | 2 (only the last window row/column mixes regions)
+  int regy[WS], regx[WS];
+#pragma unroll
+  for (int i = 0; i < WS; ++i) {
+    const int sy = wy + i, sx = wx + i;
+    regy[i] = shift ? (sy < R - WS ? 0 : (sy < R - shift ? 1 : 2)) : 0;
+    regx[i] = shift ? (sx < R - WS ? 0 : (sx < R - shift ? 1 : 2)) : 0;
+  }
+  int qreg = 0;
+#pragma unroll
+  for (int i = 0; i < WS; ++i) {
+    if (i == qy) qreg += regy[i] * 3;
+    if (i == qx) qreg += regx[i];
+  }
+  const float* brow = bias_s + (qy + WS - 1) * TBL + (qx + WS - 1);   // bias index = brow[-(ky*TBL + kx)]
+  const float mask = -100.0f * 1.4426950408889634f;
+  uint32_t r0[32], r1[32];
+  tmem_ld32(tmem, r0);
+  tmem_ld32(tmem + 32, r1);
+  tmem_ld_wait(r0);
+  tmem_ld_wait(r1);
+  float mx = -INFINITY;
+#pragma unroll
+  for (int k = 0; k < 64; ++k) {
+    if (k < NT) {
+      constexpr int dummy = 0; (void)dummy;
+      const int ky = k / WS, kx = k % WS;
+      float v = __uint_as_float(k < 32 ? r0[k & 31] : r1[k & 31]) * sl2 + brow[-(ky * TBL + kx)];
+      if (regy[ky] * 3 + regx[kx] != qreg) v += mask;
+      if (k < 32) r0[k & 31] = __float_as_uint(v); else r1[k & 31] = __float_as_uint(v);
+      mx = fmaxf(mx, v);
+    }
+  }
+  float sum = 0.f;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    uint32_t wv[16];
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      const int k = half * 32 + i;
+      const float p0 = (k < NT && rowok) ? ex2_fast(__uint_as_float(half ? r1[i] : r0[i]) - mx) : 0.f;
+      const float p1 = (k + 1 < NT && rowok) ? ex2_fast(__uint_as_float(half ? r1[i + 1] : r0[i + 1]) - mx) : 0.f;
+      sum += p0 + p1;
+      wv[i >> 1] = pack_h2(p0, p1);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      *reinterpret_cast<uint4*>(prow + (((half * 4 + j) ^ (r_in & 7)) << 4)) = make_uint4(wv[4 * j], wv[4 * j + 1], wv[4 * j + 2], wv[4 * j + 3]);
+  }
+  return rowok ? sum : 1.0f;
+}
+
+__device__ __noinline__ void attn_swin_stage(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, uint32_t ring, uint8_t* ring_ptr,
+                                uint8_t* stage_s, RoleState& rs, const WaitCtl& ctl, int warp, int lane) {
+  const int R = st.seq, ws = st.win, shift = st.shift, H = st.heads, C = st.ldo;
+  const int nwr = R / ws, nw_img = nwr * nwr, n_windows = st.batch * nw_img, n_tok = ws * ws;
+  const int items = n_windows * H;
+  const uint32_t qk_full = smem_u32(&ctl_s.qk_full), qk_empty = smem_u32(&ctl_s.qk_empty);
+  const uint32_t v_full = smem_u32(&ctl_s.v_full), v_empty = smem_u32(&ctl_s.v_empty);
+  const uint32_t s_full = smem_u32(&ctl_s.s_full), p_full = smem_u32(&ctl_s.p_full), o_full = smem_u32(&ctl_s.o_full);
+  const CUtensorMap* tm = map_ptr(ca, st.tm_qkv);
+  // shared memory: Q 16 KiB | K 16 KiB | V 16 KiB | P 16 KiB
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int item = blockIdx.x; item < items; item += gridDim.x) {
+        const int h = item % H, w = item / H;
+        const int col = (h >> 1) * 64;
+        if (!mbar_wait(qk_empty, rs.attn_bit ^ 1u, ctl, 530)) break;
+        mbar_expect_tx(qk_full, 2u * kATileBytes);
+        tma_load_2d(ring, tm, qk_full, col, (0 * n_windows + w) * 64);
+        tma_load_2d(ring + kATileBytes, tm, qk_full, col, (1 * n_windows + w) * 64);
+        if (!mbar_wait(v_empty, rs.attn_bit ^ 1u, ctl, 531)) break;
+        mbar_expect_tx(v_full, (uint32_t)kATileBytes);
+        tma_load_2d(ring + 2 * kATileBytes, tm, v_full, col, (2 * n_windows + w) * 64);
+        rs.attn_bit ^= 1u;
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = umma_idesc_f16(64u, 0u), idesc_o = umma_idesc_f16(64u, 1u);
+      const uint32_t tmem = ctl_s.tmem_base;
+      for (int item = blockIdx.x; item < items; item += gridDim.x) {
+        const int h = item % H;
+        const uint32_t half = (uint32_t)(h & 1) * 4u;                  // 64 bytes into every 128-byte row
+        if (!mbar_wait(qk_full, rs.attn_bit, ctl, 532)) break;
+        tc_fence_after_sync();
+        {
+          // S[128 x 64] = Q_h K_h^T, K = 32: two K=16 steps
+          const uint64_t hi = (uint64_t)kDescHiSw128 << 32;
+          const uint64_t qd = hi | (umma_desc_lo(ring, 16) + half), kd = hi | (umma_desc_lo(ring + kATileBytes, 16) + half);
+          umma_f16(tmem, qd, kd, idesc_s, 0u);
+          umma_f16(tmem, qd + 2u, kd + 2u, idesc_s, 1u);
+        }
+        umma_commit(s_full);
+        umma_commit(qk_empty);
+        if (!mbar_wait(p_full, rs.attn_bit, ctl, 533)) break;
+        if (!mbar_wait(v_full, rs.attn_bit, ctl, 534)) break;
+        tc_fence_after_sync();
+        // O[128 x 64] = P[128 x 64 keys] V_pair[64 keys x 64]: one K chunk of 64
+        umma_f16_k64(tmem + 128, umma_desc_lo(ring + 3 * kATileBytes, 16), umma_desc_lo(ring + 2 * kATileBytes, 8192), 128u,
+                     idesc_o, 0u);
+        umma_commit(o_full);
+        umma_commit(v_empty);
+        rs.attn_bit ^= 1u;
+      }
+    }
+    __syncwarp();
+  } else if (warp < 6) {
+    const int q = warp & 3, r_in = q * 32 + lane;
+    const uint32_t tmem = ctl_s.tmem_base + ((uint32_t)(q * 32) << 16);
+    const float sl2 = st.scale * 1.4426950408889634f, l2e = 1.4426950408889634f;
+    const __half* table = reinterpret_cast<const __half*>(st.rel_bias);
+    __half* ctx = reinterpret_cast<__half*>(st.out);
+    const int tbl = 2 * ws - 1;
+    float* bias_s = reinterpret_cast<float*>(stage_s);               // this head's column of the bias table (x log2 e)
+    uint8_t* prow = ring_ptr + 3 * kATileBytes + r_in * 128;
+    for (int item = blockIdx.x; item < items; item += gridDim.x) {
+      const int h = item % H, wg = item / H, w = wg % nw_img;
+      const int wy = (w / nwr) * ws, wx = (w % nwr) * ws;
+      named_barrier_sync(2, 128);                                    // previous item's readers are done with bias_s
+      for (int i = r_in; i < tbl * tbl; i += 128) bias_s[i] = __half2float(table[i * H + h]) * l2e;
+      named_barrier_sync(2, 128);
+      if (!mbar_wait_warp(s_full, rs.attn_bit, ctl, 535, lane)) break;
+      tc_fence_after_sync();
+      float sum = 1.0f;
+      if (ws == 7) sum = swin_softmax_row<7>(tmem, bias_s, prow, r_in, wy, wx, R, shift, sl2);
+      else sum = swin_softmax_row<8>(tmem, bias_s, prow, r_in, wy, wx, R, shift, sl2);
+      const float inv = 1.0f / sum;
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(p_full);
+      if (!mbar_wait_warp(o_full, rs.attn_bit, ctl, 536, lane)) break;
+      tc_fence_after_sync();
+      {
+        uint32_t o[32];
+        tmem_ld32(tmem + 128 + (h & 1) * 32, o);
+        tmem_ld_wait(o);
+        if (r_in < n_tok) {
+          uint4* dst = reinterpret_cast<uint4*>(ctx + ((size_t)wg * 64 + r_in) * C + h * 32);
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            dst[i] = make_uint4(pack_h2(__uint_as_float(o[8 * i]) * inv, __uint_as_float(o[8 * i + 1]) * inv),
+                                pack_h2(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv),
+                                pack_h2(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv),
+                                pack_h2(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv));
+        }
+      }
+      tc_fence_before_sync();
+      rs.attn_bit ^= 1u;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------
 // LayerNorm stage.  Rows stream through shared memory in batches fetched by bulk copies (all
 // split-K planes plus the residual of a batch are in flight together, several batches deep), so
 // the stage is bound by memory bandwidth rather than by per-warp load latency.  A warp owns a
@@ -926,12 +1138,13 @@ __device__ __forceinline__ void ln_rows2(const float* pl0, const float* pl1, int
                                          const __half* res0, const __half* res1, const __half* bias,
                                          const __half* gamma, const __half* beta, float eps, __half* out0, __half* out1,
                                          int lane) {
-  const bool two = pl1 != nullptr;
+  const bool two = out1 != nullptr;
   float z[2][NJ][4];
 #pragma unroll
   for (int j = 0; j < NJ; ++j) {
-    const float4 a = *reinterpret_cast<const float4*>(pl0 + (lane + 32 * j) * 4);
-    const float4 b = two ? *reinterpret_cast<const float4*>(pl1 + (lane + 32 * j) * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 a = n_partial > 0 ? *reinterpret_cast<const float4*>(pl0 + (lane + 32 * j) * 4) : zero4;
+    const float4 b = (two && n_partial > 0) ? *reinterpret_cast<const float4*>(pl1 + (lane + 32 * j) * 4) : zero4;
     z[0][j][0] = a.x; z[0][j][1] = a.y; z[0][j][2] = a.z; z[0][j][3] = a.w;
     z[1][j][0] = b.x; z[1][j][1] = b.y; z[1][j][2] = b.z; z[1][j][3] = b.w;
   }
@@ -1023,7 +1236,7 @@ __device__ __forceinline__ void ln_rows2(const float* pl0, const float* pl1, int
   }
 }
 
-__device__ void ln_stage(const Stage& st, const MegaParams& p, SmemCtl& cs, uint32_t ring, uint8_t* ring_ptr,
+__device__ __noinline__ void ln_stage(const Stage& st, const MegaParams& p, SmemCtl& cs, uint32_t ring, uint8_t* ring_ptr,
                          RoleState& rs, const WaitCtl& ctl, int warp, int lane) {
   const int N = st.N, M = st.M, P = st.n_partial;
   const __half* resid = reinterpret_cast<const __half*>(sel_ptr(st.resid_sel, st.resid, p));
@@ -1081,7 +1294,7 @@ __device__ void ln_stage(const Stage& st, const MegaParams& p, SmemCtl& cs, uint
       const __half* ra = resid ? rbase + (size_t)r * N : nullptr;
       const __half* rb2 = (resid && two) ? rbase + (size_t)r2 * N : nullptr;
       __half* o0 = out + (size_t)(row0 + r) * N;
-      __half* o1 = out + (size_t)(row0 + r2) * N;
+      __half* o1 = two ? out + (size_t)(row0 + r2) * N : nullptr;
       switch (N >> 7) {
         case 1: ln_rows2<1>(pl0, pl1, P, rb * N, ra, rb2, bias, gamma, beta, st.eps, o0, o1, lane); break;
         case 2: ln_rows2<2>(pl0, pl1, P, rb * N, ra, rb2, bias, gamma, beta, st.eps, o0, o1, lane); break;
@@ -1175,6 +1388,8 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
     const Stage& st = cs.stage;
     if (st.type == STAGE_GEMM) {
       gemm_stage(st, ca, cs, ring, vec_s, stage_s, rs, ctl, warp, lane);
+    } else if (st.type == STAGE_ATTN_SWIN) {
+      attn_swin_stage(st, ca, cs, ring, ring_ptr, stage_s, rs, ctl, warp, lane);
     } else if (st.type == STAGE_ATTN) {
       if (st.seq <= 128) attn_stage_pp(st, ca, cs, ring, ring_ptr, stage_s, rs, ctl, warp, lane);
       else attn_stage(st, ca, cs, ring, ring_ptr, rs, ctl, warp, lane);

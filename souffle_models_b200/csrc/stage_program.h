@@ -14,12 +14,15 @@ enum StageType : int {
   STAGE_GEMM = 0,   // C = A . B with a fused epilogue
   STAGE_ATTN = 1,   // per (sequence, head, query tile): softmax(Q K^T * scale + mask) V
   STAGE_LN = 2,     // z = sum_p partial[p] + bias + resid ; y = LayerNorm(z)
+  STAGE_ATTN_SWIN = 3,  // per (window, head): softmax(Q K^T * scale + relative-position bias + shift mask) V
 };
 
 enum EpilogueKind : int {
   EPI_F16 = 0,      // out[row, col] = f16(act(acc + bias)) (+ resid)
   EPI_QKV = 1,      // like EPI_F16 but scattered head-split to [3][B][heads][S][d]
   EPI_PARTIAL = 2,  // raw fp32 accumulators to partial[split][row][col]
+  EPI_SWIN_QKV = 3, // rows (tokens) are rolled by -shift and scattered window-major: [3][windows][64][C]
+  EPI_SWIN_PROJ = 4,// rows arrive window-major, are rolled back to token order; + bias + residual[token]
 };
 
 enum Activation : int { ACT_NONE = 0, ACT_RELU = 1, ACT_GELU = 2 };
@@ -52,6 +55,8 @@ struct Stage {
   const int* lens;   // per-sequence valid length or null (selected at call time when lens_from_call)
   int lens_from_call;
   int tm_qkv;        // tensor map over the head-split buffer viewed as [3*B*heads*S][d], box 64 x 128
+  int win, shift;    // Swin: window size (7) and cyclic shift; `seq` is then the side of the token grid
+  const void* rel_bias;  // Swin: fp16 [(2*win-1)^2][heads] relative-position bias table
   void* probs;       // optional fp16 [B*heads][S][S] normalised probabilities (debug / parity output)
   // ---- layer norm ----
   const void* gamma; // fp16 [N] or null
