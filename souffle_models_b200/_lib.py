@@ -32,6 +32,16 @@ class BertLayerWeights(C.Structure):
                                           "fc1_b", "fc2_w", "fc2_b", "ln2_g", "ln2_b")]
 
 
+class SwinDesc(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("batch", "res", "dim", "heads", "window", "shift", "mlp_ratio")] + \
+               [("eps", C.c_float), ("timeout_ms", C.c_int32)]
+
+
+class SwinWeights(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("ln1_g", "ln1_b", "qkv_w", "qkv_b", "rel_bias", "proj_w", "proj_b", "ln2_g",
+                                          "ln2_b", "fc1_w", "fc1_b", "fc2_w", "fc2_b")]
+
+
 class LstmDesc(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("layers", "hidden", "steps", "ref_input_delay", "timeout_ms")]
 
@@ -63,6 +73,10 @@ SIGNATURES = {
     "souffle_layernorm_forward": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                             C.c_void_p, C.c_int32, C.c_int32, C.c_float, C.c_void_p, C.c_size_t,
                                             C.c_void_p]),
+    "souffle_swin_block_plan_create": (C.c_int, [C.POINTER(SwinDesc), C.POINTER(SwinWeights), C.POINTER(C.c_void_p)]),
+    "souffle_swin_block_plan_destroy": (C.c_int, [C.c_void_p]),
+    "souffle_swin_block_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "souffle_swin_block_plan_status": (C.c_int, [C.c_void_p]),
     "souffle_workspace_status": (C.c_int, [C.c_void_p, C.c_void_p]),
 }
 

@@ -110,7 +110,7 @@ __global__ void transpose_kn_to_nk(const __half* __restrict__ src, __half* __res
 struct TileChoice {
   int bm = 128, bn = 0, split = 1;
 };
-static TileChoice choose_tiles(int M, int N, int K, int sms, bool allow_split, bool b_mn, bool head_split = false) {
+static TileChoice choose_tiles(int M, int N, int K, int sms, bool allow_split, bool b_mn, int head_split = 0) {
   const int kch = K / 64;
   double best = 1e300;
   TileChoice bt;
@@ -121,7 +121,8 @@ static TileChoice choose_tiles(int M, int N, int K, int sms, bool allow_split, b
       const int bn = cands[ci];
       if (N % bn) continue;
       if (b_mn && bn % 64) continue;
-      if (head_split && bn != 16 && bn % 32) continue;   // 32-column epilogue chunks must not straddle a head
+      if (head_split == 1 && bn != 16 && bn % 32) continue;   // 32-column epilogue chunks must not straddle a head
+      if (head_split == 2 && bn % 32) continue;               // row-permuting epilogues have no 16-column path
       if (196608 / ((bm + bn) * 128) < 2) continue;
       for (int split = 1; split <= (allow_split ? 16 : 1); ++split) {
         if (kch % split) continue;
@@ -183,6 +184,7 @@ static int launch_mega(const CallArgs& args, int grid, cudaStream_t stream) {
 static int stage_items(const Stage& s) {
   if (s.type == STAGE_GEMM) return ((s.M + s.bm - 1) / s.bm) * (s.N / s.bn) * s.splitk;
   if (s.type == STAGE_ATTN) return s.batch * s.heads * ((s.seq + 127) / 128);
+  if (s.type == STAGE_ATTN_SWIN) return s.batch * (s.seq / s.win) * (s.seq / s.win) * s.heads;
   return (s.M + kThreads / 32 - 1) / (kThreads / 32);
 }
 
@@ -281,7 +283,7 @@ static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* la
   SF_CUDA(cudaMemset(p->d_status, 0, 64));
 
   // ---- tiling ----
-  TileChoice t_qkv = choose_tiles(M, 3 * H, H, sms, false, false, true), t_fc1 = choose_tiles(M, F, H, sms, false, false),
+  TileChoice t_qkv = choose_tiles(M, 3 * H, H, sms, false, false, 1), t_fc1 = choose_tiles(M, F, H, sms, false, false),
              t_proj = choose_tiles(M, H, H, sms, true, false), t_fc2 = choose_tiles(M, H, F, sms, true, false);
   if (d.bm_qkv) t_qkv.bm = d.bm_qkv;
   if (d.bn_qkv) t_qkv.bn = d.bn_qkv;
@@ -698,6 +700,196 @@ int souffle_layernorm_forward(const float* partial, int32_t n_partial, const voi
   const int sms = di->sms < di->max_ctas ? di->sms : di->max_ctas;
   const int items = stage_items(s);
   return launch_mega(args, items < sms ? items : sms, st);
+}
+
+// ======================================================================================
+// Swin block plan (shares the plan machinery of the encoder)
+// ======================================================================================
+struct SouffleSwinPlan {
+  SouffleBertPlan base;
+  SouffleSwinDesc desc;
+};
+
+static int launch_plan(SouffleBertPlan* plan, const void* x, void* y, const int32_t* lens, int timeout_ms, cudaStream_t st) {
+  CallArgs args;
+  memset(&args, 0, sizeof(args));
+  args.call_maps[0] = plan->x_map;
+  MegaParams& mp = args.p;
+  mp.stages = plan->d_stages;
+  mp.n_stages = (int)plan->stages.size();
+  mp.maps = plan->d_maps;
+  mp.n_maps = (int)plan->maps.size();
+  mp.x = x;
+  mp.y = y;
+  mp.lens = lens;
+  const unsigned par = plan->launch_id & 1u;
+  mp.sync = plan->d_sync + 2 * par;
+  mp.sync_next = plan->d_sync + 2 * (par ^ 1u);
+  mp.status = plan->d_status;
+  mp.timeout_ns = (unsigned long long)(timeout_ms > 0 ? timeout_ms : 2000) * 1000000ull;
+  int rc = launch_mega(args, plan->grid, st);
+  if (rc) return rc;
+  plan->launch_id++;
+  plan->launches = 1;
+  return SOUFFLE_OK;
+}
+
+static int finish_plan(SouffleBertPlan* p, int sms) {
+  int rc;
+  int max_items = 1;
+  for (const Stage& s : p->stages) {
+    const int it = stage_items(s);
+    if (it > max_items) max_items = it;
+  }
+  p->grid = max_items < sms ? max_items : sms;
+  if ((rc = plan_alloc(p, (void**)&p->d_stages, p->stages.size() * sizeof(Stage)))) return rc;
+  if ((rc = plan_alloc(p, (void**)&p->d_maps, p->maps.size() * sizeof(CUtensorMap)))) return rc;
+  SF_CUDA(cudaMemcpy(p->d_stages, p->stages.data(), p->stages.size() * sizeof(Stage), cudaMemcpyHostToDevice));
+  SF_CUDA(cudaMemcpy(p->d_maps, p->maps.data(), p->maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice));
+  SF_CUDA(cudaDeviceSynchronize());
+  return SOUFFLE_OK;
+}
+
+static int build_swin_plan(SouffleSwinPlan* sp, const SouffleSwinWeights& w) {
+  SouffleBertPlan* p = &sp->base;
+  const SouffleSwinDesc& d = sp->desc;
+  DeviceInfo* di = nullptr;
+  int rc = device_info(&di);
+  if (rc) return rc;
+  p->device = di->device;
+  const int sms = di->sms < di->max_ctas ? di->sms : di->max_ctas;
+  const int R = d.res, C = d.dim, Hh = d.heads, ws = d.window, F = C * d.mlp_ratio;
+  const int T = d.batch * R * R, nWt = d.batch * (R / ws) * (R / ws), Mw = nWt * 64;
+  __half *y1, *qkvw, *ctxw, *x1, *y2, *hid;
+  if ((rc = plan_alloc(p, (void**)&y1, (size_t)T * C * 2))) return rc;
+  if ((rc = plan_alloc(p, (void**)&qkvw, (size_t)3 * Mw * C * 2))) return rc;
+  if ((rc = plan_alloc(p, (void**)&ctxw, (size_t)Mw * C * 2))) return rc;
+  if ((rc = plan_alloc(p, (void**)&x1, (size_t)T * C * 2))) return rc;
+  if ((rc = plan_alloc(p, (void**)&y2, (size_t)T * C * 2))) return rc;
+  if ((rc = plan_alloc(p, (void**)&hid, (size_t)T * F * 2))) return rc;
+  if ((rc = plan_alloc(p, (void**)&p->d_sync, 64))) return rc;
+  if ((rc = plan_alloc(p, (void**)&p->d_status, 64))) return rc;
+  SF_CUDA(cudaMemset(p->d_sync, 0, 64));
+  SF_CUDA(cudaMemset(p->d_status, 0, 64));
+  SF_CUDA(cudaMemset(qkvw, 0, (size_t)3 * Mw * C * 2));     // padding slots stay zero for ever
+  SF_CUDA(cudaMemset(ctxw, 0, (size_t)Mw * C * 2));
+  // weights: repack [K][N] -> [N][K]
+  __half *wqkv_t, *wo_t, *w1_t, *w2_t;
+  if ((rc = plan_alloc(p, (void**)&wqkv_t, (size_t)3 * C * C * 2))) return rc;
+  if ((rc = plan_alloc(p, (void**)&wo_t, (size_t)C * C * 2))) return rc;
+  if ((rc = plan_alloc(p, (void**)&w1_t, (size_t)C * F * 2))) return rc;
+  if ((rc = plan_alloc(p, (void**)&w2_t, (size_t)F * C * 2))) return rc;
+  const dim3 tb(32, 8);
+  transpose_kn_to_nk<<<dim3(3 * C / 32, C / 32), tb>>>(reinterpret_cast<const __half*>(w.qkv_w), wqkv_t, C, 3 * C);
+  transpose_kn_to_nk<<<dim3(C / 32, C / 32), tb>>>(reinterpret_cast<const __half*>(w.proj_w), wo_t, C, C);
+  transpose_kn_to_nk<<<dim3(F / 32, C / 32), tb>>>(reinterpret_cast<const __half*>(w.fc1_w), w1_t, C, F);
+  transpose_kn_to_nk<<<dim3(C / 32, F / 32), tb>>>(reinterpret_cast<const __half*>(w.fc2_w), w2_t, F, C);
+  SF_CUDA(cudaGetLastError());
+  auto copy_vec = [&](const void* src, size_t n, const void** dst) -> int {
+    *dst = nullptr;
+    if (!src) return SOUFFLE_OK;
+    void* v;
+    int r2 = plan_alloc(p, &v, n * 2);
+    if (r2) return r2;
+    if (cudaMemcpy(v, src, n * 2, cudaMemcpyDeviceToDevice) != cudaSuccess) return fail(SOUFFLE_CUDA_ERROR, "copying a parameter vector failed");
+    *dst = v;
+    return SOUFFLE_OK;
+  };
+  const void *ln1_g, *ln1_b, *qkv_b, *relb, *proj_b, *ln2_g, *ln2_b, *fc1_b, *fc2_b;
+  const int tbl = (2 * ws - 1) * (2 * ws - 1);
+  if ((rc = copy_vec(w.ln1_g, C, &ln1_g)) || (rc = copy_vec(w.ln1_b, C, &ln1_b)) || (rc = copy_vec(w.qkv_b, 3 * C, &qkv_b)) ||
+      (rc = copy_vec(w.rel_bias, (size_t)tbl * Hh, &relb)) || (rc = copy_vec(w.proj_b, C, &proj_b)) ||
+      (rc = copy_vec(w.ln2_g, C, &ln2_g)) || (rc = copy_vec(w.ln2_b, C, &ln2_b)) || (rc = copy_vec(w.fc1_b, F, &fc1_b)) ||
+      (rc = copy_vec(w.fc2_b, C, &fc2_b)))
+    return rc;
+  if (!relb) return fail(SOUFFLE_BAD_POINTER, "rel_bias must be given");
+  if ((ln1_g == nullptr) != (ln1_b == nullptr) || (ln2_g == nullptr) != (ln2_b == nullptr))
+    return fail(SOUFFLE_BAD_ARGUMENT, "gamma and beta must be given together");
+
+  const TileChoice t_qkv = choose_tiles(T, 3 * C, C, sms, false, false, 2), t_proj = choose_tiles(Mw, C, C, sms, false, false, 2),
+                   t_fc1 = choose_tiles(T, F, C, sms, false, false, 0), t_fc2 = choose_tiles(T, C, F, sms, false, false, 0);
+  int m_y1, m_ctx, m_y2, m_hid, m_qkv, m_wqkv, m_wo, m_w1, m_w2;
+  if ((rc = add_map(p, y1, T, C, t_qkv.bm, &m_y1)) || (rc = add_map(p, ctxw, Mw, C, t_proj.bm, &m_ctx)) ||
+      (rc = add_map(p, y2, T, C, t_fc1.bm, &m_y2)) || (rc = add_map(p, hid, T, F, t_fc2.bm, &m_hid)) ||
+      (rc = add_map(p, qkvw, (uint64_t)3 * Mw, C, 128, &m_qkv)) || (rc = add_map(p, wqkv_t, 3 * C, C, t_qkv.bn, &m_wqkv)) ||
+      (rc = add_map(p, wo_t, C, C, t_proj.bn, &m_wo)) || (rc = add_map(p, w1_t, F, C, t_fc1.bn, &m_w1)) ||
+      (rc = add_map(p, w2_t, C, F, t_fc2.bn, &m_w2)))
+    return rc;
+
+  Stage s = blank_stage(STAGE_LN);                       // LN1(x)
+  s.M = T; s.N = C; s.ldo = C; s.n_partial = 0; s.resid_sel = PTR_CALL_X; s.out = y1; s.gamma = ln1_g; s.beta = ln1_b; s.eps = d.eps;
+  p->stages.push_back(s);
+  s = blank_stage(STAGE_GEMM);                           // QKV, rolled and scattered window-major
+  s.tm_a = m_y1; s.tm_b = m_wqkv; s.M = T; s.N = 3 * C; s.K = C; s.bm = t_qkv.bm; s.bn = t_qkv.bn; s.epi = EPI_SWIN_QKV;
+  s.bias = qkv_b; s.out = qkvw; s.ldo = C; s.batch = d.batch; s.heads = Hh; s.head_dim = 32; s.seq = R; s.win = ws; s.shift = d.shift;
+  p->stages.push_back(s);
+  s = blank_stage(STAGE_ATTN_SWIN);                      // window attention
+  s.tm_qkv = m_qkv; s.batch = d.batch; s.heads = Hh; s.head_dim = 32; s.seq = R; s.win = ws; s.shift = d.shift; s.ldo = C;
+  s.scale = 1.0f / sqrtf(32.0f); s.rel_bias = relb; s.out = ctxw;
+  p->stages.push_back(s);
+  s = blank_stage(STAGE_GEMM);                           // proj, window reverse, roll back, + x
+  s.tm_a = m_ctx; s.tm_b = m_wo; s.M = Mw; s.N = C; s.K = C; s.bm = t_proj.bm; s.bn = t_proj.bn; s.epi = EPI_SWIN_PROJ;
+  s.bias = proj_b; s.resid_sel = PTR_CALL_X; s.out = x1; s.ldo = C; s.batch = d.batch; s.heads = Hh; s.head_dim = 32; s.seq = R;
+  s.win = ws; s.shift = d.shift;
+  p->stages.push_back(s);
+  s = blank_stage(STAGE_LN);                             // LN2(x1)
+  s.M = T; s.N = C; s.ldo = C; s.n_partial = 0; s.resid = x1; s.out = y2; s.gamma = ln2_g; s.beta = ln2_b; s.eps = d.eps;
+  p->stages.push_back(s);
+  s = blank_stage(STAGE_GEMM);                           // FC1 + GELU
+  s.tm_a = m_y2; s.tm_b = m_w1; s.M = T; s.N = F; s.K = C; s.bm = t_fc1.bm; s.bn = t_fc1.bn; s.epi = EPI_F16; s.act = ACT_GELU;
+  s.bias = fc1_b; s.out = hid; s.ldo = F;
+  p->stages.push_back(s);
+  s = blank_stage(STAGE_GEMM);                           // FC2 + x1
+  s.tm_a = m_hid; s.tm_b = m_w2; s.M = T; s.N = C; s.K = F; s.bm = t_fc2.bm; s.bn = t_fc2.bn; s.epi = EPI_F16; s.bias = fc2_b;
+  s.resid = x1; s.out_sel = PTR_CALL_Y; s.ldo = C;
+  p->stages.push_back(s);
+  return finish_plan(p, sms);
+}
+
+int souffle_swin_block_plan_create(const SouffleSwinDesc* desc, const SouffleSwinWeights* weights, SouffleSwinPlan** plan_out) {
+  if (!desc || !weights || !plan_out) return fail(SOUFFLE_BAD_ARGUMENT, "null argument");
+  *plan_out = nullptr;
+  const SouffleSwinDesc& d = *desc;
+  if (d.batch < 1 || d.res < 1) return fail(SOUFFLE_BAD_SHAPE, "batch and res must be >= 1");
+  if (d.window != 7 && d.window != 8) return fail(SOUFFLE_BAD_SHAPE, "window must be 7 or 8 (got %d)", d.window);
+  if (d.res % d.window) return fail(SOUFFLE_BAD_SHAPE, "res %d is not a multiple of the window %d", d.res, d.window);
+  if (d.shift < 0 || d.shift >= d.window) return fail(SOUFFLE_BAD_SHAPE, "shift must be in [0, window)");
+  if (d.dim != 128 && d.dim != 256 && d.dim != 512 && d.dim != 768 && d.dim != 1024)
+    return fail(SOUFFLE_BAD_SHAPE, "dim %d must be 128, 256, 512, 768 or 1024", d.dim);
+  if (d.heads < 2 || d.heads % 2 || d.heads * 32 != d.dim) return fail(SOUFFLE_BAD_SHAPE, "heads must be even with dim / heads == 32");
+  if (d.mlp_ratio < 1 || d.dim * d.mlp_ratio > 4096) return fail(SOUFFLE_BAD_SHAPE, "dim * mlp_ratio must be in (0, 4096]");
+  if (!aligned16(weights->qkv_w) || !aligned16(weights->proj_w) || !aligned16(weights->fc1_w) || !aligned16(weights->fc2_w))
+    return fail(SOUFFLE_BAD_POINTER, "weight matrices must be non-null and 16-byte aligned");
+  SouffleSwinPlan* sp = new SouffleSwinPlan();
+  sp->desc = d;
+  int rc = build_swin_plan(sp, *weights);
+  if (rc) {
+    const std::string keep = g_last_error;
+    souffle_swin_block_plan_destroy(sp);
+    g_last_error = keep;
+    return rc;
+  }
+  *plan_out = sp;
+  return SOUFFLE_OK;
+}
+
+int souffle_swin_block_plan_destroy(SouffleSwinPlan* sp) {
+  if (!sp) return SOUFFLE_OK;
+  cudaDeviceSynchronize();
+  for (void* a : sp->base.allocs) cudaFree(a);
+  delete sp;
+  return SOUFFLE_OK;
+}
+
+int souffle_swin_block_forward(SouffleSwinPlan* sp, const void* x, void* y, souffle_stream_t stream) {
+  if (!sp) return fail(SOUFFLE_BAD_ARGUMENT, "null plan");
+  if (!aligned16(x) || !aligned16(y)) return fail(SOUFFLE_BAD_POINTER, "x and y must be non-null and 16-byte aligned");
+  return launch_plan(&sp->base, x, y, nullptr, sp->desc.timeout_ms, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int souffle_swin_block_plan_status(SouffleSwinPlan* sp) {
+  if (!sp) return fail(SOUFFLE_BAD_ARGUMENT, "null plan");
+  return souffle_bert_plan_status(&sp->base);
 }
 
 // ======================================================================================

@@ -122,3 +122,49 @@ def layernorm(partial: torch.Tensor, resid=None, bias=None, gamma=None, beta=Non
     if check:
         _lib.check(lib.souffle_workspace_status(ws.data_ptr(), _stream_ptr()))
     return out
+
+
+class SwinBlock:
+    """Plan for one Swin block (see SouffleSwinDesc in the header): weights dict with the keys of
+    oracle.souffle_oracle.make_swin_params, fp16 CUDA tensors, matrices [K][N]."""
+
+    KEYS = ("ln1_g", "ln1_b", "qkv_w", "qkv_b", "rel_bias", "proj_w", "proj_b", "ln2_g", "ln2_b", "fc1_w", "fc1_b",
+            "fc2_w", "fc2_b")
+
+    def __init__(self, batch: int, res: int, dim: int, heads: int, window: int, shift: int, params, mlp_ratio: int = 4,
+                 eps: float = 1e-5):
+        lib = _lib.load()
+        self.batch, self.res, self.dim = batch, res, dim
+        d = _lib.SwinDesc(batch=batch, res=res, dim=dim, heads=heads, window=window, shift=shift, mlp_ratio=mlp_ratio, eps=eps)
+        w = _lib.SwinWeights()
+        for k in self.KEYS:
+            t = params.get(k)
+            if t is not None:
+                _check_f16_cuda(t, k)
+            setattr(w, k, t.data_ptr() if t is not None else None)
+        self._h = C.c_void_p()
+        _lib.check(lib.souffle_swin_block_plan_create(C.byref(d), C.byref(w), C.byref(self._h)))
+        self._lib = lib
+
+    def close(self) -> None:
+        if getattr(self, "_h", None) is not None and self._h.value:
+            self._lib.souffle_swin_block_plan_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """x: fp16 CUDA [batch*res*res, dim]; asynchronous."""
+        _check_f16_cuda(x, "x")
+        if x.numel() != self.batch * self.res * self.res * self.dim:
+            raise ValueError("x has the wrong number of elements for this plan")
+        y = torch.empty_like(x)
+        _lib.check(self._lib.souffle_swin_block_forward(self._h, x.data_ptr(), y.data_ptr(), _stream_ptr()))
+        return y
+
+    def status(self) -> None:
+        _lib.check(self._lib.souffle_swin_block_plan_status(self._h))

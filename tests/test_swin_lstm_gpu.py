@@ -86,3 +86,33 @@ def test_layernorm_entry_point(P, M, N):
     out = swin.layernorm(part.cuda(), resid.cuda(), bias.cuda(), gamma.cuda(), beta.cuda(), eps=1e-12)
     want = so.layer_norm(part.sum(0) + bias.float() + resid.float(), gamma, beta, 1e-12)
     assert (out.float().cpu() - want).abs().max() < 5e-3
+
+
+@pytest.mark.parametrize("shift", [0, 3])
+def test_swin_block_matches_oracle(shift):
+    """Benchmark config 4: 14x14 tokens, C=512, 16 heads x 32, window 7, shifted pair, bias table, GELU MLP."""
+    from souffle_models_b200 import swin
+    cfg = so.SwinConfig()
+    p = so.make_swin_params(cfg, 1238 + shift, zero_bias=False)
+    x = _rand((196, 512), 11 + shift)
+    blk = swin.SwinBlock(1, 14, 512, 16, 7, shift, {k: v.cuda() for k, v in p.items()})
+    y = blk.forward(x.cuda())
+    blk.status()
+    want = so.swin_block(cfg, x, p, shift)
+    err = (y.float().cpu() - want).abs()
+    assert err.max() < 2e-2 and err.pow(2).mean().sqrt() < 3e-3
+    y2 = blk.forward(x.cuda())
+    blk.status()
+    assert torch.equal(y, y2)
+
+
+def test_swin_block_batch2_window8():
+    from souffle_models_b200 import swin
+    cfg = so.SwinConfig(res=16, dim=256, heads=8, window=8)
+    p = so.make_swin_params(cfg, 77, zero_bias=False)
+    x = _rand((2 * 256, 256), 5)
+    blk = swin.SwinBlock(2, 16, 256, 8, 8, 4, {k: v.cuda() for k, v in p.items()})
+    y = blk.forward(x.cuda())
+    blk.status()
+    want = torch.cat([so.swin_block(cfg, x[:256], p, 4), so.swin_block(cfg, x[256:], p, 4)])
+    assert (y.float().cpu() - want).abs().max() < 2e-2
