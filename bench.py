@@ -260,13 +260,39 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     print(json.dumps(out))
 
 
+def profile_case(batch: int, n_layers: int) -> None:
+    """Eight forward calls of one plan, nothing else: the target of `ncu -k regex:souffle_megakernel -s 4 -c 1`."""
+    from oracle import souffle_oracle as so
+    from souffle_models_b200 import bert
+    cfg = so.BertConfig(batch, SEQ, HEADS, HEAD_DIM, FFN, "std")
+    layers = [{k: v.cuda() for k, v in w.items()} for w in so.make_bert_weights(cfg, SEED, n_layers)]
+    x, lens = so.make_bert_input(cfg, SEED, ragged=batch > 1)
+    enc = bert.BertEncoder(batch, SEQ, HEADS, HEAD_DIM, FFN, layers)
+    xs, ls = x.cuda(), (lens.cuda() if lens is not None else None)
+    y = torch.empty_like(xs)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for i in range(8):
+        if i == 3:
+            e0.record()
+        enc.forward(xs, ls, y)
+    e1.record()
+    e1.synchronize()
+    enc.status()
+    print(f"batch {batch}, {n_layers} layers: {e0.elapsed_time(e1) * 1000 / 5:.1f} us per call")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--profile-case", nargs=2, type=int, metavar=("BATCH", "LAYERS"), default=None,
+                    help="build a plan for BATCH sequences x LAYERS layers and call forward 8 times (for ncu captures)")
     args = ap.parse_args()
+    if args.profile_case:
+        profile_case(*args.profile_case)
+        return
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -130,7 +130,8 @@ int souffle_bert_plan_copy_buffer(SouffleBertPlan* plan, int which, void* dst, s
 /* Synchronises the plan's device and reports the device-side status of the last launch:
  * SOUFFLE_OK, or SOUFFLE_DEVICE_TIMEOUT with the stage/CTA in souffle_last_error(). */
 int souffle_bert_plan_status(SouffleBertPlan* plan);
-/* Per-stage stamps of the last launch (desc.profile=1): out[stage][cta][8] int64 SM-clock values
+/* Per-stage stamps of the last launch (desc.profile=1): out[n_stages + 1][cta][8] int64 SM-clock values (the last
+ * record holds {kernel entry, prologue done, last stage done}); for the stages
  * {stage start, this CTA's work done, barrier left} and, for GEMM stages, cycle totals {MMA issuer waiting
  * for operands, MMA issuer waiting for a free accumulator, producer waiting for a free ring slot, epilogue
  * waiting for an accumulator, epilogue busy}; differences within one CTA are cycles.

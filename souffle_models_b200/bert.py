@@ -109,7 +109,7 @@ class BertEncoder:
         """[stages, grid, 8] int64 SM-clock stamps / role cycle totals of the last launch
         (needs tuning={'profile': 1}; layout in include/souffle_b200.h)."""
         i = self.info()
-        out = torch.zeros(i["stages"], i["grid"], 8, dtype=torch.int64)
+        out = torch.zeros(i["stages"] + 1, i["grid"], 8, dtype=torch.int64)    # last record: kernel entry/prologue/exit
         _lib.check(self._lib.souffle_bert_plan_read_profile(self._h, out.data_ptr(), out.numel()))
         return out
 
@@ -162,3 +162,20 @@ def souffle_bert_layer(src: torch.Tensor, qkv_weight: torch.Tensor, attn_fc_weig
     enc.status()
     return [enc.buffer("qkv").reshape(3 * B, heads, S, 64), enc.buffer("probs"), enc.buffer("ctx"),
             enc.buffer("ln1"), enc.buffer("fc1"), out]
+
+
+def souffle_bert_base() -> int:
+    """Drop-in for souffle_bert_base.souffle_bert_base() (cpp/bert/bert_base_impl.cu:277-308): a 12-layer
+    BERT-base encoder at batch 1, sequence 384 with zero-filled parameters and input (the reference reads no
+    files either, :280-283), run as one launch.  Returns 0 like the reference."""
+    cfg = dict(batch=1, seq=384, heads=12, head_dim=64, ffn=3072)
+    H, F = 768, 3072
+    z = lambda *s: torch.zeros(*s, dtype=torch.float16, device="cuda")
+    layer = dict(qkv_w=z(3, H, H), qkv_b=z(3, H), proj_w=z(H, H), proj_b=z(H), ln1_g=z(H) + 1, ln1_b=z(H),
+                 fc1_w=z(H, F), fc1_b=z(F), fc2_w=z(F, H), fc2_b=z(H), ln2_g=z(H) + 1, ln2_b=z(H))
+    enc = BertEncoder(cfg["batch"], cfg["seq"], cfg["heads"], cfg["head_dim"], cfg["ffn"], [layer] * 12, variant=STD,
+                      eps=1e-6)
+    enc.forward(z(1, 384, H))
+    enc.status()
+    enc.close()
+    return 0

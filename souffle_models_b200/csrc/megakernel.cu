@@ -86,6 +86,7 @@ struct __align__(8) SmemCtl {
   uint64_t ln_full[4];
   uint32_t tmem_base;
   int abort;
+  unsigned long long deadline_ns;   // read from the global timer once per CTA
   Stage stage;        // current stage, copied once per stage
 };
 static_assert(sizeof(SmemCtl) <= kCtlBytes, "control block too large");
@@ -1327,6 +1328,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 souffle_megakernel(const __grid_constant__ CallArgs ca) {
   const MegaParams& p = ca.p;
   extern __shared__ uint8_t smem_raw[];
+  const long long t_entry = clock64();
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t pad = ((raw + 1023u) & ~1023u) - raw;      // 1024-byte alignment for swizzled tiles
   SmemCtl& cs = *reinterpret_cast<SmemCtl*>(smem_raw + pad);
@@ -1355,6 +1357,7 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
     for (int i = 0; i < 7; ++i) mbar_init(smem_u32(&cs.attn1[i]), i == 5 ? 128 : 1);
     for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&cs.ln_full[i]), 1);
     cs.abort = 0;
+    cs.deadline_ns = globaltimer_ns() + p.timeout_ns;
     fence_mbar_init();
     if (blockIdx.x == 0) {          // the other launch parity's barrier words start clean
       p.sync_next[0] = 0u;
@@ -1372,7 +1375,12 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
   WaitCtl ctl;
   ctl.abort_smem = &cs.abort;
   ctl.status_g = p.status;
-  ctl.deadline_ns = globaltimer_ns() + p.timeout_ns;
+  ctl.deadline_ns = cs.deadline_ns;
+  if (p.prof && threadIdx.x == 0) {          // one record past the stages: kernel entry, prologue done, ...
+    long long* pr = p.prof + ((size_t)p.n_stages * gridDim.x + blockIdx.x) * 8;
+    pr[0] = t_entry;
+    pr[1] = clock64();
+  }
 
   RoleState rs;
   for (int si = 0; si < p.n_stages; ++si) {
@@ -1407,6 +1415,7 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
   }
 
   __syncthreads();
+  if (p.prof && threadIdx.x == 0) p.prof[((size_t)p.n_stages * gridDim.x + blockIdx.x) * 8 + 2] = clock64();
   if (cs.abort) {
     // let copies that were already issued land before the CTA's shared memory is released
     const unsigned long long t0 = globaltimer_ns();

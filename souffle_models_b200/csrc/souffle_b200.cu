@@ -11,6 +11,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -176,6 +177,11 @@ static int device_info(DeviceInfo** out) {
 
 static int launch_mega(const CallArgs& args, int grid, cudaStream_t stream) {
   void* kargs[] = {const_cast<CallArgs*>(&args)};
+  static const bool plain = getenv("SOUFFLE_PLAIN_LAUNCH") != nullptr;     // experiment: non-cooperative launch
+  if (plain) {
+    SF_CUDA(cudaLaunchKernel((const void*)souffle_megakernel, dim3(grid), dim3(kThreads), kargs, (size_t)kSmemBytes, stream));
+    return SOUFFLE_OK;
+  }
   SF_CUDA(cudaLaunchCooperativeKernel((const void*)souffle_megakernel, dim3(grid), dim3(kThreads), kargs,
                                       (size_t)kSmemBytes, stream));
   return SOUFFLE_OK;
@@ -423,7 +429,7 @@ static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* la
   p->grid = max_items < sms ? max_items : sms;
 
   if (d.profile) {
-    const size_t pb = p->stages.size() * (size_t)p->grid * 8 * sizeof(long long);
+    const size_t pb = (p->stages.size() + 1) * (size_t)p->grid * 8 * sizeof(long long);
     if ((rc = plan_alloc(p, (void**)&p->d_prof, pb))) return rc;
     SF_CUDA(cudaMemset(p->d_prof, 0, pb));
   }
@@ -588,7 +594,7 @@ int souffle_bert_plan_status(SouffleBertPlan* plan) {
 int souffle_bert_plan_read_profile(SouffleBertPlan* plan, int64_t* out, size_t capacity_elems) {
   if (!plan || !out) return fail(SOUFFLE_BAD_ARGUMENT, "null argument");
   if (!plan->d_prof) return fail(SOUFFLE_BAD_ARGUMENT, "the plan was created without desc.profile");
-  const size_t n = plan->stages.size() * (size_t)plan->grid * 8;
+  const size_t n = (plan->stages.size() + 1) * (size_t)plan->grid * 8;
   if (capacity_elems < n) return fail(SOUFFLE_BAD_ARGUMENT, "profile needs %zu elements, got %zu", n, capacity_elems);
   SF_CUDA(cudaDeviceSynchronize());
   SF_CUDA(cudaMemcpy(out, plan->d_prof, n * sizeof(long long), cudaMemcpyDeviceToHost));
