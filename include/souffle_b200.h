@@ -130,16 +130,23 @@ int souffle_bert_plan_copy_buffer(SouffleBertPlan* plan, int which, void* dst, s
 /* Synchronises the plan's device and reports the device-side status of the last launch:
  * SOUFFLE_OK, or SOUFFLE_DEVICE_TIMEOUT with the stage/CTA in souffle_last_error(). */
 int souffle_bert_plan_status(SouffleBertPlan* plan);
-/* Per-stage stamps of the last launch (desc.profile=1): out[n_stages + 1][cta][8] int64 SM-clock values (the last
+/* Per-stage stamps of the last launch (desc.profile=1): out[n_stages + 1][cta][16] int64 SM-clock values (the last
  * record holds {kernel entry, prologue done, last stage done}); for the stages
  * {stage start, this CTA's work done, barrier left} and, for GEMM stages, cycle totals {MMA issuer waiting
  * for operands, MMA issuer waiting for a free accumulator, producer waiting for a free ring slot, epilogue
- * waiting for an accumulator, epilogue busy}; differences within one CTA are cycles.
+ * waiting for an accumulator, epilogue busy} and, in words 8..15 of a GEMM record, the first epilogue warp's cycles in
+ * {TMEM loads, arithmetic, stores} and the stamps {first operand copy issued, first operand chunk landed, last
+ * accumulator committed, first accumulator seen by the epilogue, epilogue finished}; differences within one CTA
+ * are cycles.
  * The in-kernel counterpart of the reference's profile_grid_clock buffers
  * (cpp/bert/kernels/fused_sqq_bert.cu:2330,2770; cpp/bert/bert_binding.cu:67-76).  Synchronises. */
 int souffle_bert_plan_read_profile(SouffleBertPlan* plan, int64_t* out, size_t capacity_elems);
 /* Number of kernels launched by the last forward call and the persistent grid size. */
 int souffle_bert_plan_info(SouffleBertPlan* plan, int* launches_out, int* grid_out, int* n_stages_out);
+/* The tiling chosen for stage `index` of the program: out[0..5] = {stage type (0 GEMM, 1 attention, 2 LayerNorm),
+ * tile rows, tile columns, split-K factor, work items, ring slots}.  The reference fixes these at compile time
+ * (cpp/bert/kernels/bert.h:18-52); here they depend on the shape and on the SM count. */
+int souffle_bert_plan_stage_info(SouffleBertPlan* plan, int index, int out[6]);
 
 /* ------------------------------------------------------------------------------------------
  * Stacked LSTM, batch 1, as one wavefront launch.  Replaces fused_lstm<1,10,256,100>

@@ -105,11 +105,17 @@ class BertEncoder:
         _lib.check(self._lib.souffle_bert_plan_info(self._h, C.byref(a), C.byref(b), C.byref(c)))
         return dict(launches=a.value, grid=b.value, stages=c.value)
 
+    def stage_info(self, index: int) -> Dict[str, int]:
+        """Tiling of stage `index`: type (0 GEMM, 1 attention, 2 LayerNorm), tile rows/columns, split-K, items, ring slots."""
+        out = (C.c_int * 6)()
+        _lib.check(self._lib.souffle_bert_plan_stage_info(self._h, index, out))
+        return dict(type=out[0], bm=out[1], bn=out[2], splitk=out[3], items=out[4], slots=out[5])
+
     def read_profile(self) -> torch.Tensor:
-        """[stages, grid, 8] int64 SM-clock stamps / role cycle totals of the last launch
+        """[stages + 1, grid, 16] int64 SM-clock stamps / role cycle totals of the last launch
         (needs tuning={'profile': 1}; layout in include/souffle_b200.h)."""
         i = self.info()
-        out = torch.zeros(i["stages"] + 1, i["grid"], 8, dtype=torch.int64)    # last record: kernel entry/prologue/exit
+        out = torch.zeros(i["stages"] + 1, i["grid"], 16, dtype=torch.int64)    # last record: kernel entry/prologue/exit
         _lib.check(self._lib.souffle_bert_plan_read_profile(self._h, out.data_ptr(), out.numel()))
         return out
 

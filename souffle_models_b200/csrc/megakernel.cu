@@ -110,19 +110,18 @@ __device__ __forceinline__ const void* sel_ptr(int sel, const void* plan, const 
 // grid barrier: one monotonic arrival counter per launch, bounded spin
 // ------------------------------------------------------------------------------------
 __device__ bool grid_barrier(const MegaParams& p, const WaitCtl& ctl, int where) {
-  // Every thread orders its generic-proxy writes before async-proxy reads; the CTA barrier then orders all
-  // of them before thread 0, whose gpu-scope release (cumulative) publishes them to the other CTAs.
-  fence_proxy_async();
+  // The CTA barrier orders every thread's global writes before thread 0, whose gpu-scope release is
+  // cumulative and publishes them to the other CTAs.  On the way out thread 0's acquire, the second CTA
+  // barrier and a proxy fence order the other CTAs' writes before this CTA's TMA and bulk-copy reads.
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence();
-    if (p.prof) p.prof[((size_t)where * gridDim.x + blockIdx.x) * 8 + 1] = clock64();
+    if (p.prof) p.prof[((size_t)where * gridDim.x + blockIdx.x) * kProfSlots + 1] = clock64();
     // The counter only grows during a launch: barrier number `where` is passed once every CTA
     // has added 1 for it.  (The launch that runs next clears the other counter, see the prologue.)
     unsigned* count = p.sync;
     const unsigned target = (unsigned)(where + 1) * gridDim.x;
     const bool skip = p.skip_arrival > 0 && where == 0 && (int)blockIdx.x == p.skip_arrival - 1;
-    if (skip) *ctl.abort_smem = 1; else atom_add_release_u32(count, 1u);
+    if (skip) *ctl.abort_smem = 1; else red_add_release_u32(count, 1u);
     uint32_t spins = 0;
     while (!skip && ld_acquire_u32(count) < target) {
       if (((++spins) & 0x3F) == 0) {
@@ -142,36 +141,46 @@ __device__ bool grid_barrier(const MegaParams& p, const WaitCtl& ctl, int where)
 // ------------------------------------------------------------------------------------
 // GEMM stage
 // ------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t fast_div(uint32_t n, uint32_t d, uint32_t mg) {
+  return d == 1u ? n : __umulhi(n, mg);
+}
+
 struct GemmGeom {
   int tiles_n, splitk, items, kchunks, bn, bm, nh, slot_bytes, nslots;
 };
-__device__ __forceinline__ GemmGeom gemm_geom(const Stage& st, int max_slots) {
+__device__ __forceinline__ GemmGeom gemm_geom(const Stage& st) {
   GemmGeom g;
   g.bn = st.bn;
-  g.bm = st.bm == 256 ? 256 : 128;
-  g.nh = g.bm / 128;                       // 128-row halves per tile, each with its own accumulator
-  g.tiles_n = st.N / st.bn;
+  g.bm = st.bm;
+  g.nh = st.bm >> 7;                       // 128-row halves per tile, each with its own accumulator
+  g.tiles_n = st.tiles_n;
   g.splitk = st.splitk;
-  g.items = ((st.M + g.bm - 1) / g.bm) * g.tiles_n * g.splitk;
-  g.kchunks = st.K / 64 / st.splitk;
-  g.slot_bytes = g.nh * kATileBytes + st.bn * 128;
-  int n = kRingBytes / g.slot_bytes;
-  g.nslots = n > kMaxSlots ? kMaxSlots : n;
-  if (max_slots > 0 && g.nslots > max_slots) g.nslots = max_slots;
+  g.items = st.items;
+  g.kchunks = st.kchunks;
+  g.slot_bytes = st.slot_bytes;
+  g.nslots = st.nslots;
   return g;
+}
+// work item -> (m tile, n tile, k split)
+__device__ __forceinline__ void gemm_item(const Stage& st, int item, int& mt, int& nt, int& ks) {
+  const uint32_t q = fast_div((uint32_t)item, (uint32_t)st.splitk, st.mg_splitk);
+  ks = item - (int)q * st.splitk;
+  const uint32_t m = fast_div(q, (uint32_t)st.tiles_n, st.mg_tiles_n);
+  nt = (int)q - (int)m * st.tiles_n;
+  mt = (int)m;
 }
 
 // Epilogue parameters of a stage, copied into registers once (the stage record itself lives in
 // shared memory and would otherwise be re-read around every asm statement).
 struct EpiCtx {
-  int epi, act, M, N, ldo, heads, head_dim, seq, win, shift;
-  size_t head_plane;       // seq * head_dim
-  size_t qkv_plane;        // batch * heads * seq * head_dim
+  int epi, act, M, N, ldo;
   const __half* bias_s;    // bias staged in shared memory, or null
   const __half* resid;
   __half* out;
   float* partial;
+  bool prof;
 };
+constexpr uint32_t kNoRow = 0xFFFFFFFFu;      // "this row is outside the matrix"
 
 // A thread that owns one row of a 32-row block holds 64 bytes of that row.  Written straight to global
 // memory, one store instruction would touch 32 different lines with 16 bytes each.  Going through the
@@ -215,19 +224,63 @@ __device__ __forceinline__ int swin_slot_to_token(int slot, int R, int win, int 
   return img * R * R + ty * R + tx;
 }
 
-// One 32-column chunk of the accumulator block: r[i] = column col+i of this thread's row `row`.
-// `trow[i]` = global row index of row (8*i + lane/4) of the same 32-row block (for the staged stores).
-__device__ __forceinline__ void epilogue_chunk32(const EpiCtx& e, uint8_t* sbuf, const uint32_t (&r)[32], int row,
-                                                 const int (&trow)[4], int col, int ks, int lane) {
-  uint8_t* rowptr[4];
+// Output addressing is split into a row part, computed once per tile, and a column part, computed once
+// per chunk; both are element offsets that fit 32 bits (the host rejects larger buffers).
+// Row part: offset of matrix row `row` in the stage's output (kNoRow past the end).  The residual, where a
+// stage has one, is laid out like the output, so the same offset addresses it.
+template <bool kSwin>
+__device__ __forceinline__ uint32_t epi_row_offset(const Stage& st, const EpiCtx& e, int row, int ks) {
+  if (row >= e.M) return kNoRow;
+  if (e.epi == EPI_PARTIAL) return (uint32_t)(ks * e.M + row) * (uint32_t)e.N;
+  if (e.epi == EPI_QKV) {
+    // [3][B][heads][S][d]: row -> (sequence, token)
+    const uint32_t b = fast_div((uint32_t)row, (uint32_t)st.seq, st.mg_seq), sq = (uint32_t)row - b * (uint32_t)st.seq;
+    return (b * (uint32_t)(st.heads * st.seq) + sq) * (uint32_t)st.head_dim;
+  }
+  if constexpr (kSwin) {
+    if (e.epi == EPI_SWIN_QKV) return (uint32_t)swin_token_to_slot(row, st.seq, st.win, st.shift) * (uint32_t)e.ldo;
+    if (e.epi == EPI_SWIN_PROJ) {
+      const int t = swin_slot_to_token(row, st.seq, st.win, st.shift, e.M >> 6);
+      return t >= 0 ? (uint32_t)t * (uint32_t)e.ldo : kNoRow;
+    }
+  }
+  return (uint32_t)row * (uint32_t)e.ldo;
+}
+// Column part: offset of column `col` (a multiple of 16; a chunk never straddles a head or a q/k/v plane).
+template <bool kSwin>
+__device__ __forceinline__ uint32_t epi_col_offset(const Stage& st, const EpiCtx& e, int col) {
+  if (e.epi == EPI_QKV) {
+    const uint32_t g = fast_div((uint32_t)col, (uint32_t)st.head_dim, st.mg_head_dim), dd = (uint32_t)col - g * (uint32_t)st.head_dim;
+    const uint32_t which = fast_div(g, (uint32_t)st.heads, st.mg_heads), hh = g - which * (uint32_t)st.heads;
+    const uint32_t head_plane = (uint32_t)(st.seq * st.head_dim);
+    return (which * (uint32_t)(st.batch * st.heads) + hh) * head_plane + dd;
+  }
+  if constexpr (kSwin) {
+    if (e.epi == EPI_SWIN_QKV) {
+      // [3][windows][64][C]: the column picks q/k/v and the channel
+      const int which = col / e.ldo, ch = col - which * e.ldo;
+      const uint32_t plane = (uint32_t)((e.M + st.seq * st.seq - 1) / (st.seq * st.seq)) * (uint32_t)((st.seq / st.win) * (st.seq / st.win) * 64) * (uint32_t)e.ldo;
+      return (uint32_t)which * plane + (uint32_t)ch;
+    }
+  }
+  return (uint32_t)col;
+}
+
+// One 32-column chunk of the accumulator block: r[i] = column col+i of this thread's own row, whose output
+// offset is `own`; `so[i]` = output offset of row (8*i + lane/4) of the same 32-row block (staged stores).
+template <bool kSwin>
+__device__ __forceinline__ void epilogue_chunk32(const Stage& st, const EpiCtx& e, uint8_t* sbuf, const uint32_t (&r)[32],
+                                                 uint32_t own, const uint32_t (&so)[4], int col, int lane, unsigned& t_mid) {
   if (e.epi == EPI_PARTIAL) {
-    // fp32 planes: two halves of 16 columns = 64 bytes per row each
+    // fp32 planes: two halves of 16 columns = 64 bytes per row each.  (Storing each thread's own 128-byte
+    // row segment directly measured twice as slow: an instruction's cost grows with the lines it touches.)
+    if (e.prof) t_mid = (unsigned)clock64();
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
+      uint8_t* rowptr[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i)
-        rowptr[i] = trow[i] < e.M ? reinterpret_cast<uint8_t*>(e.partial + ((size_t)ks * e.M + trow[i]) * e.N + col + 16 * half)
-                                  : nullptr;
+        rowptr[i] = so[i] != kNoRow ? reinterpret_cast<uint8_t*>(e.partial + (so[i] + (uint32_t)(col + 16 * half))) : nullptr;
       uint32_t w[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) w[i] = r[16 * half + i];
@@ -259,10 +312,8 @@ __device__ __forceinline__ void epilogue_chunk32(const EpiCtx& e, uint8_t* sbuf,
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
   }
-  int resid_row = row < e.M ? row : -1;
-  if (e.epi == EPI_SWIN_PROJ) resid_row = swin_slot_to_token(row, e.seq, e.win, e.shift, e.M >> 6);
-  if (e.resid && resid_row >= 0) {
-    const uint4* r4 = reinterpret_cast<const uint4*>(e.resid + (size_t)resid_row * e.ldo + col);
+  if (e.resid && own != kNoRow) {
+    const uint4* r4 = reinterpret_cast<const uint4*>(e.resid + own + col);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const uint4 u = r4[i];
@@ -275,48 +326,23 @@ __device__ __forceinline__ void epilogue_chunk32(const EpiCtx& e, uint8_t* sbuf,
       }
     }
   }
-  if (e.epi == EPI_QKV) {
-    // [3][B][heads][S][d]: column -> (which of q/k/v, head, offset in head); row -> (sequence, token)
-    const int g = col / e.head_dim, dd = col - g * e.head_dim;      // g = which * heads + head
-    const int which = g / e.heads, hh = g - which * e.heads;
-    const size_t coloff = (size_t)which * e.qkv_plane + (size_t)hh * e.head_plane + dd;
+  const uint32_t coff = epi_col_offset<kSwin>(st, e, col);
+  uint8_t* rowptr[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int b = trow[i] / e.seq, sq = trow[i] - b * e.seq;
-      rowptr[i] = trow[i] < e.M ? reinterpret_cast<uint8_t*>(e.out + coloff + (size_t)b * e.heads * e.head_plane + (size_t)sq * e.head_dim)
-                                : nullptr;
-    }
-  } else if (e.epi == EPI_SWIN_QKV) {
-    // [3][windows][64][C]: the column picks q/k/v and the channel, the row its window slot
-    const int which = col / e.ldo, ch = col - which * e.ldo;
-    const size_t plane = (size_t)((e.M + e.seq * e.seq - 1) / (e.seq * e.seq)) * (e.seq / e.win) * (e.seq / e.win) * 64 * e.ldo;
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-      rowptr[i] = trow[i] < e.M ? reinterpret_cast<uint8_t*>(e.out + (size_t)which * plane +
-                                                              (size_t)swin_token_to_slot(trow[i], e.seq, e.win, e.shift) * e.ldo + ch)
-                                : nullptr;
-  } else if (e.epi == EPI_SWIN_PROJ) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int t = trow[i] < e.M ? swin_slot_to_token(trow[i], e.seq, e.win, e.shift, e.M >> 6) : -1;
-      rowptr[i] = t >= 0 ? reinterpret_cast<uint8_t*>(e.out + (size_t)t * e.ldo + col) : nullptr;
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-      rowptr[i] = trow[i] < e.M ? reinterpret_cast<uint8_t*>(e.out + (size_t)trow[i] * e.ldo + col) : nullptr;
-  }
+  for (int i = 0; i < 4; ++i) rowptr[i] = so[i] != kNoRow ? reinterpret_cast<uint8_t*>(e.out + (so[i] + coff)) : nullptr;
   uint32_t w[16];
 #pragma unroll
   for (int i = 0; i < 16; ++i) w[i] = pack_h2(v[2 * i], v[2 * i + 1]);
+  if (e.prof) t_mid = (unsigned)clock64();
   staged_store_64B(sbuf, w, rowptr, lane);
 }
 
 // 16-column tail chunk (tile widths that are an odd multiple of 16): direct stores.
-__device__ __forceinline__ void epilogue_chunk16(const EpiCtx& e, const uint32_t (&r)[16], int row, int col, int ks) {
-  if (row >= e.M) return;
+template <bool kSwin>
+__device__ __forceinline__ void epilogue_chunk16(const Stage& st, const EpiCtx& e, const uint32_t (&r)[16], uint32_t own, int col) {
+  if (own == kNoRow) return;
   if (e.epi == EPI_PARTIAL) {
-    float4* dst = reinterpret_cast<float4*>(e.partial + ((size_t)ks * e.M + row) * e.N + col);
+    float4* dst = reinterpret_cast<float4*>(e.partial + own + col);
 #pragma unroll
     for (int i = 0; i < 4; ++i)
       dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]),
@@ -342,23 +368,20 @@ __device__ __forceinline__ void epilogue_chunk16(const EpiCtx& e, const uint32_t
     for (int i = 0; i < 16; ++i) v[i] = gelu_tanh(v[i]);
   }
   if (e.resid) {
+    const uint4* r4 = reinterpret_cast<const uint4*>(e.resid + own + col);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(e.resid + (size_t)row * e.ldo + col + 2 * i));
-      v[2 * i] += f.x;
-      v[2 * i + 1] += f.y;
+    for (int i = 0; i < 2; ++i) {
+      const uint4 u = r4[i];
+      const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(h[j]);
+        v[8 * i + 2 * j] += f.x;
+        v[8 * i + 2 * j + 1] += f.y;
+      }
     }
   }
-  __half* dst;
-  if (e.epi == EPI_QKV) {
-    const int g = col / e.head_dim, dd = col - g * e.head_dim;
-    const int which = g / e.heads, hh = g - which * e.heads;
-    const int b = row / e.seq, sq = row - b * e.seq;
-    dst = e.out + (size_t)which * e.qkv_plane + ((size_t)b * e.heads + hh) * e.head_plane + (size_t)sq * e.head_dim + dd;
-  } else {
-    dst = e.out + (size_t)row * e.ldo + col;
-  }
-  uint4* d4 = reinterpret_cast<uint4*>(dst);
+  uint4* d4 = reinterpret_cast<uint4*>(e.out + (own + epi_col_offset<kSwin>(st, e, col)));
   d4[0] = make_uint4(pack_h2(v[0], v[1]), pack_h2(v[2], v[3]), pack_h2(v[4], v[5]), pack_h2(v[6], v[7]));
   d4[1] = make_uint4(pack_h2(v[8], v[9]), pack_h2(v[10], v[11]), pack_h2(v[12], v[13]), pack_h2(v[14], v[15]));
 }
@@ -366,10 +389,11 @@ __device__ __forceinline__ void epilogue_chunk16(const EpiCtx& e, const uint32_t
 // Tiles are bm x bn with bm = 128 (two accumulators used alternately, so the epilogue of one tile
 // overlaps the main loop of the next) or bm = 256 (two 128-row halves share every B tile, which
 // halves the B traffic per FLOP; each half has its own accumulator and hand-shake).
-__device__ __noinline__ void gemm_stage(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, uint32_t ring, __half* vec_s,
+template <bool kSwin>
+__device__ __forceinline__ void gemm_stage(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, uint32_t ring, __half* vec_s,
                            uint8_t* stage_s, RoleState& rs, const WaitCtl& ctl, int warp, int lane) {
   const MegaParams& p = ca.p;
-  const GemmGeom g = gemm_geom(st, p.max_slots);
+  const GemmGeom g = gemm_geom(st);
   if (rs.slot >= (uint32_t)g.nslots) rs.slot = 0;
   const uint32_t full0 = smem_u32(&ctl_s.full[0]), empty0 = smem_u32(&ctl_s.empty[0]);
   const uint32_t tfull0 = smem_u32(&ctl_s.tmem_full[0]), tempty0 = smem_u32(&ctl_s.tmem_empty[0]);
@@ -390,16 +414,16 @@ __device__ __noinline__ void gemm_stage(const Stage& st, const CallArgs& ca, Sme
       const CUtensorMap* tmA = map_ptr(ca, st.tm_a);
       const CUtensorMap* tmB = map_ptr(ca, st.tm_b);
       bool ok = true;
-      long long t_wait = 0;
+      long long t_wait = 0, t_first = 0;
       const bool prof = p.prof != nullptr;
       uint32_t s = rs.slot, bits = rs.slot_bits;
       for (int item = blockIdx.x; ok && item < g.items; item += gridDim.x) {
-        const int ks = item % g.splitk;
-        const int nt = (item / g.splitk) % g.tiles_n;
-        const int mt = item / (g.splitk * g.tiles_n);
+        int mt, nt, ks;
+        gemm_item(st, item, mt, nt, ks);
         const int m0 = mt * g.bm, n0 = nt * g.bn, kbase = ks * g.kchunks;
         // CTAs start at different K chunks so they do not all pull the same A tile at once
-        int kk = (int)((blockIdx.x + (unsigned)item) % (unsigned)g.kchunks);
+        const uint32_t rot = blockIdx.x + (uint32_t)item;
+        int kk = (int)(rot - fast_div(rot, (uint32_t)g.kchunks, st.mg_kchunks) * (uint32_t)g.kchunks);
         for (int kc = 0; kc < g.kchunks; ++kc) {
           const long long tw = prof ? clock64() : 0;
           if (!mbar_wait(empty0 + 8 * s, ((bits >> s) & 1u) ^ 1u, ctl, 100 + (int)s)) { ok = false; break; }
@@ -408,6 +432,7 @@ __device__ __noinline__ void gemm_stage(const Stage& st, const CallArgs& ca, Sme
           mbar_expect_tx(fb, (uint32_t)g.slot_bytes);
           const uint32_t a_dst = ring + s * g.slot_bytes, b_dst = a_dst + a_bytes;
           const int k0 = (kbase + kk) * 64;
+          if (prof && !t_first) t_first = clock64();
           tma_load_2d(a_dst, tmA, fb, k0, m0);                  // box rows = bm: both halves in one copy
           if (!st.b_mn_major) {
             tma_load_2d(b_dst, tmB, fb, k0, n0);
@@ -421,7 +446,11 @@ __device__ __noinline__ void gemm_stage(const Stage& st, const CallArgs& ca, Sme
       }
       rs.slot = s;
       rs.slot_bits = bits;
-      if (p.prof) p.prof[((size_t)st.prof_index * gridDim.x + blockIdx.x) * 8 + 5] = t_wait;
+      if (p.prof) {
+        long long* pr = p.prof + ((size_t)st.prof_index * gridDim.x + blockIdx.x) * kProfSlots;
+        pr[5] = t_wait;
+        pr[11] = t_first;
+      }
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -436,7 +465,7 @@ __device__ __noinline__ void gemm_stage(const Stage& st, const CallArgs& ca, Sme
       const uint32_t bstep = st.b_mn_major ? 128u : 2u;       // 16 K-rows = 2048 B, or 16 halves = 32 B
       const bool prof = p.prof != nullptr;
       bool ok = true;
-      long long t_full = 0, t_acc = 0;
+      long long t_full = 0, t_acc = 0, t_first = 0, t_last = 0;
       for (int item = blockIdx.x; ok && item < g.items; item += gridDim.x) {
         const uint32_t acc0 = g.nh == 2 ? 0u : rs.acc;       // accumulator of half 0; half 1 uses buffer 1
         const uint32_t d0 = tmem + acc0 * kAccStride, d1 = d0 + kAccStride;
@@ -453,7 +482,11 @@ __device__ __noinline__ void gemm_stage(const Stage& st, const CallArgs& ca, Sme
           const uint32_t s = rs.slot;
           const long long tw = prof ? clock64() : 0;
           if (!mbar_wait(full0 + 8 * s, (rs.slot_bits >> s) & 1u, ctl, 300 + (int)s)) { ok = false; break; }
-          if (prof) t_full += clock64() - tw;
+          if (prof) {
+            const long long tn = clock64();
+            t_full += tn - tw;
+            if (!t_first) t_first = tn;
+          }
           tc_fence_after_sync();
           const uint32_t a_lo = a_lo0 + s * slot16, b_lo = b_lo0 + s * slot16;
           if (g.nh == 2) umma_f16_k64_x2(d0, d1, a_lo, b_lo, bstep, idesc, (uint32_t)(kc != 0));
@@ -468,12 +501,15 @@ __device__ __noinline__ void gemm_stage(const Stage& st, const CallArgs& ca, Sme
           umma_commit(tfull0 + 8 * acc);
           rs.acc_bits ^= 1u << acc;
         }
+        if (prof) t_last = clock64();
         if (g.nh == 1) rs.acc ^= 1u;
       }
       if (p.prof) {
-        long long* pr = p.prof + ((size_t)st.prof_index * gridDim.x + blockIdx.x) * 8;
+        long long* pr = p.prof + ((size_t)st.prof_index * gridDim.x + blockIdx.x) * kProfSlots;
         pr[3] = t_full;
         pr[4] = t_acc;
+        pr[12] = t_first;
+        pr[13] = t_last;
       }
     }
     __syncwarp();
@@ -484,62 +520,81 @@ __device__ __noinline__ void gemm_stage(const Stage& st, const CallArgs& ca, Sme
     const int full_chunks = g.bn >> 5;
     EpiCtx e;
     e.epi = st.epi; e.act = st.act; e.M = st.M; e.N = st.N; e.ldo = st.ldo;
-    e.heads = st.heads; e.head_dim = st.head_dim; e.seq = st.seq; e.win = st.win; e.shift = st.shift;
-    e.head_plane = (size_t)st.seq * st.head_dim;
-    e.qkv_plane = (size_t)st.batch * st.heads * e.head_plane;
     e.bias_s = bias_s;
     e.resid = reinterpret_cast<const __half*>(sel_ptr(st.resid_sel, st.resid, p));
     e.out = reinterpret_cast<__half*>(const_cast<void*>(sel_ptr(st.out_sel, st.out, p)));
     e.partial = st.partial;
     const bool prof = p.prof != nullptr;
+    e.prof = prof;
     uint8_t* sbuf = stage_s + (warp - 2) * kStageWarp;
-    long long t_wait = 0, t_busy = 0;
+    unsigned t_wait = 0, t_busy = 0, t_tmem = 0, t_math = 0, t_store = 0;   // cycle totals (32 bits are plenty)
+    long long t_first = 0;
     for (int item = blockIdx.x; item < g.items; item += gridDim.x) {
-      const int ks = item % g.splitk;
-      const int nt = (item / g.splitk) % g.tiles_n;
-      const int mt = item / (g.splitk * g.tiles_n);
+      int mt, nt, ks;
+      gemm_item(st, item, mt, nt, ks);
       const uint32_t acc0 = g.nh == 2 ? 0u : rs.acc;
       bool ok = true;
       for (int h = 0; h < g.nh; ++h) {
         const uint32_t acc = acc0 + (uint32_t)h;
-        const long long tw = prof ? clock64() : 0;
+        const unsigned tw = prof ? (unsigned)clock64() : 0u;
         ok = mbar_wait_warp(tfull0 + 8 * acc, (rs.acc_bits >> acc) & 1u, ctl, 400 + (int)acc, lane);
         if (!ok) break;
-        const long long tb = prof ? clock64() : 0;
-        t_wait += tb - tw;
+        unsigned tb = 0;
+        if (prof) {
+          const long long now = clock64();
+          tb = (unsigned)now;
+          t_wait += tb - tw;
+          if (!t_first) t_first = now;
+        }
         tc_fence_after_sync();
         const int row0 = mt * g.bm + h * 128 + q * 32;
-        const int row = row0 + lane;
-        int trow[4];
+        const bool nostore = (p.dbg_flags & 1) != 0;
+        const uint32_t own = nostore ? kNoRow : epi_row_offset<kSwin>(st, e, row0 + lane, ks);
+        uint32_t so[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) trow[i] = (p.dbg_flags & 1) ? 0x7fffffff : row0 + 8 * i + (lane >> 2);
+        for (int i = 0; i < 4; ++i) so[i] = nostore ? kNoRow : epi_row_offset<kSwin>(st, e, row0 + 8 * i + (lane >> 2), ks);
         const uint32_t t0 = tmem + acc * kAccStride;
         const int colbase = nt * g.bn;
         // this warp takes chunks cpar, cpar+2, ... (its partner warp on the same lane quarter the others)
         for (int c = (p.dbg_flags & 2) ? full_chunks : cpar; c < full_chunks; c += 2) {
           uint32_t r[32];
+          const unsigned tl = prof ? (unsigned)clock64() : 0u;
           tmem_ld32(t0 + c * 32, r);
           tmem_ld_wait(r);
-          epilogue_chunk32(e, sbuf, r, row, trow, colbase + c * 32, ks, lane);
+          unsigned tm = 0, tmid = 0;
+          if (prof) {
+            tm = (unsigned)clock64();
+            t_tmem += tm - tl;
+          }
+          epilogue_chunk32<kSwin>(st, e, sbuf, r, own, so, colbase + c * 32, lane, tmid);
+          if (prof) {
+            t_math += tmid - tm;
+            t_store += (unsigned)clock64() - tmid;
+          }
         }
         if ((g.bn & 16) && (full_chunks & 1) == cpar) {
           uint32_t r[16];
           tmem_ld16(t0 + full_chunks * 32, r);
           tmem_ld_wait(r);
-          epilogue_chunk16(e, r, row, colbase + full_chunks * 32, ks);
+          epilogue_chunk16<kSwin>(st, e, r, own, colbase + full_chunks * 32);
         }
         tc_fence_before_sync();
         mbar_arrive(tempty0 + 8 * acc);
         rs.acc_bits ^= 1u << acc;
-        if (prof) t_busy += clock64() - tb;
+        if (prof) t_busy += (unsigned)clock64() - tb;
       }
       if (!ok) break;
       if (g.nh == 1) rs.acc ^= 1u;
     }
     if (p.prof && warp == 2 && lane == 0) {
-      long long* pr = p.prof + ((size_t)st.prof_index * gridDim.x + blockIdx.x) * 8;
+      long long* pr = p.prof + ((size_t)st.prof_index * gridDim.x + blockIdx.x) * kProfSlots;
       pr[6] = t_wait;
       pr[7] = t_busy;
+      pr[8] = t_tmem;
+      pr[9] = t_math;
+      pr[10] = t_store;
+      pr[14] = t_first;
+      pr[15] = clock64();
     }
   }
 }
@@ -547,7 +602,7 @@ __device__ __noinline__ void gemm_stage(const Stage& st, const CallArgs& ca, Sme
 // ------------------------------------------------------------------------------------
 // attention stage: one work item = (sequence, head, 128-query tile); S <= 384, head_dim 64
 // ------------------------------------------------------------------------------------
-__device__ __noinline__ void attn_stage(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, uint32_t ring, uint8_t* ring_ptr,
+__device__ __forceinline__ void attn_stage(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, uint32_t ring, uint8_t* ring_ptr,
                            RoleState& rs, const WaitCtl& ctl, int warp, int lane) {
   const MegaParams& p = ca.p;
   const int S = st.seq, B = st.batch, H = st.heads;
@@ -742,7 +797,7 @@ enum AttnBar : int { AB_QK_FULL = 0, AB_QK_EMPTY, AB_V_FULL, AB_V_EMPTY, AB_S_FU
 constexpr int kPipeBytes = 5 * kATileBytes;      // Q 16 KiB, K 16, V 16, P 32
 constexpr int kPipeOCol = 256;                   // TMEM: scores at 0 / 128, outputs at 256 / 320
 
-__device__ __noinline__ void attn_stage_pp(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, uint32_t ring, uint8_t* ring_ptr,
+__device__ __forceinline__ void attn_stage_pp(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, uint32_t ring, uint8_t* ring_ptr,
                               uint8_t* stage_s, RoleState& rs, const WaitCtl& ctl, int warp, int lane) {
   const MegaParams& p = ca.p;
   const int S = st.seq, B = st.batch, H = st.heads;
@@ -943,7 +998,7 @@ __device__ __noinline__ void attn_stage_pp(const Stage& st, const CallArgs& ca, 
       if (prof) { const long long c4 = clock64(); t_ws += c1 - c0; t_sm += c2 - c1; t_wo += c3 - c2; t_ep += c4 - c3; t_p1 += c1a - c1; }
     }
     if (prof && warp == 2 && lane == 0) {  // [3] waiting for scores, [4] softmax, [5] waiting for P.V, [6] output
-      long long* pr = p.prof + ((size_t)st.prof_index * gridDim.x + blockIdx.x) * 8;
+      long long* pr = p.prof + ((size_t)st.prof_index * gridDim.x + blockIdx.x) * kProfSlots;
       pr[3] = t_ws; pr[4] = t_sm; pr[5] = t_wo; pr[6] = t_ep; pr[7] = t_p1;
     }
     if (g) rs.attn_bit1 = bit; else rs.attn_bit = bit;
@@ -1237,7 +1292,7 @@ __device__ __forceinline__ void ln_rows2(const float* pl0, const float* pl1, int
   }
 }
 
-__device__ __noinline__ void ln_stage(const Stage& st, const MegaParams& p, SmemCtl& cs, uint32_t ring, uint8_t* ring_ptr,
+__device__ __forceinline__ void ln_stage(const Stage& st, const MegaParams& p, SmemCtl& cs, uint32_t ring, uint8_t* ring_ptr,
                          RoleState& rs, const WaitCtl& ctl, int warp, int lane) {
   const int N = st.N, M = st.M, P = st.n_partial;
   const __half* resid = reinterpret_cast<const __half*>(sel_ptr(st.resid_sel, st.resid, p));
@@ -1311,7 +1366,7 @@ __device__ __noinline__ void ln_stage(const Stage& st, const MegaParams& p, Smem
     if (threadIdx.x == 0 && next < n_batches) issue(next, buf);
   }
   if (prof && warp == 2 && lane == 0) {    // [3] waiting for a batch, [4] waiting for the other warps
-    long long* pr = p.prof + ((size_t)st.prof_index * gridDim.x + blockIdx.x) * 8;
+    long long* pr = p.prof + ((size_t)st.prof_index * gridDim.x + blockIdx.x) * kProfSlots;
     pr[3] = t_wait;
     pr[4] = t_sync;
     pr[5] = rb;
@@ -1324,11 +1379,25 @@ __device__ __noinline__ void ln_stage(const Stage& st, const MegaParams& p, Smem
 // ------------------------------------------------------------------------------------
 // 320 threads leave 168 registers per thread (the register file is handed out per four warps); the
 // epilogue is written to stay below that without spilling.
+// The kernel exists in two builds.  <false> runs BERT layers, plain GEMMs and LayerNorm with every stage
+// inlined (fastest: one register allocation over the whole role code).  <true> adds the Swin epilogues and
+// the window-attention stage; with those inlined as well the allocation no longer fits 168 registers, so
+// that build keeps its stages out of line.
+__device__ __noinline__ void gemm_stage_ool(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, uint32_t ring, __half* vec_s,
+                                            uint8_t* stage_s, RoleState& rs, const WaitCtl& ctl, int warp, int lane) {
+  gemm_stage<true>(st, ca, ctl_s, ring, vec_s, stage_s, rs, ctl, warp, lane);
+}
+__device__ __noinline__ void ln_stage_ool(const Stage& st, const MegaParams& p, SmemCtl& cs, uint32_t ring, uint8_t* ring_ptr,
+                                          RoleState& rs, const WaitCtl& ctl, int warp, int lane) {
+  ln_stage(st, p, cs, ring, ring_ptr, rs, ctl, warp, lane);
+}
+
+template <bool kSwin>
 __global__ void __launch_bounds__(kThreads, 1)
 souffle_megakernel(const __grid_constant__ CallArgs ca) {
   const MegaParams& p = ca.p;
   extern __shared__ uint8_t smem_raw[];
-  const long long t_entry = clock64();
+  if (p.prof && threadIdx.x == 0) p.prof[((size_t)p.n_stages * gridDim.x + blockIdx.x) * kProfSlots] = clock64();
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t pad = ((raw + 1023u) & ~1023u) - raw;      // 1024-byte alignment for swizzled tiles
   SmemCtl& cs = *reinterpret_cast<SmemCtl*>(smem_raw + pad);
@@ -1377,8 +1446,7 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
   ctl.status_g = p.status;
   ctl.deadline_ns = cs.deadline_ns;
   if (p.prof && threadIdx.x == 0) {          // one record past the stages: kernel entry, prologue done, ...
-    long long* pr = p.prof + ((size_t)p.n_stages * gridDim.x + blockIdx.x) * 8;
-    pr[0] = t_entry;
+    long long* pr = p.prof + ((size_t)p.n_stages * gridDim.x + blockIdx.x) * kProfSlots;
     pr[1] = clock64();
   }
 
@@ -1392,30 +1460,34 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
     }
     if (threadIdx.x == 0) cs.stage.prof_index = si;
     __syncthreads();
-    if (p.prof && threadIdx.x == 0) p.prof[((size_t)si * gridDim.x + blockIdx.x) * 8 + 0] = clock64();
+    if (p.prof && threadIdx.x == 0) p.prof[((size_t)si * gridDim.x + blockIdx.x) * kProfSlots + 0] = clock64();
     const Stage& st = cs.stage;
-    if (st.type == STAGE_GEMM) {
-      gemm_stage(st, ca, cs, ring, vec_s, stage_s, rs, ctl, warp, lane);
-    } else if (st.type == STAGE_ATTN_SWIN) {
-      attn_swin_stage(st, ca, cs, ring, ring_ptr, stage_s, rs, ctl, warp, lane);
-    } else if (st.type == STAGE_ATTN) {
-      if (st.seq <= 128) attn_stage_pp(st, ca, cs, ring, ring_ptr, stage_s, rs, ctl, warp, lane);
-      else attn_stage(st, ca, cs, ring, ring_ptr, rs, ctl, warp, lane);
+    if constexpr (kSwin) {
+      if (st.type == STAGE_GEMM) gemm_stage_ool(st, ca, cs, ring, vec_s, stage_s, rs, ctl, warp, lane);
+      else if (st.type == STAGE_ATTN_SWIN) attn_swin_stage(st, ca, cs, ring, ring_ptr, stage_s, rs, ctl, warp, lane);
+      else if (st.type == STAGE_LN) ln_stage_ool(st, p, cs, ring, ring_ptr, rs, ctl, warp, lane);
     } else {
-      ln_stage(st, p, cs, ring, ring_ptr, rs, ctl, warp, lane);
+      if (st.type == STAGE_GEMM) {
+        gemm_stage<false>(st, ca, cs, ring, vec_s, stage_s, rs, ctl, warp, lane);
+      } else if (st.type == STAGE_ATTN) {
+        if (st.seq <= 128) attn_stage_pp(st, ca, cs, ring, ring_ptr, stage_s, rs, ctl, warp, lane);
+        else attn_stage(st, ca, cs, ring, ring_ptr, rs, ctl, warp, lane);
+      } else if (st.type == STAGE_LN) {
+        ln_stage(st, p, cs, ring, ring_ptr, rs, ctl, warp, lane);
+      }
     }
     if (si + 1 < p.n_stages) {
       if (!grid_barrier(p, ctl, si)) break;
     } else {
       __syncthreads();
-      if (p.prof && threadIdx.x == 0) p.prof[((size_t)si * gridDim.x + blockIdx.x) * 8 + 1] = clock64();
+      if (p.prof && threadIdx.x == 0) p.prof[((size_t)si * gridDim.x + blockIdx.x) * kProfSlots + 1] = clock64();
     }
-    if (p.prof && threadIdx.x == 0) p.prof[((size_t)si * gridDim.x + blockIdx.x) * 8 + 2] = clock64();
+    if (p.prof && threadIdx.x == 0) p.prof[((size_t)si * gridDim.x + blockIdx.x) * kProfSlots + 2] = clock64();
     if (cs.abort) break;
   }
 
   __syncthreads();
-  if (p.prof && threadIdx.x == 0) p.prof[((size_t)p.n_stages * gridDim.x + blockIdx.x) * 8 + 2] = clock64();
+  if (p.prof && threadIdx.x == 0) p.prof[((size_t)p.n_stages * gridDim.x + blockIdx.x) * kProfSlots + 2] = clock64();
   if (cs.abort) {
     // let copies that were already issued land before the CTA's shared memory is released
     const unsigned long long t0 = globaltimer_ns();

@@ -164,9 +164,12 @@ static int device_info(DeviceInfo** out) {
     SF_CUDA(cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev));
     if (d.cc_major != 10)
       return fail(SOUFFLE_BAD_DEVICE, "device %d has compute capability %d.x; this library needs sm_100", dev, d.cc_major);
-    SF_CUDA(cudaFuncSetAttribute(souffle_megakernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-    int per_sm = 0;
-    SF_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, souffle_megakernel, kThreads, kSmemBytes));
+    SF_CUDA(cudaFuncSetAttribute(souffle_megakernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    SF_CUDA(cudaFuncSetAttribute(souffle_megakernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    int per_sm = 0, per_sm_swin = 0;
+    SF_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, souffle_megakernel<false>, kThreads, kSmemBytes));
+    SF_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm_swin, souffle_megakernel<true>, kThreads, kSmemBytes));
+    if (per_sm_swin < per_sm) per_sm = per_sm_swin;
     d.max_ctas = per_sm * d.sms;
     if (d.max_ctas < 1) return fail(SOUFFLE_NOT_CORESIDENT, "megakernel does not fit on an SM of device %d", dev);
     d.device = dev;
@@ -175,15 +178,11 @@ static int device_info(DeviceInfo** out) {
   return SOUFFLE_OK;
 }
 
-static int launch_mega(const CallArgs& args, int grid, cudaStream_t stream) {
+// `swin` selects the build of the kernel that knows the Swin epilogues and the window-attention stage.
+static int launch_mega(const CallArgs& args, int grid, cudaStream_t stream, bool swin = false) {
   void* kargs[] = {const_cast<CallArgs*>(&args)};
-  static const bool plain = getenv("SOUFFLE_PLAIN_LAUNCH") != nullptr;     // experiment: non-cooperative launch
-  if (plain) {
-    SF_CUDA(cudaLaunchKernel((const void*)souffle_megakernel, dim3(grid), dim3(kThreads), kargs, (size_t)kSmemBytes, stream));
-    return SOUFFLE_OK;
-  }
-  SF_CUDA(cudaLaunchCooperativeKernel((const void*)souffle_megakernel, dim3(grid), dim3(kThreads), kargs,
-                                      (size_t)kSmemBytes, stream));
+  const void* fn = swin ? (const void*)souffle_megakernel<true> : (const void*)souffle_megakernel<false>;
+  SF_CUDA(cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kThreads), kargs, (size_t)kSmemBytes, stream));
   return SOUFFLE_OK;
 }
 
@@ -192,6 +191,31 @@ static int stage_items(const Stage& s) {
   if (s.type == STAGE_ATTN) return s.batch * s.heads * ((s.seq + 127) / 128);
   if (s.type == STAGE_ATTN_SWIN) return s.batch * (s.seq / s.win) * (s.seq / s.win) * s.heads;
   return (s.M + kThreads / 32 - 1) / (kThreads / 32);
+}
+
+// Fills the derived fields of a GEMM stage (tile counts, ring geometry, magic divisors) and checks that its
+// output fits the kernel's 32-bit element offsets.
+static int finalize_stage(Stage& s, int max_slots) {
+  if (s.type != STAGE_GEMM) return SOUFFLE_OK;
+  s.tiles_n = s.N / s.bn;
+  s.kchunks = s.K / 64 / s.splitk;
+  s.items = stage_items(s);
+  s.slot_bytes = (s.bm / 128) * 16384 + s.bn * 128;
+  int n = 196608 / s.slot_bytes;
+  if (n > 8) n = 8;
+  if (max_slots > 0 && n > max_slots) n = max_slots;
+  s.nslots = n;
+  s.mg_splitk = fast_div_magic((uint32_t)s.splitk);
+  s.mg_tiles_n = fast_div_magic((uint32_t)s.tiles_n);
+  s.mg_kchunks = fast_div_magic((uint32_t)s.kchunks);
+  s.mg_seq = fast_div_magic((uint32_t)(s.seq > 0 ? s.seq : 1));
+  s.mg_head_dim = fast_div_magic((uint32_t)(s.head_dim > 0 ? s.head_dim : 1));
+  s.mg_heads = fast_div_magic((uint32_t)(s.heads > 0 ? s.heads : 1));
+  const unsigned long long out_elems = (unsigned long long)s.M * (unsigned long long)s.N * (s.epi == EPI_PARTIAL ? s.splitk : 1);
+  // 2^20 rows keep every multiply-high division exact (numerator * divisor < 2^32)
+  if (s.M > (1 << 20) || out_elems * (s.epi == EPI_SWIN_QKV ? 2 : 1) >= 0xFFFF0000ull || (long long)s.items * 16 >= (1ll << 32))
+    return fail(SOUFFLE_BAD_SHAPE, "GEMM stage %d x %d (split %d) is too large for 32-bit output offsets", s.M, s.N, s.splitk);
+  return SOUFFLE_OK;
 }
 
 static int decode_status(const int* h, const char* what) {
@@ -429,10 +453,12 @@ static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* la
   p->grid = max_items < sms ? max_items : sms;
 
   if (d.profile) {
-    const size_t pb = (p->stages.size() + 1) * (size_t)p->grid * 8 * sizeof(long long);
+    const size_t pb = (p->stages.size() + 1) * (size_t)p->grid * kProfSlots * sizeof(long long);
     if ((rc = plan_alloc(p, (void**)&p->d_prof, pb))) return rc;
     SF_CUDA(cudaMemset(p->d_prof, 0, pb));
   }
+  for (Stage& fs : p->stages)
+    if ((rc = finalize_stage(fs, p->desc.debug_max_slots & 0xFF))) return rc;
   if ((rc = plan_alloc(p, (void**)&p->d_stages, p->stages.size() * sizeof(Stage)))) return rc;
   if ((rc = plan_alloc(p, (void**)&p->d_maps, p->maps.size() * sizeof(CUtensorMap)))) return rc;
   SF_CUDA(cudaMemcpy(p->d_stages, p->stages.data(), p->stages.size() * sizeof(Stage), cudaMemcpyHostToDevice));
@@ -594,7 +620,7 @@ int souffle_bert_plan_status(SouffleBertPlan* plan) {
 int souffle_bert_plan_read_profile(SouffleBertPlan* plan, int64_t* out, size_t capacity_elems) {
   if (!plan || !out) return fail(SOUFFLE_BAD_ARGUMENT, "null argument");
   if (!plan->d_prof) return fail(SOUFFLE_BAD_ARGUMENT, "the plan was created without desc.profile");
-  const size_t n = (plan->stages.size() + 1) * (size_t)plan->grid * 8;
+  const size_t n = (plan->stages.size() + 1) * (size_t)plan->grid * kProfSlots;
   if (capacity_elems < n) return fail(SOUFFLE_BAD_ARGUMENT, "profile needs %zu elements, got %zu", n, capacity_elems);
   SF_CUDA(cudaDeviceSynchronize());
   SF_CUDA(cudaMemcpy(out, plan->d_prof, n * sizeof(long long), cudaMemcpyDeviceToHost));
@@ -606,6 +632,16 @@ int souffle_bert_plan_info(SouffleBertPlan* plan, int* launches_out, int* grid_o
   if (launches_out) *launches_out = plan->launches;
   if (grid_out) *grid_out = plan->grid;
   if (n_stages_out) *n_stages_out = (int)plan->stages.size();
+  return SOUFFLE_OK;
+}
+
+int souffle_bert_plan_stage_info(SouffleBertPlan* plan, int index, int out[6]) {
+  if (!plan || !out) return fail(SOUFFLE_BAD_ARGUMENT, "null argument");
+  if (index < 0 || index >= (int)plan->stages.size()) return fail(SOUFFLE_BAD_ARGUMENT, "stage index %d out of range", index);
+  const Stage& s = plan->stages[index];
+  out[0] = s.type; out[1] = s.bm; out[2] = s.bn; out[3] = s.splitk; out[4] = stage_items(s);
+  const int slot = (s.bm == 256 ? 2 : 1) * 16384 + s.bn * 128;
+  out[5] = s.type == STAGE_GEMM ? (196608 / slot > 8 ? 8 : 196608 / slot) : 0;
   return SOUFFLE_OK;
 }
 
@@ -631,7 +667,7 @@ static int fill_gemm_stage(Stage* s, int tm_a, int tm_b, const void* out, int M,
   if (!t.bn) return fail(SOUFFLE_BAD_SHAPE, "N=%d must be a multiple of 64", N);
   s->tm_a = tm_a; s->tm_b = tm_b; s->M = M; s->N = N; s->K = K; s->bm = t.bm; s->bn = t.bn; s->b_mn_major = 1;
   s->epi = EPI_F16; s->out = const_cast<void*>(out); s->ldo = N;
-  return SOUFFLE_OK;
+  return finalize_stage(*s, 0);
 }
 
 int souffle_gemm_f16(const void* a, const void* w_kn, void* c, int32_t M, int32_t N, int32_t K, void* workspace,
@@ -733,7 +769,7 @@ static int launch_plan(SouffleBertPlan* plan, const void* x, void* y, const int3
   mp.sync_next = plan->d_sync + 2 * (par ^ 1u);
   mp.status = plan->d_status;
   mp.timeout_ns = (unsigned long long)(timeout_ms > 0 ? timeout_ms : 2000) * 1000000ull;
-  int rc = launch_mega(args, plan->grid, st);
+  int rc = launch_mega(args, plan->grid, st, /*swin=*/true);
   if (rc) return rc;
   plan->launch_id++;
   plan->launches = 1;
@@ -748,6 +784,8 @@ static int finish_plan(SouffleBertPlan* p, int sms) {
     if (it > max_items) max_items = it;
   }
   p->grid = max_items < sms ? max_items : sms;
+  for (Stage& fs : p->stages)
+    if ((rc = finalize_stage(fs, p->desc.debug_max_slots & 0xFF))) return rc;
   if ((rc = plan_alloc(p, (void**)&p->d_stages, p->stages.size() * sizeof(Stage)))) return rc;
   if ((rc = plan_alloc(p, (void**)&p->d_maps, p->maps.size() * sizeof(CUtensorMap)))) return rc;
   SF_CUDA(cudaMemcpy(p->d_stages, p->stages.data(), p->stages.size() * sizeof(Stage), cudaMemcpyHostToDevice));

@@ -64,9 +64,18 @@ struct Stage {
   float eps;
   int n_partial;     // number of fp32 partial planes to sum
   int prof_index;    // filled in by the kernel: position of this stage in the program
+  // ---- derived on the host by finalize_stage(): the kernel's lone producer / MMA lanes would otherwise
+  //      spend a few thousand cycles per stage in integer divisions ----
+  int tiles_n, kchunks, items, slot_bytes, nslots;
+  uint32_t mg_splitk, mg_tiles_n, mg_kchunks;   // magic multipliers, see fast_div()
+  uint32_t mg_seq, mg_head_dim, mg_heads;
 };
+
+// q = n / d for n * d < 2^32 as one multiply-high: mg = ceil(2^32 / d); d == 1 has no 32-bit multiplier.
+inline uint32_t fast_div_magic(uint32_t d) { return d <= 1 ? 0u : (uint32_t)((0x100000000ull + d - 1) / d); }
 
 constexpr int kMaxTensorMaps = 80;
 constexpr int kMaxStages = 96;
+constexpr int kProfSlots = 16;   // int64 words per (stage, CTA) record of the in-kernel profile
 
 }  // namespace souffle

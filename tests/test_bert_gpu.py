@@ -124,6 +124,19 @@ def test_tile_overrides_agree():
     assert (y0 - y1).abs().max() < 4e-3
 
 
+def test_stage_info_reports_the_tiling():
+    cfg = so.BertConfig(2, 128, 12, 64, 3072, "std")
+    layers = so.make_bert_weights(cfg, 5, 1)
+    enc = _encoder(cfg, layers, tuning=dict(bm_fc1=128, bn_fc1=128))
+    types = [enc.stage_info(i)["type"] for i in range(7)]
+    assert types == [0, 1, 0, 2, 0, 0, 2]          # QKV, attention, proj, LN1, FC1, FC2, LN2
+    fc1 = enc.stage_info(4)
+    assert (fc1["bm"], fc1["bn"], fc1["splitk"]) == (128, 128, 1)
+    assert fc1["items"] == (256 // 128) * (3072 // 128) and fc1["slots"] == 6
+    with pytest.raises(Exception):
+        enc.stage_info(7)
+
+
 def test_host_buffer_entry_point():
     cfg = so.BertConfig(2, 128, 12, 64, 3072, "std")
     layers = so.make_bert_weights(cfg, 5, 1)
