@@ -305,10 +305,11 @@ __device__ __forceinline__ void epilogue_chunk32(const Stage& st, const EpiCtx& 
       }
     }
   }
+  const bool gelu_packed = e.act == ACT_GELU && e.resid == nullptr;   // GELU on fp16 pairs after packing (below)
   if (e.act == ACT_RELU) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.0f);
-  } else if (e.act == ACT_GELU) {
+  } else if (e.act == ACT_GELU && !gelu_packed) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
   }
@@ -333,6 +334,10 @@ __device__ __forceinline__ void epilogue_chunk32(const Stage& st, const EpiCtx& 
   uint32_t w[16];
 #pragma unroll
   for (int i = 0; i < 16; ++i) w[i] = pack_h2(v[2 * i], v[2 * i + 1]);
+  if (gelu_packed) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) w[i] = gelu_tanh_h2(w[i]);
+  }
   if (e.prof) t_mid = (unsigned)clock64();
   staged_store_64B(sbuf, w, rowptr, lane);
 }
@@ -890,64 +895,86 @@ __device__ __forceinline__ void attn_stage_pp(const Stage& st, const CallArgs& c
       const long long c1 = prof ? clock64() : 0;
       tc_fence_after_sync();
       const uint32_t ts = tmem + g * 128;
-      // ---- pass 1: row maximum of the scaled, masked scores (base-2 domain), four running maxima ----
+      // Masked keys (>= kv_len) get -10000 added, which underflows to probability 0 in fp32 and never wins
+      // the maximum, so both passes only visit the 16-column blocks that hold valid keys.  TMEM loads are
+      // double-buffered 16 columns at a time: the next block is in flight while this one is processed.
+      const int kvl = kv_len < 1 ? 1 : (kv_len > S ? S : kv_len);
+      const int nb = (kvl + 15) >> 4;
+      uint32_t ra[16], rb[16];
+      // ---- pass 1: row maximum of the raw scores of the valid keys (the scale is positive) ----
       float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
-      for (int c = 0; c < n_chunks; ++c) {
-        uint32_t r[32];
-        tmem_ld32(ts + c * 32, r);
-        tmem_ld_wait(r);
+      auto max16 = [&](const uint32_t (&r)[16], int blk) {
+        const int key0 = blk * 16;
+        if (key0 + 16 <= kvl) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          const int key = c * 32 + i;
-          float t0 = __uint_as_float(r[i]) * sl2, t1 = __uint_as_float(r[i + 1]) * sl2,
-                t2 = __uint_as_float(r[i + 2]) * sl2, t3 = __uint_as_float(r[i + 3]) * sl2;
-          if (key + 3 >= kv_len) {
-            t0 = key < S ? t0 + (key >= kv_len ? mask_l2 : 0.f) : -INFINITY;
-            t1 = key + 1 < S ? t1 + (key + 1 >= kv_len ? mask_l2 : 0.f) : -INFINITY;
-            t2 = key + 2 < S ? t2 + (key + 2 >= kv_len ? mask_l2 : 0.f) : -INFINITY;
-            t3 = key + 3 < S ? t3 + (key + 3 >= kv_len ? mask_l2 : 0.f) : -INFINITY;
+          for (int i = 0; i < 16; i += 4) {
+            m0 = fmaxf(m0, __uint_as_float(r[i])); m1 = fmaxf(m1, __uint_as_float(r[i + 1]));
+            m2 = fmaxf(m2, __uint_as_float(r[i + 2])); m3 = fmaxf(m3, __uint_as_float(r[i + 3]));
           }
-          m0 = fmaxf(m0, t0); m1 = fmaxf(m1, t1); m2 = fmaxf(m2, t2); m3 = fmaxf(m3, t3);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) m0 = fmaxf(m0, key0 + i < kvl ? __uint_as_float(r[i]) : -INFINITY);
+        }
+      };
+      tmem_ld16(ts, ra);
+      tmem_ld_wait(ra);
+      for (int blk = 0; blk < nb; blk += 2) {
+        if (blk + 1 < nb) tmem_ld16(ts + (blk + 1) * 16, rb);
+        max16(ra, blk);
+        if (blk + 1 < nb) {
+          tmem_ld_wait(rb);
+          if (blk + 2 < nb) tmem_ld16(ts + (blk + 2) * 16, ra);
+          max16(rb, blk + 1);
+          if (blk + 2 < nb) tmem_ld_wait(ra);
         }
       }
-      const float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+      const float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * sl2;
       const long long c1a = prof ? clock64() : 0;
       // ---- pass 2: unnormalised probabilities -> fp16 A-operand tile (128B-swizzled rows) ----
       float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-      for (int c = 0; c < 4; ++c) {
-        uint32_t w[16];
-        if (c >= n_chunks) {
+      auto exp16 = [&](const uint32_t (&r)[16], int blk) {
+        const int key0 = blk * 16;
+        uint32_t w[8];
+        if (key0 + 16 <= kvl) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) w[i] = 0u;
-        } else {
-          uint32_t r[32];
-          tmem_ld32(ts + c * 32, r);
-          tmem_ld_wait(r);
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            const int key = c * 32 + i;
-            float t0 = __uint_as_float(r[i]) * sl2, t1 = __uint_as_float(r[i + 1]) * sl2,
-                  t2 = __uint_as_float(r[i + 2]) * sl2, t3 = __uint_as_float(r[i + 3]) * sl2;
-            float p0, p1, p2, p3;
-            if (key + 3 >= kv_len) {
-              p0 = key < S ? ex2_fast(t0 + (key >= kv_len ? mask_l2 : 0.f) - mx) : 0.f;
-              p1 = key + 1 < S ? ex2_fast(t1 + (key + 1 >= kv_len ? mask_l2 : 0.f) - mx) : 0.f;
-              p2 = key + 2 < S ? ex2_fast(t2 + (key + 2 >= kv_len ? mask_l2 : 0.f) - mx) : 0.f;
-              p3 = key + 3 < S ? ex2_fast(t3 + (key + 3 >= kv_len ? mask_l2 : 0.f) - mx) : 0.f;
-            } else {
-              p0 = ex2_fast(t0 - mx); p1 = ex2_fast(t1 - mx); p2 = ex2_fast(t2 - mx); p3 = ex2_fast(t3 - mx);
-            }
+          for (int i = 0; i < 16; i += 4) {
+            const float p0 = ex2_fast(fmaf(__uint_as_float(r[i]), sl2, -mx)), p1 = ex2_fast(fmaf(__uint_as_float(r[i + 1]), sl2, -mx));
+            const float p2 = ex2_fast(fmaf(__uint_as_float(r[i + 2]), sl2, -mx)), p3 = ex2_fast(fmaf(__uint_as_float(r[i + 3]), sl2, -mx));
             s0 += p0; s1 += p1; s2 += p2; s3 += p3;
             w[i >> 1] = pack_h2(p0, p1);
             w[(i >> 1) + 1] = pack_h2(p2, p3);
           }
-        }
-        uint8_t* base = pbase + (c >> 1) * kATileBytes;
+        } else {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int j = (c & 1) * 4 + i;
-          *reinterpret_cast<uint4*>(base + ((j ^ (r_in & 7)) << 4)) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+          for (int i = 0; i < 16; i += 2) {
+            const float p0 = key0 + i < kvl ? ex2_fast(fmaf(__uint_as_float(r[i]), sl2, -mx)) : 0.f;
+            const float p1 = key0 + i + 1 < kvl ? ex2_fast(fmaf(__uint_as_float(r[i + 1]), sl2, -mx)) : 0.f;
+            s0 += p0; s1 += p1;
+            w[i >> 1] = pack_h2(p0, p1);
+          }
         }
+        uint8_t* base = pbase + (blk >> 2) * kATileBytes;
+        const int j = (blk & 3) * 2;
+        *reinterpret_cast<uint4*>(base + ((j ^ (r_in & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(base + (((j + 1) ^ (r_in & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+      };
+      tmem_ld16(ts, ra);
+      tmem_ld_wait(ra);
+      for (int blk = 0; blk < nb; blk += 2) {
+        if (blk + 1 < nb) tmem_ld16(ts + (blk + 1) * 16, rb);
+        exp16(ra, blk);
+        if (blk + 1 < nb) {
+          tmem_ld_wait(rb);
+          if (blk + 2 < nb) tmem_ld16(ts + (blk + 2) * 16, ra);
+          exp16(rb, blk + 1);
+          if (blk + 2 < nb) tmem_ld_wait(ra);
+        }
+      }
+      for (int blk = nb; blk < 8; ++blk) {                    // keys past the valid ones: probability 0
+        uint8_t* base = pbase + (blk >> 2) * kATileBytes;
+        const int j = (blk & 3) * 2;
+        *reinterpret_cast<uint4*>(base + ((j ^ (r_in & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(base + (((j + 1) ^ (r_in & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
       }
       const float inv = 1.0f / ((s0 + s1) + (s2 + s3));
       if (probs) {                                            // parity output: normalised probabilities
@@ -1219,7 +1246,7 @@ __device__ __forceinline__ void ln_rows2(const float* pl0, const float* pl1, int
   for (int j = 0; j < NJ; ++j) {
     float add[4] = {0.f, 0.f, 0.f, 0.f};
     if (bias) {
-      const uint2 u = __ldg(reinterpret_cast<const uint2*>(bias + (lane + 32 * j) * 4));
+      const uint2 u = *reinterpret_cast<const uint2*>(bias + (lane + 32 * j) * 4);
       const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
       const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
       add[0] = f0.x; add[1] = f0.y; add[2] = f1.x; add[3] = f1.y;
@@ -1271,8 +1298,8 @@ __device__ __forceinline__ void ln_rows2(const float* pl0, const float* pl1, int
   for (int j = 0; j < NJ; ++j) {
     float g[4] = {1.f, 1.f, 1.f, 1.f}, bt[4] = {0.f, 0.f, 0.f, 0.f};
     if (gamma) {
-      const uint2 ug = __ldg(reinterpret_cast<const uint2*>(gamma + (lane + 32 * j) * 4));
-      const uint2 ub = __ldg(reinterpret_cast<const uint2*>(beta + (lane + 32 * j) * 4));
+      const uint2 ug = *reinterpret_cast<const uint2*>(gamma + (lane + 32 * j) * 4);
+      const uint2 ub = *reinterpret_cast<const uint2*>(beta + (lane + 32 * j) * 4);
       const float2 g0 = __half22float2(*reinterpret_cast<const __half2*>(&ug.x));
       const float2 g1 = __half22float2(*reinterpret_cast<const __half2*>(&ug.y));
       const float2 b0 = __half22float2(*reinterpret_cast<const __half2*>(&ub.x));
@@ -1293,7 +1320,7 @@ __device__ __forceinline__ void ln_rows2(const float* pl0, const float* pl1, int
 }
 
 __device__ __forceinline__ void ln_stage(const Stage& st, const MegaParams& p, SmemCtl& cs, uint32_t ring, uint8_t* ring_ptr,
-                         RoleState& rs, const WaitCtl& ctl, int warp, int lane) {
+                                         __half* vec_s, RoleState& rs, const WaitCtl& ctl, int warp, int lane) {
   const int N = st.N, M = st.M, P = st.n_partial;
   const __half* resid = reinterpret_cast<const __half*>(sel_ptr(st.resid_sel, st.resid, p));
   __half* out = reinterpret_cast<__half*>(const_cast<void*>(sel_ptr(st.out_sel, st.out, p)));
@@ -1306,6 +1333,8 @@ __device__ __forceinline__ void ln_stage(const Stage& st, const MegaParams& p, S
   rb = rb > 20 ? 20 : (rb < 1 ? 1 : rb);
   const int per_cta = (M + (int)gridDim.x - 1) / (int)gridDim.x;
   if (rb > per_cta) rb = per_cta;
+  // bias | gamma | beta side by side in shared memory, when a CTA normalises enough rows to pay for the copy
+  const bool stage_vecs = 3 * N * 2 <= kVecBytes && per_cta >= 4;
   if (rb > kThreads / 32) rb -= rb % (kThreads / 32);        // whole rounds of one or two rows per warp
   const int batch_bytes = rb * row_bytes;
   int nbuf = kRingBytes / batch_bytes;
@@ -1327,6 +1356,21 @@ __device__ __forceinline__ void ln_stage(const Stage& st, const MegaParams& p, S
   if (threadIdx.x == 0) {
     int b = blockIdx.x;
     for (int j = 0; j < nbuf && b < n_batches; ++j, b += gridDim.x) issue(b, j);
+  }
+  // The per-column vectors go to shared memory once (while the first batches are in flight): read from global
+  // memory inside the row loop, a miss in the small L1 costs an L2 round trip in the middle of every row.
+  if (stage_vecs) {
+    const __half* srcs[3] = {bias, gamma, beta};
+#pragma unroll
+    for (int v = 0; v < 3; ++v) {
+      if (!srcs[v]) continue;
+      const uint2* src = reinterpret_cast<const uint2*>(srcs[v]);
+      uint2* dst = reinterpret_cast<uint2*>(vec_s + v * N);
+      for (int i = threadIdx.x; i < N / 4; i += kThreads) dst[i] = __ldg(src + i);
+    }
+    __syncthreads();
+    if (bias) bias = vec_s;
+    if (gamma) { gamma = vec_s + N; beta = vec_s + 2 * N; }
   }
   int k = 0;
   const bool prof = p.prof != nullptr;
@@ -1388,8 +1432,8 @@ __device__ __noinline__ void gemm_stage_ool(const Stage& st, const CallArgs& ca,
   gemm_stage<true>(st, ca, ctl_s, ring, vec_s, stage_s, rs, ctl, warp, lane);
 }
 __device__ __noinline__ void ln_stage_ool(const Stage& st, const MegaParams& p, SmemCtl& cs, uint32_t ring, uint8_t* ring_ptr,
-                                          RoleState& rs, const WaitCtl& ctl, int warp, int lane) {
-  ln_stage(st, p, cs, ring, ring_ptr, rs, ctl, warp, lane);
+                                          __half* vec_s, RoleState& rs, const WaitCtl& ctl, int warp, int lane) {
+  ln_stage(st, p, cs, ring, ring_ptr, vec_s, rs, ctl, warp, lane);
 }
 
 template <bool kSwin>
@@ -1397,7 +1441,11 @@ __global__ void __launch_bounds__(kThreads, 1)
 souffle_megakernel(const __grid_constant__ CallArgs ca) {
   const MegaParams& p = ca.p;
   extern __shared__ uint8_t smem_raw[];
-  if (p.prof && threadIdx.x == 0) p.prof[((size_t)p.n_stages * gridDim.x + blockIdx.x) * kProfSlots] = clock64();
+  if (p.prof && threadIdx.x == 0) {
+    long long* pr = p.prof + ((size_t)p.n_stages * gridDim.x + blockIdx.x) * kProfSlots;
+    pr[0] = clock64();
+    pr[3] = (long long)globaltimer_ns();        // wall clock shared by all SMs: launch skew between CTAs
+  }
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t pad = ((raw + 1023u) & ~1023u) - raw;      // 1024-byte alignment for swizzled tiles
   SmemCtl& cs = *reinterpret_cast<SmemCtl*>(smem_raw + pad);
@@ -1465,7 +1513,7 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
     if constexpr (kSwin) {
       if (st.type == STAGE_GEMM) gemm_stage_ool(st, ca, cs, ring, vec_s, stage_s, rs, ctl, warp, lane);
       else if (st.type == STAGE_ATTN_SWIN) attn_swin_stage(st, ca, cs, ring, ring_ptr, stage_s, rs, ctl, warp, lane);
-      else if (st.type == STAGE_LN) ln_stage_ool(st, p, cs, ring, ring_ptr, rs, ctl, warp, lane);
+      else if (st.type == STAGE_LN) ln_stage_ool(st, p, cs, ring, ring_ptr, vec_s, rs, ctl, warp, lane);
     } else {
       if (st.type == STAGE_GEMM) {
         gemm_stage<false>(st, ca, cs, ring, vec_s, stage_s, rs, ctl, warp, lane);
@@ -1473,7 +1521,7 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
         if (st.seq <= 128) attn_stage_pp(st, ca, cs, ring, ring_ptr, stage_s, rs, ctl, warp, lane);
         else attn_stage(st, ca, cs, ring, ring_ptr, rs, ctl, warp, lane);
       } else if (st.type == STAGE_LN) {
-        ln_stage(st, p, cs, ring, ring_ptr, rs, ctl, warp, lane);
+        ln_stage(st, p, cs, ring, ring_ptr, vec_s, rs, ctl, warp, lane);
       }
     }
     if (si + 1 < p.n_stages) {
@@ -1487,7 +1535,11 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
   }
 
   __syncthreads();
-  if (p.prof && threadIdx.x == 0) p.prof[((size_t)p.n_stages * gridDim.x + blockIdx.x) * kProfSlots + 2] = clock64();
+  if (p.prof && threadIdx.x == 0) {
+    long long* pr = p.prof + ((size_t)p.n_stages * gridDim.x + blockIdx.x) * kProfSlots;
+    pr[2] = clock64();
+    pr[4] = (long long)globaltimer_ns();
+  }
   if (cs.abort) {
     // let copies that were already issued land before the CTA's shared memory is released
     const unsigned long long t0 = globaltimer_ns();

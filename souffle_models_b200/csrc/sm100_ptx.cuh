@@ -310,6 +310,19 @@ __device__ __forceinline__ float gelu_tanh(float x) {
   const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
   return 0.5f * x * (1.0f + tanh_fast(u));
 }
+// The same GELU on a pair of fp16 values (the result is stored as fp16 anyway): six packed operations and
+// one packed tanh for two elements.  Overflow of x*x saturates tanh at +-1, which is the right limit.
+__device__ __forceinline__ uint32_t gelu_tanh_h2(uint32_t xw) {
+  const __half2 x = *reinterpret_cast<const __half2*>(&xw);
+  const __half2 c0 = __float2half2_rn(0.7978845608028654f), c1 = __float2half2_rn(0.7978845608028654f * 0.044715f);
+  const __half2 u = __hmul2(x, __hfma2(__hmul2(x, x), c1, c0));
+  uint32_t uw = *reinterpret_cast<const uint32_t*>(&u), tw;
+  asm("tanh.approx.f16x2 %0, %1;" : "=r"(tw) : "r"(uw));
+  const __half2 t = *reinterpret_cast<const __half2*>(&tw);
+  const __half2 hx = __hmul2(x, __float2half2_rn(0.5f));
+  const __half2 y = __hfma2(hx, t, hx);
+  return *reinterpret_cast<const uint32_t*>(&y);
+}
 __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
   __half2 h = __floats2half2_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&h);
