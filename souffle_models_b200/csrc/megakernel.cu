@@ -83,7 +83,7 @@ struct __align__(8) SmemCtl {
   uint64_t tmem_empty[2];
   uint64_t qk_full, qk_empty, v_full, v_empty, s_full, p_full, o_full;   // attention, pipeline 0
   uint64_t attn1[7];                                                     // attention, pipeline 1 (same order)
-  uint64_t ln_full[4];
+  uint64_t ln_full[4], ln_empty[4];
   uint32_t tmem_base;
   int abort;
   unsigned long long deadline_ns;   // read from the global timer once per CTA
@@ -1327,94 +1327,112 @@ __device__ __forceinline__ void ln_stage(const Stage& st, const MegaParams& p, S
   const __half* bias = reinterpret_cast<const __half*>(st.bias);
   const __half* gamma = reinterpret_cast<const __half*>(st.gamma);
   const __half* beta = reinterpret_cast<const __half*>(st.beta);
+  // Warp 0 only feeds the ring (issuing a bulk copy of tens of KB stalls the issuing thread until the copy
+  // engine has taken the previous ones); warps 1..9 normalise rows, two per warp and round.
+  constexpr int kComp = kThreads / 32 - 1;
+  // Batch geometry comes from the host (finalize_stage): rows per batch -- up to 96 KB so that two batches are
+  // in flight, at most two rows per warp, and few enough that every CTA gets work -- buffers, batch count.
   const int row_bytes = (P * 4 + (resid ? 2 : 0)) * N;
-  // rows per batch: up to 96 KB (two batches in flight), at most 20 rows, and few enough that every CTA gets work
-  int rb = 98304 / row_bytes;
-  rb = rb > 20 ? 20 : (rb < 1 ? 1 : rb);
-  const int per_cta = (M + (int)gridDim.x - 1) / (int)gridDim.x;
-  if (rb > per_cta) rb = per_cta;
-  // bias | gamma | beta side by side in shared memory, when a CTA normalises enough rows to pay for the copy
-  const bool stage_vecs = 3 * N * 2 <= kVecBytes && per_cta >= 4;
-  if (rb > kThreads / 32) rb -= rb % (kThreads / 32);        // whole rounds of one or two rows per warp
-  const int batch_bytes = rb * row_bytes;
-  int nbuf = kRingBytes / batch_bytes;
-  nbuf = nbuf > kLnMaxBufs ? kLnMaxBufs : nbuf;
-  const int n_batches = (M + rb - 1) / rb;
-  const int nwarps = kThreads / 32;
-
-  auto issue = [&](int batch, int buf) {
-    const int row0 = batch * rb;
-    const int rows = (M - row0) < rb ? (M - row0) : rb;
-    const uint32_t bar = smem_u32(&cs.ln_full[buf]);
-    const uint32_t dst = ring + buf * batch_bytes;
-    mbar_expect_tx(bar, (uint32_t)(rows * row_bytes));
-    for (int pl = 0; pl < P; ++pl)
-      bulk_load(dst + pl * rb * N * 4, st.partial + ((size_t)pl * M + row0) * N, (uint32_t)(rows * N * 4), bar);
-    if (resid) bulk_load(dst + P * rb * N * 4, resid + (size_t)row0 * N, (uint32_t)(rows * N * 2), bar);
-  };
-
-  if (threadIdx.x == 0) {
-    int b = blockIdx.x;
-    for (int j = 0; j < nbuf && b < n_batches; ++j, b += gridDim.x) issue(b, j);
-  }
-  // The per-column vectors go to shared memory once (while the first batches are in flight): read from global
-  // memory inside the row loop, a miss in the small L1 costs an L2 round trip in the middle of every row.
-  if (stage_vecs) {
-    const __half* srcs[3] = {bias, gamma, beta};
-#pragma unroll
-    for (int v = 0; v < 3; ++v) {
-      if (!srcs[v]) continue;
-      const uint2* src = reinterpret_cast<const uint2*>(srcs[v]);
-      uint2* dst = reinterpret_cast<uint2*>(vec_s + v * N);
-      for (int i = threadIdx.x; i < N / 4; i += kThreads) dst[i] = __ldg(src + i);
-    }
-    __syncthreads();
-    if (bias) bias = vec_s;
-    if (gamma) { gamma = vec_s + N; beta = vec_s + 2 * N; }
-  }
-  int k = 0;
+  const int rb = st.bm, batch_bytes = st.slot_bytes, nbuf = st.nslots, n_batches = st.items;
+  const bool stage_vecs = st.kchunks != 0;   // bias | gamma | beta side by side in shared memory
+  const int my_batches = n_batches > (int)blockIdx.x ? (n_batches - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  const uint32_t full0 = smem_u32(&cs.ln_full[0]), empty0 = smem_u32(&cs.ln_empty[0]);
+  uint32_t bits = rs.ln_bits;
   const bool prof = p.prof != nullptr;
-  long long t_wait = 0, t_sync = 0;
-  for (int batch = blockIdx.x; batch < n_batches; batch += gridDim.x, ++k) {
-    const int buf = k % nbuf;
-    const long long tw = prof ? clock64() : 0;
-    const bool ok = mbar_wait_warp(smem_u32(&cs.ln_full[buf]), (rs.ln_bits >> buf) & 1u, ctl, 600 + buf, lane);
-    if (prof) t_wait += clock64() - tw;
-    rs.ln_bits ^= 1u << buf;
-    if (!ok) break;
-    const int row0 = batch * rb;
-    const int rows = (M - row0) < rb ? (M - row0) : rb;
-    const float* base = reinterpret_cast<const float*>(ring_ptr + buf * batch_bytes);
-    const __half* rbase = reinterpret_cast<const __half*>(ring_ptr + buf * batch_bytes + P * rb * N * 4);
-    for (int r = warp; r < rows; r += 2 * nwarps) {
-      const int r2 = r + nwarps;
-      const bool two = r2 < rows;
-      const float* pl0 = base + (size_t)r * N;
-      const float* pl1 = two ? base + (size_t)r2 * N : nullptr;
-      const __half* ra = resid ? rbase + (size_t)r * N : nullptr;
-      const __half* rb2 = (resid && two) ? rbase + (size_t)r2 * N : nullptr;
-      __half* o0 = out + (size_t)(row0 + r) * N;
-      __half* o1 = two ? out + (size_t)(row0 + r2) * N : nullptr;
-      switch (N >> 7) {
-        case 1: ln_rows2<1>(pl0, pl1, P, rb * N, ra, rb2, bias, gamma, beta, st.eps, o0, o1, lane); break;
-        case 2: ln_rows2<2>(pl0, pl1, P, rb * N, ra, rb2, bias, gamma, beta, st.eps, o0, o1, lane); break;
-        case 4: ln_rows2<4>(pl0, pl1, P, rb * N, ra, rb2, bias, gamma, beta, st.eps, o0, o1, lane); break;
-        case 6: ln_rows2<6>(pl0, pl1, P, rb * N, ra, rb2, bias, gamma, beta, st.eps, o0, o1, lane); break;
-        default: ln_rows2<8>(pl0, pl1, P, rb * N, ra, rb2, bias, gamma, beta, st.eps, o0, o1, lane); break;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      if (prof) p.prof[((size_t)st.prof_index * gridDim.x + blockIdx.x) * kProfSlots + 9] = clock64();
+      int buf = 0;
+      for (int k = 0; k < my_batches; ++k) {
+        const int batch = blockIdx.x + k * gridDim.x;
+        if (!mbar_wait(empty0 + 8 * buf, ((bits >> buf) & 1u) ^ 1u, ctl, 610 + buf)) break;
+        const int row0 = batch * rb;
+        const int rows = (M - row0) < rb ? (M - row0) : rb;
+        const uint32_t bar = full0 + 8 * buf;
+        const uint32_t dst = ring + buf * batch_bytes;
+        mbar_expect_tx(bar, (uint32_t)(rows * row_bytes));
+        for (int pl = 0; pl < P; ++pl)
+          bulk_load(dst + pl * rb * N * 4, st.partial + ((size_t)pl * M + row0) * N, (uint32_t)(rows * N * 4), bar);
+        if (resid) bulk_load(dst + P * rb * N * 4, resid + (size_t)row0 * N, (uint32_t)(rows * N * 2), bar);
+        bits ^= 1u << buf;
+        buf = buf + 1 == nbuf ? 0 : buf + 1;
       }
+      if (prof) p.prof[((size_t)st.prof_index * gridDim.x + blockIdx.x) * kProfSlots + 10] = clock64();
     }
-    const long long ts = prof ? clock64() : 0;
-    __syncthreads();                       // every warp is done with this buffer before it is refilled
-    if (prof) t_sync += clock64() - ts;
-    const int next = batch + nbuf * (int)gridDim.x;
-    if (threadIdx.x == 0 && next < n_batches) issue(next, buf);
+    __syncwarp();
+  } else {
+    const int cw = warp - 1;
+    // The per-column vectors go to shared memory once (while the first batches are in flight): read from global
+    // memory inside the row loop, a miss in the small L1 costs an L2 round trip in the middle of every row.
+    if (stage_vecs) {
+      const __half* srcs[3] = {bias, gamma, beta};
+#pragma unroll
+      for (int v = 0; v < 3; ++v) {
+        if (!srcs[v]) continue;
+        const uint2* src = reinterpret_cast<const uint2*>(srcs[v]);
+        uint2* dst = reinterpret_cast<uint2*>(vec_s + v * N);
+        for (int i = threadIdx.x - 32; i < N / 4; i += kThreads - 32) dst[i] = __ldg(src + i);
+      }
+      named_barrier_sync(2, kThreads - 32);
+      if (bias) bias = vec_s;
+      if (gamma) { gamma = vec_s + N; beta = vec_s + 2 * N; }
+    }
+    unsigned t_wait = 0, t_comp = 0;
+    int buf = 0;
+    for (int k = 0; k < my_batches; ++k) {
+      const int batch = blockIdx.x + k * gridDim.x;
+      const unsigned tw = prof ? (unsigned)clock64() : 0u;
+      const bool ok = mbar_wait_warp(full0 + 8 * buf, (bits >> buf) & 1u, ctl, 600 + buf, lane);
+      const unsigned tc = prof ? (unsigned)clock64() : 0u;
+      t_wait += tc - tw;
+      bits ^= 1u << buf;
+      if (!ok) break;
+      const int row0 = batch * rb;
+      const int rows = (M - row0) < rb ? (M - row0) : rb;
+      const float* base = reinterpret_cast<const float*>(ring_ptr + buf * batch_bytes);
+      const __half* rbase = reinterpret_cast<const __half*>(ring_ptr + buf * batch_bytes + P * rb * N * 4);
+      for (int r = cw; r < rows; r += 2 * kComp) {
+        const int r2 = r + kComp;
+        const bool two = r2 < rows;
+        const float* pl0 = base + (size_t)r * N;
+        const float* pl1 = two ? base + (size_t)r2 * N : nullptr;
+        const __half* ra = resid ? rbase + (size_t)r * N : nullptr;
+        const __half* rb2 = (resid && two) ? rbase + (size_t)r2 * N : nullptr;
+        __half* o0 = out + (size_t)(row0 + r) * N;
+        __half* o1 = two ? out + (size_t)(row0 + r2) * N : nullptr;
+        switch (N >> 7) {
+          case 1: ln_rows2<1>(pl0, pl1, P, rb * N, ra, rb2, bias, gamma, beta, st.eps, o0, o1, lane); break;
+          case 2: ln_rows2<2>(pl0, pl1, P, rb * N, ra, rb2, bias, gamma, beta, st.eps, o0, o1, lane); break;
+          case 4: ln_rows2<4>(pl0, pl1, P, rb * N, ra, rb2, bias, gamma, beta, st.eps, o0, o1, lane); break;
+          case 6: ln_rows2<6>(pl0, pl1, P, rb * N, ra, rb2, bias, gamma, beta, st.eps, o0, o1, lane); break;
+          default: ln_rows2<8>(pl0, pl1, P, rb * N, ra, rb2, bias, gamma, beta, st.eps, o0, o1, lane); break;
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty0 + 8 * buf);    // this warp is done with the buffer
+      if (prof) t_comp += (unsigned)clock64() - tc;
+      buf = buf + 1 == nbuf ? 0 : buf + 1;
+    }
+    if (prof && lane == 0)
+      atomicMax(reinterpret_cast<unsigned long long*>(p.prof + ((size_t)st.prof_index * gridDim.x + blockIdx.x) * kProfSlots + 11),
+                (unsigned long long)clock64());
+    if (prof && warp == 2 && lane == 0) {    // [3] waiting for a batch, [7] normalising
+      long long* pr = p.prof + ((size_t)st.prof_index * gridDim.x + blockIdx.x) * kProfSlots;
+      pr[3] = t_wait;
+      pr[4] = 0;
+      pr[5] = rb;
+      pr[6] = nbuf;
+      pr[7] = t_comp;
+      pr[8] = my_batches;
+    }
   }
-  if (prof && warp == 2 && lane == 0) {    // [3] waiting for a batch, [4] waiting for the other warps
-    long long* pr = p.prof + ((size_t)st.prof_index * gridDim.x + blockIdx.x) * kProfSlots;
-    pr[3] = t_wait;
-    pr[4] = t_sync;
-    pr[5] = rb;
-    pr[6] = nbuf;
+  // every thread leaves with the same view of the buffers' phase bits
+  {
+    const int q = my_batches / nbuf, rem = my_batches - q * nbuf;     // buffers 0..rem-1 were used q+1 times
+    uint32_t flip = (q & 1) ? (1u << nbuf) - 1u : 0u;
+    if (rem) flip ^= (1u << rem) - 1u;
+    rs.ln_bits ^= flip;
   }
 }
 
@@ -1472,7 +1490,10 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
     mbar_init(smem_u32(&cs.p_full), 128);
     mbar_init(smem_u32(&cs.o_full), 1);
     for (int i = 0; i < 7; ++i) mbar_init(smem_u32(&cs.attn1[i]), i == 5 ? 128 : 1);
-    for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&cs.ln_full[i]), 1);
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(smem_u32(&cs.ln_full[i]), 1);
+      mbar_init(smem_u32(&cs.ln_empty[i]), kThreads / 32 - 1);
+    }
     cs.abort = 0;
     cs.deadline_ns = globaltimer_ns() + p.timeout_ns;
     fence_mbar_init();

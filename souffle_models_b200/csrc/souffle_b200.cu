@@ -190,12 +190,32 @@ static int stage_items(const Stage& s) {
   if (s.type == STAGE_GEMM) return ((s.M + s.bm - 1) / s.bm) * (s.N / s.bn) * s.splitk;
   if (s.type == STAGE_ATTN) return s.batch * s.heads * ((s.seq + 127) / 128);
   if (s.type == STAGE_ATTN_SWIN) return s.batch * (s.seq / s.win) * (s.seq / s.win) * s.heads;
-  return (s.M + kThreads / 32 - 1) / (kThreads / 32);
+  return (s.M + kThreads / 32 - 2) / (kThreads / 32 - 1);       // one row per normalising warp (all warps but the first)
 }
 
 // Fills the derived fields of a GEMM stage (tile counts, ring geometry, magic divisors) and checks that its
 // output fits the kernel's 32-bit element offsets.
-static int finalize_stage(Stage& s, int max_slots) {
+static int finalize_stage(Stage& s, int max_slots, int grid) {
+  if (s.type == STAGE_LN) {
+    // Rows per batch: up to 96 KB (two batches in flight), at most two rows per normalising warp, and few
+    // enough that every CTA gets work.  The per-column vectors are staged in shared memory when a CTA
+    // normalises enough rows to pay for the copy.
+    const int comp = kThreads / 32 - 1;
+    const bool has_resid = s.resid != nullptr || s.resid_sel != PTR_PLAN;
+    const int row_bytes = (s.n_partial * 4 + (has_resid ? 2 : 0)) * s.N;
+    int rb = 98304 / row_bytes;
+    rb = rb > 2 * comp ? 2 * comp : (rb < 1 ? 1 : rb);
+    const int per_cta = (s.M + grid - 1) / grid;
+    if (rb > per_cta) rb = per_cta;
+    if (rb > comp) rb -= rb % comp;
+    s.bm = rb;
+    s.slot_bytes = rb * row_bytes;
+    s.nslots = 196608 / s.slot_bytes > 4 ? 4 : 196608 / s.slot_bytes;
+    s.items = (s.M + rb - 1) / rb;
+    s.kchunks = (3 * s.N * 2 <= 8192 && per_cta >= 4) ? 1 : 0;
+    if (s.nslots < 1) return fail(SOUFFLE_BAD_SHAPE, "LayerNorm rows of %d bytes do not fit the staging ring", row_bytes);
+    return SOUFFLE_OK;
+  }
   if (s.type != STAGE_GEMM) return SOUFFLE_OK;
   s.tiles_n = s.N / s.bn;
   s.kchunks = s.K / 64 / s.splitk;
@@ -458,7 +478,7 @@ static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* la
     SF_CUDA(cudaMemset(p->d_prof, 0, pb));
   }
   for (Stage& fs : p->stages)
-    if ((rc = finalize_stage(fs, p->desc.debug_max_slots & 0xFF))) return rc;
+    if ((rc = finalize_stage(fs, p->desc.debug_max_slots & 0xFF, p->grid))) return rc;
   if ((rc = plan_alloc(p, (void**)&p->d_stages, p->stages.size() * sizeof(Stage)))) return rc;
   if ((rc = plan_alloc(p, (void**)&p->d_maps, p->maps.size() * sizeof(CUtensorMap)))) return rc;
   SF_CUDA(cudaMemcpy(p->d_stages, p->stages.data(), p->stages.size() * sizeof(Stage), cudaMemcpyHostToDevice));
@@ -667,7 +687,7 @@ static int fill_gemm_stage(Stage* s, int tm_a, int tm_b, const void* out, int M,
   if (!t.bn) return fail(SOUFFLE_BAD_SHAPE, "N=%d must be a multiple of 64", N);
   s->tm_a = tm_a; s->tm_b = tm_b; s->M = M; s->N = N; s->K = K; s->bm = t.bm; s->bn = t.bn; s->b_mn_major = 1;
   s->epi = EPI_F16; s->out = const_cast<void*>(out); s->ldo = N;
-  return finalize_stage(*s, 0);
+  return finalize_stage(*s, 0, 1);
 }
 
 int souffle_gemm_f16(const void* a, const void* w_kn, void* c, int32_t M, int32_t N, int32_t K, void* workspace,
@@ -741,7 +761,9 @@ int souffle_layernorm_forward(const float* partial, int32_t n_partial, const voi
   args.p.n_stages = 1;
   const int sms = di->sms < di->max_ctas ? di->sms : di->max_ctas;
   const int items = stage_items(s);
-  return launch_mega(args, items < sms ? items : sms, st);
+  const int grid = items < sms ? items : sms;
+  if ((rc = finalize_stage(s, 0, grid))) return rc;
+  return launch_mega(args, grid, st);
 }
 
 // ======================================================================================
@@ -785,7 +807,7 @@ static int finish_plan(SouffleBertPlan* p, int sms) {
   }
   p->grid = max_items < sms ? max_items : sms;
   for (Stage& fs : p->stages)
-    if ((rc = finalize_stage(fs, p->desc.debug_max_slots & 0xFF))) return rc;
+    if ((rc = finalize_stage(fs, p->desc.debug_max_slots & 0xFF, p->grid))) return rc;
   if ((rc = plan_alloc(p, (void**)&p->d_stages, p->stages.size() * sizeof(Stage)))) return rc;
   if ((rc = plan_alloc(p, (void**)&p->d_maps, p->maps.size() * sizeof(CUtensorMap)))) return rc;
   SF_CUDA(cudaMemcpy(p->d_stages, p->stages.data(), p->stages.size() * sizeof(Stage), cudaMemcpyHostToDevice));
