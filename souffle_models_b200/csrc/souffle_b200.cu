@@ -212,7 +212,7 @@ static int finalize_stage(Stage& s, int max_slots, int grid) {
     s.slot_bytes = rb * row_bytes;
     s.nslots = 196608 / s.slot_bytes > 4 ? 4 : 196608 / s.slot_bytes;
     s.items = (s.M + rb - 1) / rb;
-    s.kchunks = (3 * s.N * 2 <= 8192 && per_cta >= 4) ? 1 : 0;
+    s.kchunks = (3 * s.N * 2 <= 8192) ? 1 : 0;
     if (s.nslots < 1) return fail(SOUFFLE_BAD_SHAPE, "LayerNorm rows of %d bytes do not fit the staging ring", row_bytes);
     return SOUFFLE_OK;
   }
