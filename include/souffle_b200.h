@@ -194,7 +194,9 @@ int souffle_lstm_forward_static(const SouffleLstmDesc* desc, const void* w_in, c
  * Replaces swin_ffn (swin_transformer_binding.cu:62-100, shapes (256,2048,512),(256,512,2048))
  * and swin_trans_fc2 (swin_trans_fc2_binding.cu:19-55) for any K % 64 == 0, N % 64 == 0.
  * `workspace` must hold souffle_gemm_workspace_bytes() bytes and is reusable across calls
- * that do not overlap.
+ * that do not overlap.  The library clears it the first time it sees the address and keeps the barrier words
+ * consistent from call to call; nobody else may write its first 128 bytes in between (a workspace that was
+ * handed out again with other contents costs one call that ends in SOUFFLE_DEVICE_TIMEOUT).
  * ------------------------------------------------------------------------------------------ */
 size_t souffle_gemm_workspace_bytes(void);
 int souffle_gemm_f16(const void* a, const void* w_kn, void* c, int32_t M, int32_t N, int32_t K,
@@ -202,7 +204,11 @@ int souffle_gemm_f16(const void* a, const void* w_kn, void* c, int32_t M, int32_
 
 /* fc1 -> grid barrier -> fc2 in one launch, no bias/activation, both results returned:
  * hidden[M][F] = src[M][C] . fc1_w[C][F];  out[M][C] = hidden . fc2_w[F][C]
- * (cpp/swin_transformer/swin_transformer_binding.cu:155-209). */
+ * (cpp/swin_transformer/swin_transformer_binding.cu:155-209).  With a workspace of
+ * souffle_swin_mlp_workspace_bytes(M, C, F) bytes fc2 is cut along K into fp32 planes that a third stage of the
+ * same launch sums (the reference's fc2 runs its long K loop on 32 blocks, kernels/swin_fused_ffn_*.cu:393);
+ * with only souffle_gemm_workspace_bytes() it runs unsplit. */
+size_t souffle_swin_mlp_workspace_bytes(int32_t M, int32_t C, int32_t F);
 int souffle_swin_mlp_forward(const void* src, const void* fc1_w, const void* fc2_w, void* hidden, void* out,
                              int32_t M, int32_t C, int32_t F, void* workspace, size_t workspace_bytes,
                              souffle_stream_t stream);

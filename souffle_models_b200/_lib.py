@@ -69,6 +69,7 @@ SIGNATURES = {
     "souffle_gemm_workspace_bytes": (C.c_size_t, []),
     "souffle_gemm_f16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
                                    C.c_void_p, C.c_size_t, C.c_void_p]),
+    "souffle_swin_mlp_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32]),
     "souffle_swin_mlp_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
                                            C.c_int32, C.c_int32, C.c_void_p, C.c_size_t, C.c_void_p]),
     "souffle_layernorm_forward": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,

@@ -69,7 +69,7 @@ struct MegaParams {
 constexpr int kCallMaps = 4;
 struct CallArgs {
   CUtensorMap call_maps[kCallMaps];
-  Stage inline_stages[2];
+  Stage inline_stages[3];
   MegaParams p;
 };
 __device__ __forceinline__ const CUtensorMap* map_ptr(const CallArgs& a, int idx) {
@@ -1264,6 +1264,14 @@ __device__ __forceinline__ void ln_rows2(const float* pl0, const float* pl1, int
 #pragma unroll
       for (int i = 0; i < 4; ++i) z[r][j][i] += add[i] + rr[i];
     }
+  }
+  if (eps < 0.0f) {                     // sum only: the split-K reduction of a GEMM whose consumer reads fp16
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+      *reinterpret_cast<uint2*>(out0 + (lane + 32 * j) * 4) = make_uint2(pack_h2(z[0][j][0], z[0][j][1]), pack_h2(z[0][j][2], z[0][j][3]));
+      if (two) *reinterpret_cast<uint2*>(out1 + (lane + 32 * j) * 4) = make_uint2(pack_h2(z[1][j][0], z[1][j][1]), pack_h2(z[1][j][2], z[1][j][3]));
+    }
+    return;
   }
   const float inv_n = 1.0f / (float)(NJ * 128);
   float sa = 0.0f, sb = 0.0f;

@@ -13,7 +13,9 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 #include "../../include/souffle_b200.h"
@@ -670,12 +672,30 @@ int souffle_bert_plan_stage_info(SouffleBertPlan* plan, int index, int out[6]) {
 // ======================================================================================
 size_t souffle_gemm_workspace_bytes(void) { return 256; }
 
+// The barrier words of a caller-owned workspace: two (count, spare) pairs used by alternate launches; the
+// kernel clears the pair of the NEXT launch in its prologue (see souffle_megakernel), so the workspace needs a
+// memset only the first time this library sees it, and a launch that ended in a device timeout leaves the
+// other pair clean for the call after it.
+static std::mutex g_ws_mutex;
+static std::unordered_map<const void*, unsigned> g_ws_launches;
+
 static int ws_prepare(void* workspace, size_t ws_bytes, cudaStream_t st, MegaParams* mp) {
   if (!aligned16(workspace) || ws_bytes < souffle_gemm_workspace_bytes())
     return fail(SOUFFLE_BAD_POINTER, "workspace must be 16-byte aligned and hold %zu bytes", souffle_gemm_workspace_bytes());
-  SF_CUDA(cudaMemsetAsync(workspace, 0, 128, st));
-  mp->sync = reinterpret_cast<unsigned*>(workspace);
-  mp->sync_next = mp->sync + 2;
+  unsigned launch = 0;
+  {
+    std::lock_guard<std::mutex> lock(g_ws_mutex);
+    auto it = g_ws_launches.find(workspace);
+    if (it == g_ws_launches.end()) {
+      SF_CUDA(cudaMemsetAsync(workspace, 0, 128, st));
+      g_ws_launches.emplace(workspace, 1u);
+    } else {
+      launch = it->second++;
+    }
+  }
+  const unsigned par = launch & 1u;
+  mp->sync = reinterpret_cast<unsigned*>(workspace) + 2 * par;
+  mp->sync_next = reinterpret_cast<unsigned*>(workspace) + 2 * (par ^ 1u);
   mp->status = reinterpret_cast<int*>(reinterpret_cast<char*>(workspace) + 64);
   mp->timeout_ns = 2000ull * 1000000ull;
   return SOUFFLE_OK;
@@ -711,6 +731,19 @@ int souffle_gemm_f16(const void* a, const void* w_kn, void* c, int32_t M, int32_
   return launch_mega(args, items < sms ? items : sms, st);
 }
 
+// FC2 of the MLP has few output tiles and a long K (256 x 512 outputs, K = 2048 in the reference's shape), so
+// it is cut along K into fp32 planes and a third stage sums them: the LayerNorm stage in its sum-only mode.
+// The planes live behind the barrier words of the workspace.
+static int swin_mlp_split(int M, int C, int F, int sms) {
+  const TileChoice t = choose_tiles(M, C, F, sms, true, true);
+  return t.bn ? t.split : 1;
+}
+
+size_t souffle_swin_mlp_workspace_bytes(int32_t M, int32_t C, int32_t F) {
+  if (M < 1 || C < 64 || F < 64) return souffle_gemm_workspace_bytes();
+  return souffle_gemm_workspace_bytes() + (size_t)16 * M * C * sizeof(float);      // room for the deepest split
+}
+
 int souffle_swin_mlp_forward(const void* src, const void* fc1_w, const void* fc2_w, void* hidden, void* out, int32_t M,
                              int32_t C, int32_t F, void* workspace, size_t workspace_bytes, souffle_stream_t stream) {
   if (M < 1 || C < 64 || C % 64 || F < 64 || F % 64)
@@ -726,16 +759,39 @@ int souffle_swin_mlp_forward(const void* src, const void* fc1_w, const void* fc2
   if ((rc = ws_prepare(workspace, workspace_bytes, st, &args.p))) return rc;
   const int sms = di->sms < di->max_ctas ? di->sms : di->max_ctas;
   if ((rc = fill_gemm_stage(&args.inline_stages[0], -1, -2, hidden, M, F, C, sms))) return rc;
-  if ((rc = fill_gemm_stage(&args.inline_stages[1], -3, -4, out, M, C, F, sms))) return rc;
+  // split FC2 when the caller's workspace has room for the planes and the reduction stage supports the width
+  int split = swin_mlp_split(M, C, F, sms);
+  const bool can_reduce = C == 128 || C == 256 || C == 512 || C == 768 || C == 1024;
+  const size_t plane_bytes = (size_t)M * C * sizeof(float);
+  if (!can_reduce || workspace_bytes < souffle_gemm_workspace_bytes() + (size_t)split * plane_bytes) split = 1;
+  Stage& s2 = args.inline_stages[1];
+  if (split > 1) {
+    const TileChoice t = choose_tiles(M, C, F, sms, true, true);
+    s2 = blank_stage(STAGE_GEMM);
+    s2.tm_a = -3; s2.tm_b = -4; s2.M = M; s2.N = C; s2.K = F; s2.bm = t.bm; s2.bn = t.bn; s2.splitk = split; s2.b_mn_major = 1;
+    s2.epi = EPI_PARTIAL; s2.ldo = C;
+    s2.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + souffle_gemm_workspace_bytes());
+    if ((rc = finalize_stage(s2, 0, 1))) return rc;
+  } else if ((rc = fill_gemm_stage(&s2, -3, -4, out, M, C, F, sms))) {
+    return rc;
+  }
   if ((rc = make_map(&args.call_maps[0], src, M, C, (uint32_t)args.inline_stages[0].bm))) return rc;
   if ((rc = make_map(&args.call_maps[1], fc1_w, C, F, 64))) return rc;
-  if ((rc = make_map(&args.call_maps[2], hidden, M, F, (uint32_t)args.inline_stages[1].bm))) return rc;
+  if ((rc = make_map(&args.call_maps[2], hidden, M, F, (uint32_t)s2.bm))) return rc;
   if ((rc = make_map(&args.call_maps[3], fc2_w, F, C, 64))) return rc;
-  args.p.n_stages = 2;
+  args.p.n_stages = split > 1 ? 3 : 2;
   int items = stage_items(args.inline_stages[0]);
-  const int i2 = stage_items(args.inline_stages[1]);
+  const int i2 = stage_items(s2);
   if (i2 > items) items = i2;
-  return launch_mega(args, items < sms ? items : sms, st);
+  const int grid = items < sms ? items : sms;
+  if (split > 1) {
+    Stage& s3 = args.inline_stages[2];
+    s3 = blank_stage(STAGE_LN);
+    s3.M = M; s3.N = C; s3.ldo = C; s3.partial = s2.partial; s3.n_partial = split; s3.out = out;
+    s3.eps = -1.0f;                                    // sum only
+    if ((rc = finalize_stage(s3, 0, grid))) return rc;
+  }
+  return launch_mega(args, grid, st);
 }
 
 int souffle_layernorm_forward(const float* partial, int32_t n_partial, const void* bias, const void* resid,
@@ -1119,6 +1175,10 @@ int souffle_workspace_status(void* workspace, souffle_stream_t stream) {
   SF_CUDA(cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(stream)));
   int h[4] = {0, 0, 0, 0};
   SF_CUDA(cudaMemcpy(h, reinterpret_cast<char*>(workspace) + 64, sizeof(h), cudaMemcpyDeviceToHost));
+  if (h[0] != DEV_OK) {                 // start over: the next call on this workspace clears all of it
+    std::lock_guard<std::mutex> lock(g_ws_mutex);
+    g_ws_launches.erase(workspace);
+  }
   return decode_status(h, "souffle workspace");
 }
 

@@ -13,10 +13,12 @@ from .bert import _check_f16_cuda, _stream_ptr
 _ws = {}
 
 
-def _workspace() -> torch.Tensor:
+def _workspace(nbytes: int = 0) -> torch.Tensor:
+    """Per-device scratch for the plan-less entry points (barrier words, then split-K planes); grows on demand."""
     dev = torch.cuda.current_device()
-    if dev not in _ws:
-        _ws[dev] = torch.zeros(int(_lib.load().souffle_gemm_workspace_bytes()), dtype=torch.uint8, device="cuda")
+    need = max(int(nbytes), int(_lib.load().souffle_gemm_workspace_bytes()))
+    if dev not in _ws or _ws[dev].numel() < need:
+        _ws[dev] = torch.zeros(need, dtype=torch.uint8, device="cuda")
     return _ws[dev]
 
 
@@ -64,8 +66,8 @@ def swin_fused_feed_mlp(src: torch.Tensor, fc1_weight: torch.Tensor, fc2_weight:
         raise ValueError("fc1_weight must be [C,F] and fc2_weight [F,C]")
     hidden = torch.empty(M, F, dtype=torch.float16, device=src.device)
     out = torch.empty(M, Cc, dtype=torch.float16, device=src.device)
-    ws = _workspace()
     lib = _lib.load()
+    ws = _workspace(lib.souffle_swin_mlp_workspace_bytes(M, Cc, F))
     _lib.check(lib.souffle_swin_mlp_forward(src.data_ptr(), fc1_weight.data_ptr(), fc2_weight.data_ptr(),
                                             hidden.data_ptr(), out.data_ptr(), M, Cc, F, ws.data_ptr(), ws.numel(),
                                             _stream_ptr()))
