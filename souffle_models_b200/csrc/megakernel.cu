@@ -608,7 +608,7 @@ __device__ __forceinline__ void gemm_stage(const Stage& st, const CallArgs& ca, 
 // attention stage: one work item = (sequence, head, 128-query tile); S <= 384, head_dim 64
 // ------------------------------------------------------------------------------------
 __device__ __forceinline__ void attn_stage(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, uint32_t ring, uint8_t* ring_ptr,
-                           RoleState& rs, const WaitCtl& ctl, int warp, int lane) {
+                                           uint8_t* stage_s, RoleState& rs, const WaitCtl& ctl, int warp, int lane) {
   const MegaParams& p = ca.p;
   const int S = st.seq, B = st.batch, H = st.heads;
   const int n_kb = (S + 127) / 128;
@@ -667,122 +667,156 @@ __device__ __forceinline__ void attn_stage(const Stage& st, const CallArgs& ca, 
       }
     }
     __syncwarp();
-  } else if (warp < 6) {
-    const int q = warp & 3;
+  } else {
+    // Both groups of four warps work on the same item: group 0 takes the first half of the 16-key blocks, group 1
+    // the second half (a thread of each group owns query row r_in); row maxima and row sums are exchanged through
+    // shared memory around two 256-thread barriers.  The output columns are split 32 / 32 likewise.
+    const int grp = (warp - 2) >> 2, q = warp & 3;
     const int r_in = q * 32 + lane;
     const uint32_t tmem = ctl_s.tmem_base + ((uint32_t)(q * 32) << 16);
     const float sl2 = st.scale * 1.4426950408889634f;
-    const float mask_l2 = -10000.0f * 1.4426950408889634f;
     const int* lens = st.lens_from_call ? p.lens : st.lens;
     __half* ctx = reinterpret_cast<__half*>(st.out);
     __half* probs = reinterpret_cast<__half*>(st.probs);
     const int hidden = H * st.head_dim;
+    // At S = 384 the tiles of this stage (Q, 3 K, 3 V, 6 P = 208 KB) run past the 192 KB ring into the vector and
+    // staging areas behind it, which no one else uses during attention; the exchange buffer sits at their very end.
+    static_assert(13 * kATileBytes <= kRingBytes + kVecBytes + kStageBytes - 2048, "attention tiles overlap the exchange buffer");
+    float* red = reinterpret_cast<float*>(stage_s + kStageBytes - 2048);   // [2 groups][128 rows] maxima, then [2][128] sums
     for (int item = blockIdx.x; item < items; item += gridDim.x) {
       const int qt = item % n_kb, h = (item / n_kb) % H, b = item / (n_kb * H);
       const int kv_len = lens ? lens[b] : S;
       bool ok = mbar_wait_warp(s_full, rs.attn_bit, ctl, 520, lane);
       if (!ok) break;
       tc_fence_after_sync();
-      const int n_chunks = n_kb * 4;
-      // pass 1: row maximum of the scaled, masked scores (base-2 domain)
-      float mx = -INFINITY;
-      for (int c = 0; c < n_chunks; ++c) {
-        if (c * 32 >= S) break;
-        uint32_t r[32];
-        tmem_ld32(tmem + c * 32, r);
-        tmem_ld_wait();
-        if (c * 32 + 32 <= kv_len) {
+      // Keys >= kv_len carry the additive -1e4 mask: probability 0 in fp32, never the maximum -> only the blocks
+      // with valid keys are visited; the other P blocks are written as zeros.
+      const int kvl = kv_len < 1 ? 1 : (kv_len > S ? S : kv_len);
+      const int nb = (kvl + 15) >> 4, nb_all = n_kb * 8;
+      const int nb_half = (nb + 1) >> 1;
+      const int blk0 = grp ? nb_half : 0, blk1 = grp ? nb : nb_half;       // this group's valid blocks
+      uint32_t ra[16], rb[16];
+      // ---- pass 1: maximum of the raw scores of the valid keys (the scale is positive) ----
+      float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+      auto max16 = [&](const uint32_t (&r)[16], int blk) {
+        const int key0 = blk * 16;
+        if (key0 + 16 <= kvl) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]) * sl2);
+          for (int i = 0; i < 16; i += 4) {
+            m0 = fmaxf(m0, __uint_as_float(r[i])); m1 = fmaxf(m1, __uint_as_float(r[i + 1]));
+            m2 = fmaxf(m2, __uint_as_float(r[i + 2])); m3 = fmaxf(m3, __uint_as_float(r[i + 3]));
+          }
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int key = c * 32 + i;
-            const float t = __uint_as_float(r[i]) * sl2 + (key >= kv_len ? mask_l2 : 0.0f);
-            if (key < S) mx = fmaxf(mx, t);
-          }
+          for (int i = 0; i < 16; ++i) m0 = fmaxf(m0, key0 + i < kvl ? __uint_as_float(r[i]) : -INFINITY);
+        }
+      };
+      if (blk0 < blk1) {
+        tmem_ld16(tmem + blk0 * 16, ra);
+        tmem_ld_wait(ra);
+      }
+      for (int blk = blk0; blk < blk1; blk += 2) {
+        if (blk + 1 < blk1) tmem_ld16(tmem + (blk + 1) * 16, rb);
+        max16(ra, blk);
+        if (blk + 1 < blk1) {
+          tmem_ld_wait(rb);
+          if (blk + 2 < blk1) tmem_ld16(tmem + (blk + 2) * 16, ra);
+          max16(rb, blk + 1);
+          if (blk + 2 < blk1) tmem_ld_wait(ra);
         }
       }
-      // pass 2: unnormalised probabilities -> fp16 A-operand tile in shared memory
-      float sum = 0.0f;
-      for (int c = 0; c < n_chunks; ++c) {
-        uint32_t w[16];
-        if (c * 32 >= S) {
+      red[grp * 128 + r_in] = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+      named_barrier_sync(3, 256);
+      const float mx = fmaxf(red[r_in], red[128 + r_in]) * sl2;
+      // ---- pass 2: unnormalised probabilities -> fp16 A-operand tiles (128B-swizzled rows, 64 keys per tile) ----
+      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+      uint8_t* pbase = ring_ptr + p_off + r_in * 128;
+      auto exp16 = [&](const uint32_t (&r)[16], int blk) {
+        const int key0 = blk * 16;
+        uint32_t w[8];
+        if (key0 + 16 <= kvl) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) w[i] = 0u;
+          for (int i = 0; i < 16; i += 4) {
+            const float p0 = ex2_fast(fmaf(__uint_as_float(r[i]), sl2, -mx)), p1 = ex2_fast(fmaf(__uint_as_float(r[i + 1]), sl2, -mx));
+            const float p2 = ex2_fast(fmaf(__uint_as_float(r[i + 2]), sl2, -mx)), p3 = ex2_fast(fmaf(__uint_as_float(r[i + 3]), sl2, -mx));
+            s0 += p0; s1 += p1; s2 += p2; s3 += p3;
+            w[i >> 1] = pack_h2(p0, p1);
+            w[(i >> 1) + 1] = pack_h2(p2, p3);
+          }
         } else {
-          uint32_t r[32];
-          tmem_ld32(tmem + c * 32, r);
-          tmem_ld_wait();
-          float pv[32];
-          if (c * 32 + 32 <= kv_len) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) pv[i] = ex2_fast(__uint_as_float(r[i]) * sl2 - mx);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int key = c * 32 + i;
-              const float t = __uint_as_float(r[i]) * sl2 + (key >= kv_len ? mask_l2 : 0.0f);
-              pv[i] = key < S ? ex2_fast(t - mx) : 0.0f;
-            }
+          for (int i = 0; i < 16; i += 2) {
+            const float p0 = key0 + i < kvl ? ex2_fast(fmaf(__uint_as_float(r[i]), sl2, -mx)) : 0.f;
+            const float p1 = key0 + i + 1 < kvl ? ex2_fast(fmaf(__uint_as_float(r[i + 1]), sl2, -mx)) : 0.f;
+            s0 += p0; s1 += p1;
+            w[i >> 1] = pack_h2(p0, p1);
           }
-#pragma unroll
-          for (int i = 0; i < 32; ++i) sum += pv[i];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) w[i] = pack_h2(pv[2 * i], pv[2 * i + 1]);
         }
-        uint8_t* base = ring_ptr + p_off + (c >> 1) * kATileBytes + r_in * 128;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int j = (c & 1) * 4 + i;
-          *reinterpret_cast<uint4*>(base + ((j ^ (r_in & 7)) << 4)) =
-              make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+        uint8_t* base = pbase + (blk >> 2) * kATileBytes;
+        const int j = (blk & 3) * 2;
+        *reinterpret_cast<uint4*>(base + ((j ^ (r_in & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(base + (((j + 1) ^ (r_in & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+      };
+      if (blk0 < blk1) {
+        tmem_ld16(tmem + blk0 * 16, ra);
+        tmem_ld_wait(ra);
+      }
+      for (int blk = blk0; blk < blk1; blk += 2) {
+        if (blk + 1 < blk1) tmem_ld16(tmem + (blk + 1) * 16, rb);
+        exp16(ra, blk);
+        if (blk + 1 < blk1) {
+          tmem_ld_wait(rb);
+          if (blk + 2 < blk1) tmem_ld16(tmem + (blk + 2) * 16, ra);
+          exp16(rb, blk + 1);
+          if (blk + 2 < blk1) tmem_ld_wait(ra);
         }
       }
-      const float inv = 1.0f / sum;
+      // keys past the valid ones: probability 0 (the two groups share the blocks alternately)
+      for (int blk = nb + grp; blk < nb_all; blk += 2) {
+        uint8_t* base = pbase + (blk >> 2) * kATileBytes;
+        const int j = (blk & 3) * 2;
+        *reinterpret_cast<uint4*>(base + ((j ^ (r_in & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(base + (((j + 1) ^ (r_in & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+      }
+      red[256 + grp * 128 + r_in] = (s0 + s1) + (s2 + s3);
+      fence_proxy_async_smem();                               // this thread's P rows -> visible to the MMA
+      named_barrier_sync(3, 256);
+      const float inv = 1.0f / (red[256 + r_in] + red[384 + r_in]);
       const int qrow = qt * 128 + r_in;
-      if (probs) {
+      if (probs && grp == 0) {
         // parity output: normalised probabilities [B*heads][S][S]
-        for (int c = 0; c < n_chunks && c * 32 < S; ++c) {
+        for (int c = 0; c < n_kb * 4 && c * 32 < S; ++c) {
           uint32_t r[32];
           tmem_ld32(tmem + c * 32, r);
-          tmem_ld_wait();
+          tmem_ld_wait(r);
           if (qrow < S) {
             __half* dst = probs + ((size_t)(b * H + h) * S + qrow) * S + c * 32;
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               const int key = c * 32 + i;
-              const float t = __uint_as_float(r[i]) * sl2 + (key >= kv_len ? mask_l2 : 0.0f);
-              if (key < S) dst[i] = __float2half_rn(ex2_fast(t - mx) * inv);
+              const float pv = key < kvl ? ex2_fast(fmaf(__uint_as_float(r[i]), sl2, -mx)) * inv : 0.0f;
+              if (key < S) dst[i] = __float2half_rn(pv);
             }
           }
         }
       }
-      fence_proxy_async_smem();
       tc_fence_before_sync();
-      mbar_arrive(p_full);
+      if (grp == 0) mbar_arrive(p_full);                      // 128 arrivals: group 1's rows are behind the barrier above
       ok = mbar_wait_warp(o_full, rs.attn_bit, ctl, 521, lane);
       if (!ok) break;
       tc_fence_after_sync();
       {
-        uint32_t r0[32], r1[32];
-        tmem_ld32(tmem + kOCol, r0);
-        tmem_ld32(tmem + kOCol + 32, r1);
-        tmem_ld_wait();
+        uint32_t r0[32];
+        tmem_ld32(tmem + kOCol + grp * 32, r0);               // this group's 32 of the 64 output columns
+        tmem_ld_wait(r0);
         if (qrow < S) {
-          uint4* dst = reinterpret_cast<uint4*>(ctx + ((size_t)b * S + qrow) * hidden + h * st.head_dim);
+          uint4* dst = reinterpret_cast<uint4*>(ctx + ((size_t)b * S + qrow) * hidden + h * st.head_dim + grp * 32);
 #pragma unroll
           for (int i = 0; i < 4; ++i)
             dst[i] = make_uint4(pack_h2(__uint_as_float(r0[8 * i]) * inv, __uint_as_float(r0[8 * i + 1]) * inv),
                                 pack_h2(__uint_as_float(r0[8 * i + 2]) * inv, __uint_as_float(r0[8 * i + 3]) * inv),
                                 pack_h2(__uint_as_float(r0[8 * i + 4]) * inv, __uint_as_float(r0[8 * i + 5]) * inv),
                                 pack_h2(__uint_as_float(r0[8 * i + 6]) * inv, __uint_as_float(r0[8 * i + 7]) * inv));
-#pragma unroll
-          for (int i = 0; i < 4; ++i)
-            dst[4 + i] = make_uint4(pack_h2(__uint_as_float(r1[8 * i]) * inv, __uint_as_float(r1[8 * i + 1]) * inv),
-                                    pack_h2(__uint_as_float(r1[8 * i + 2]) * inv, __uint_as_float(r1[8 * i + 3]) * inv),
-                                    pack_h2(__uint_as_float(r1[8 * i + 4]) * inv, __uint_as_float(r1[8 * i + 5]) * inv),
-                                    pack_h2(__uint_as_float(r1[8 * i + 6]) * inv, __uint_as_float(r1[8 * i + 7]) * inv));
         }
       }
       tc_fence_before_sync();
@@ -1449,10 +1483,14 @@ __device__ __forceinline__ void ln_stage(const Stage& st, const MegaParams& p, S
 // ------------------------------------------------------------------------------------
 // 320 threads leave 168 registers per thread (the register file is handed out per four warps); the
 // epilogue is written to stay below that without spilling.
-// The kernel exists in two builds.  <false> runs BERT layers, plain GEMMs and LayerNorm with every stage
-// inlined (fastest: one register allocation over the whole role code).  <true> adds the Swin epilogues and
-// the window-attention stage; with those inlined as well the allocation no longer fits 168 registers, so
-// that build keeps its stages out of line.
+// The kernel exists in three builds, so that each fits 168 registers with its stages inlined where that matters:
+//   kFamilyBert      BERT layers whose attention items outnumber the CTAs (two-pipeline attention), plain GEMMs,
+//                    LayerNorm; every stage inlined into one register allocation (fastest).
+//   kFamilyBertCoop  the same with the attention stage in which all eight softmax warps share one item: S up to
+//                    384, and short sequences at small batch, where a CTA has at most one item anyway.
+//   kFamilySwin      adds the Swin row-permuting epilogues and the window-attention stage; its stages stay out
+//                    of line (inlined as well, the allocation would no longer fit).
+constexpr int kFamilyBert = 0, kFamilyBertCoop = 1, kFamilySwin = 2;
 __device__ __noinline__ void gemm_stage_ool(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, uint32_t ring, __half* vec_s,
                                             uint8_t* stage_s, RoleState& rs, const WaitCtl& ctl, int warp, int lane) {
   gemm_stage<true>(st, ca, ctl_s, ring, vec_s, stage_s, rs, ctl, warp, lane);
@@ -1462,7 +1500,7 @@ __device__ __noinline__ void ln_stage_ool(const Stage& st, const MegaParams& p, 
   ln_stage(st, p, cs, ring, ring_ptr, vec_s, rs, ctl, warp, lane);
 }
 
-template <bool kSwin>
+template <int kFamily>
 __global__ void __launch_bounds__(kThreads, 1)
 souffle_megakernel(const __grid_constant__ CallArgs ca) {
   const MegaParams& p = ca.p;
@@ -1539,7 +1577,7 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
     __syncthreads();
     if (p.prof && threadIdx.x == 0) p.prof[((size_t)si * gridDim.x + blockIdx.x) * kProfSlots + 0] = clock64();
     const Stage& st = cs.stage;
-    if constexpr (kSwin) {
+    if constexpr (kFamily == kFamilySwin) {
       if (st.type == STAGE_GEMM) gemm_stage_ool(st, ca, cs, ring, vec_s, stage_s, rs, ctl, warp, lane);
       else if (st.type == STAGE_ATTN_SWIN) attn_swin_stage(st, ca, cs, ring, ring_ptr, stage_s, rs, ctl, warp, lane);
       else if (st.type == STAGE_LN) ln_stage_ool(st, p, cs, ring, ring_ptr, vec_s, rs, ctl, warp, lane);
@@ -1547,8 +1585,8 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
       if (st.type == STAGE_GEMM) {
         gemm_stage<false>(st, ca, cs, ring, vec_s, stage_s, rs, ctl, warp, lane);
       } else if (st.type == STAGE_ATTN) {
-        if (st.seq <= 128) attn_stage_pp(st, ca, cs, ring, ring_ptr, stage_s, rs, ctl, warp, lane);
-        else attn_stage(st, ca, cs, ring, ring_ptr, rs, ctl, warp, lane);
+        if constexpr (kFamily == kFamilyBert) attn_stage_pp(st, ca, cs, ring, ring_ptr, stage_s, rs, ctl, warp, lane);
+        else attn_stage(st, ca, cs, ring, ring_ptr, stage_s, rs, ctl, warp, lane);
       } else if (st.type == STAGE_LN) {
         ln_stage(st, p, cs, ring, ring_ptr, vec_s, rs, ctl, warp, lane);
       }

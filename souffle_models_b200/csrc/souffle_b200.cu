@@ -69,7 +69,32 @@ static EncodeTiledFn encode_fn() {
 
 // fp16 matrix [rows][cols] (cols contiguous), box = 64 columns x box_rows rows, 128B swizzle,
 // out-of-range elements read as zero.
+static int make_map_uncached(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows);
+
+// A tensor map is a pure function of (address, extents, box): the plan-less entry points, which encode four of
+// them per call, keep the last few per thread.
 static int make_map(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  struct Entry { const void* ptr; uint64_t rows, cols; uint32_t box; CUtensorMap map; };
+  constexpr int kEntries = 16;
+  static thread_local Entry cache[kEntries];
+  static thread_local int used = 0, next = 0;
+  for (int i = 0; i < used; ++i) {
+    const Entry& e = cache[i];
+    if (e.ptr == ptr && e.rows == rows && e.cols == cols && e.box == box_rows) {
+      *m = e.map;
+      return SOUFFLE_OK;
+    }
+  }
+  const int rc = make_map_uncached(m, ptr, rows, cols, box_rows);
+  if (rc) return rc;
+  Entry& e = cache[next];
+  e.ptr = ptr; e.rows = rows; e.cols = cols; e.box = box_rows; e.map = *m;
+  next = (next + 1) % kEntries;
+  if (used < kEntries) ++used;
+  return SOUFFLE_OK;
+}
+
+static int make_map_uncached(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(SOUFFLE_CUDA_ERROR, "cuTensorMapEncodeTiled is not available from the driver");
   if (!aligned16(ptr) || (cols * 2) % 16 != 0) return fail(SOUFFLE_BAD_POINTER, "tensor map needs 16-byte alignment");
@@ -166,12 +191,15 @@ static int device_info(DeviceInfo** out) {
     SF_CUDA(cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev));
     if (d.cc_major != 10)
       return fail(SOUFFLE_BAD_DEVICE, "device %d has compute capability %d.x; this library needs sm_100", dev, d.cc_major);
-    SF_CUDA(cudaFuncSetAttribute(souffle_megakernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-    SF_CUDA(cudaFuncSetAttribute(souffle_megakernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-    int per_sm = 0, per_sm_swin = 0;
-    SF_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, souffle_megakernel<false>, kThreads, kSmemBytes));
-    SF_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm_swin, souffle_megakernel<true>, kThreads, kSmemBytes));
-    if (per_sm_swin < per_sm) per_sm = per_sm_swin;
+    const void* fns[3] = {(const void*)souffle_megakernel<kFamilyBert>, (const void*)souffle_megakernel<kFamilyBertCoop>,
+                          (const void*)souffle_megakernel<kFamilySwin>};
+    int per_sm = 1 << 30;
+    for (const void* fn : fns) {
+      SF_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+      int n = 0;
+      SF_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, fn, kThreads, kSmemBytes));
+      if (n < per_sm) per_sm = n;
+    }
     d.max_ctas = per_sm * d.sms;
     if (d.max_ctas < 1) return fail(SOUFFLE_NOT_CORESIDENT, "megakernel does not fit on an SM of device %d", dev);
     d.device = dev;
@@ -180,10 +208,12 @@ static int device_info(DeviceInfo** out) {
   return SOUFFLE_OK;
 }
 
-// `swin` selects the build of the kernel that knows the Swin epilogues and the window-attention stage.
-static int launch_mega(const CallArgs& args, int grid, cudaStream_t stream, bool swin = false) {
+// `family` selects the build of the kernel (see souffle_megakernel).
+static int launch_mega(const CallArgs& args, int grid, cudaStream_t stream, int family = kFamilyBert) {
   void* kargs[] = {const_cast<CallArgs*>(&args)};
-  const void* fn = swin ? (const void*)souffle_megakernel<true> : (const void*)souffle_megakernel<false>;
+  const void* fn = family == kFamilySwin ? (const void*)souffle_megakernel<kFamilySwin>
+                   : family == kFamilyBertCoop ? (const void*)souffle_megakernel<kFamilyBertCoop>
+                                               : (const void*)souffle_megakernel<kFamilyBert>;
   SF_CUDA(cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kThreads), kargs, (size_t)kSmemBytes, stream));
   return SOUFFLE_OK;
 }
@@ -255,6 +285,7 @@ using namespace souffle;
 struct SouffleBertPlan {
   SouffleBertDesc desc;
   int device = 0, grid = 0, launches = 0;
+  int family = 0;                // which build of the kernel runs this plan (kFamilyBert / kFamilyBertCoop)
   unsigned launch_id = 0;
   std::vector<Stage> stages;
   std::vector<CUtensorMap> maps;
@@ -479,6 +510,8 @@ static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* la
     if ((rc = plan_alloc(p, (void**)&p->d_prof, pb))) return rc;
     SF_CUDA(cudaMemset(p->d_prof, 0, pb));
   }
+  // one attention item per CTA at most, or a long sequence: the stage in which all softmax warps share an item
+  p->family = (d.seq > 128 || d.batch * d.heads <= p->grid) ? kFamilyBertCoop : kFamilyBert;
   for (Stage& fs : p->stages)
     if ((rc = finalize_stage(fs, p->desc.debug_max_slots & 0xFF, p->grid))) return rc;
   if ((rc = plan_alloc(p, (void**)&p->d_stages, p->stages.size() * sizeof(Stage)))) return rc;
@@ -567,7 +600,7 @@ int souffle_bert_forward(SouffleBertPlan* plan, const void* x, const int32_t* se
   mp.skip_arrival = d.debug_skip_arrival;
   mp.max_slots = d.debug_max_slots & 0xFF;
   mp.dbg_flags = d.debug_max_slots >> 8;
-  int rc = launch_mega(args, plan->grid, reinterpret_cast<cudaStream_t>(stream));
+  int rc = launch_mega(args, plan->grid, reinterpret_cast<cudaStream_t>(stream), plan->family);
   if (rc) return rc;
   plan->launch_id++;
   plan->launches = 1;
@@ -847,7 +880,7 @@ static int launch_plan(SouffleBertPlan* plan, const void* x, void* y, const int3
   mp.sync_next = plan->d_sync + 2 * (par ^ 1u);
   mp.status = plan->d_status;
   mp.timeout_ns = (unsigned long long)(timeout_ms > 0 ? timeout_ms : 2000) * 1000000ull;
-  int rc = launch_mega(args, plan->grid, st, /*swin=*/true);
+  int rc = launch_mega(args, plan->grid, st, kFamilySwin);
   if (rc) return rc;
   plan->launch_id++;
   plan->launches = 1;
