@@ -94,6 +94,16 @@ typedef struct SouffleBertLayerWeights {
   const void* ln2_b;  /* [H]        */
 } SouffleBertLayerWeights;
 
+/* The packed parameter block of the reference's 12-layer entry (cpp/bert/bert_base_impl.cu:536-572; 7,235,328
+ * fp16 values for batch 1, seq 384, :279): the attention mask [batch][seq][seq] (1 = attend), the Q, K, V and
+ * output matrices (H x H each), the FFN matrices (H x F, F x H), then thirteen vectors: q, k, v, output bias, LN1
+ * gamma, beta, FFN bias (F), FFN output bias, LN2 gamma, beta.  The reference runs all twelve layers on this one
+ * set (:590-678).  Fills `out` with pointers into `blob` -- nothing is copied, the addresses keep the 16-byte
+ * alignment of `blob` -- `mask_out` with the mask's address and `blob_bytes` with the block's size; any of the
+ * three may be null.  Host-only arithmetic: works on any address, also without a GPU. */
+int souffle_bert_packed_weights(const void* blob, int32_t batch, int32_t seq, int32_t hidden, int32_t ffn,
+                                SouffleBertLayerWeights* out, const void** mask_out, size_t* blob_bytes);
+
 typedef struct SouffleBertPlan SouffleBertPlan;
 
 /* Set-up (allocates the plan's device workspace, repacks the weights for the tensor cores and

@@ -59,6 +59,8 @@ SIGNATURES = {
     "souffle_bert_plan_status": (C.c_int, [C.c_void_p]),
     "souffle_bert_plan_read_profile": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),
     "souffle_bert_plan_info": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "souffle_bert_packed_weights": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.POINTER(BertLayerWeights),
+                                              C.POINTER(C.c_void_p), C.POINTER(C.c_size_t)]),
     "souffle_bert_plan_stage_info": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_int)]),
     "souffle_lstm_plan_create": (C.c_int, [C.POINTER(LstmDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)]),
     "souffle_lstm_plan_destroy": (C.c_int, [C.c_void_p]),

@@ -8,7 +8,7 @@ device memory and streams.
 from __future__ import annotations
 
 import ctypes as C
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, List, Optional, Sequence, Union
 
 import torch
 
@@ -170,18 +170,60 @@ def souffle_bert_layer(src: torch.Tensor, qkv_weight: torch.Tensor, attn_fc_weig
             enc.buffer("ln1"), enc.buffer("fc1"), out]
 
 
-def souffle_bert_base() -> int:
+_PACKED_ORDER = ("qkv_w", "proj_w", "fc1_w", "fc2_w", "qkv_b", "proj_b", "ln1_g", "ln1_b", "fc1_b", "fc2_b", "ln2_g", "ln2_b")
+
+
+def packed_block_size(batch: int, seq: int, hidden: int = 768, ffn: int = 3072) -> int:
+    """Number of fp16 values in the reference's packed parameter block (cpp/bert/bert_base_impl.cu:536-538)."""
+    n = C.c_size_t()
+    _lib.check(_lib.load().souffle_bert_packed_weights(None, batch, seq, hidden, ffn, None, None, C.byref(n)))
+    return n.value // 2
+
+
+def unpack_weights(blob: torch.Tensor, batch: int, seq: int, hidden: int = 768, ffn: int = 3072):
+    """Views into the reference's packed parameter block (cpp/bert/bert_base_impl.cu:536-572): returns
+    (mask[batch, seq, seq], layer dict with the keys BertEncoder takes).  Nothing is copied; the offsets come
+    from souffle_bert_packed_weights."""
+    if blob.dtype != torch.float16 or blob.dim() != 1 or not blob.is_contiguous():
+        raise ValueError("the packed block must be a contiguous 1-D fp16 tensor")
+    if blob.numel() < packed_block_size(batch, seq, hidden, ffn):
+        raise ValueError(f"packed block holds {blob.numel()} values, {packed_block_size(batch, seq, hidden, ffn)} needed")
+    w, mask_ptr = _lib.BertLayerWeights(), C.c_void_p()
+    _lib.check(_lib.load().souffle_bert_packed_weights(blob.data_ptr(), batch, seq, hidden, ffn, C.byref(w), C.byref(mask_ptr), None))
+    shapes = dict(qkv_w=(3, hidden, hidden), proj_w=(hidden, hidden), fc1_w=(hidden, ffn), fc2_w=(ffn, hidden), qkv_b=(3, hidden),
+                  proj_b=(hidden,), ln1_g=(hidden,), ln1_b=(hidden,), fc1_b=(ffn,), fc2_b=(hidden,), ln2_g=(hidden,), ln2_b=(hidden,))
+    base = blob.data_ptr()
+
+    def view(ptr, shape):
+        off = (ptr - base) // 2
+        n = 1
+        for d in shape:
+            n *= d
+        return blob[off:off + n].view(*shape)
+
+    layer = {k: view(getattr(w, k), shapes[k]) for k in _PACKED_ORDER}
+    return view(mask_ptr.value, (batch, seq, seq)), layer
+
+
+def souffle_bert_base(model: Optional[torch.Tensor] = None, src: Optional[torch.Tensor] = None) -> Union[int, torch.Tensor]:
     """Drop-in for souffle_bert_base.souffle_bert_base() (cpp/bert/bert_base_impl.cu:277-308): a 12-layer
-    BERT-base encoder at batch 1, sequence 384 with zero-filled parameters and input (the reference reads no
-    files either, :280-283), run as one launch.  Returns 0 like the reference."""
-    cfg = dict(batch=1, seq=384, heads=12, head_dim=64, ffn=3072)
-    H, F = 768, 3072
-    z = lambda *s: torch.zeros(*s, dtype=torch.float16, device="cuda")
-    layer = dict(qkv_w=z(3, H, H), qkv_b=z(3, H), proj_w=z(H, H), proj_b=z(H), ln1_g=z(H) + 1, ln1_b=z(H),
-                 fc1_w=z(H, F), fc1_b=z(F), fc2_w=z(F, H), fc2_b=z(H), ln2_g=z(H) + 1, ln2_b=z(H))
-    enc = BertEncoder(cfg["batch"], cfg["seq"], cfg["heads"], cfg["head_dim"], cfg["ffn"], [layer] * 12, variant=STD,
-                      eps=1e-6)
-    enc.forward(z(1, 384, H))
+    BERT-base encoder at batch 1, sequence 384, all layers on one parameter set, run as one launch.
+    Without arguments the parameters and the input are zero-filled as in the reference (which has its file
+    reads commented out, :279-283) and 0 is returned like there.  With `model` (the packed block of
+    :536-572 as an fp16 CUDA tensor, see unpack_weights) and `src` [384, 768] the encoder output is returned;
+    sequence lengths are taken from the first row of the block's mask."""
+    B, S, H, F = 1, 384, 768, 3072
+    if model is None:
+        z = lambda *s: torch.zeros(*s, dtype=torch.float16, device="cuda")
+        layer = dict(qkv_w=z(3, H, H), qkv_b=z(3, H), proj_w=z(H, H), proj_b=z(H), ln1_g=z(H) + 1, ln1_b=z(H),
+                     fc1_w=z(H, F), fc1_b=z(F), fc2_w=z(F, H), fc2_b=z(H), ln2_g=z(H) + 1, ln2_b=z(H))
+        lens, x = None, z(1, S, H)
+    else:
+        mask, layer = unpack_weights(model, B, S, H, F)
+        lens = (mask[:, 0, :] > 0).sum(dim=-1).to(torch.int32)
+        x = (src if src is not None else torch.zeros(S, H, dtype=torch.float16, device="cuda")).reshape(1, S, H)
+    enc = BertEncoder(B, S, 12, 64, F, [layer] * 12, variant=STD, eps=1e-6)
+    y = enc.forward(x, lens)
     enc.status()
     enc.close()
-    return 0
+    return 0 if model is None else y.reshape(S, H)

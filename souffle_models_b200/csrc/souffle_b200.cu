@@ -690,6 +690,35 @@ int souffle_bert_plan_info(SouffleBertPlan* plan, int* launches_out, int* grid_o
   return SOUFFLE_OK;
 }
 
+int souffle_bert_packed_weights(const void* blob, int32_t batch, int32_t seq, int32_t hidden, int32_t ffn,
+                                SouffleBertLayerWeights* out, const void** mask_out, size_t* blob_bytes) {
+  if (batch < 1 || seq < 1 || hidden < 8 || hidden % 8 || ffn < 8 || ffn % 8)
+    return fail(SOUFFLE_BAD_SHAPE, "packed block needs batch, seq >= 1 and hidden, ffn multiples of 8 (got %d, %d, %d, %d)",
+                batch, seq, hidden, ffn);
+  if ((size_t)batch * seq * seq % 8) return fail(SOUFFLE_BAD_SHAPE, "mask of %d x %d x %d halves breaks the 16-byte alignment", batch, seq, seq);
+  const size_t H = (size_t)hidden, F = (size_t)ffn;
+  const __half* p = reinterpret_cast<const __half*>(blob);
+  const __half* mask = p;
+  p += (size_t)batch * seq * seq;
+  SouffleBertLayerWeights w;
+  w.qkv_w = p;  p += 3 * H * H;
+  w.proj_w = p; p += H * H;
+  w.fc1_w = p;  p += H * F;
+  w.fc2_w = p;  p += F * H;
+  w.qkv_b = p;  p += 3 * H;
+  w.proj_b = p; p += H;
+  w.ln1_g = p;  p += H;
+  w.ln1_b = p;  p += H;
+  w.fc1_b = p;  p += F;
+  w.fc2_b = p;  p += H;
+  w.ln2_g = p;  p += H;
+  w.ln2_b = p;  p += H;
+  if (out) *out = w;
+  if (mask_out) *mask_out = mask;
+  if (blob_bytes) *blob_bytes = (size_t)(reinterpret_cast<const char*>(p) - reinterpret_cast<const char*>(blob));
+  return SOUFFLE_OK;
+}
+
 int souffle_bert_plan_stage_info(SouffleBertPlan* plan, int index, int out[6]) {
   if (!plan || !out) return fail(SOUFFLE_BAD_ARGUMENT, "null argument");
   if (index < 0 || index >= (int)plan->stages.size()) return fail(SOUFFLE_BAD_ARGUMENT, "stage index %d out of range", index);

@@ -82,3 +82,24 @@ def test_persistent_kernels_do_not_spill():
     for regs, st, ld in mega + lstm:
         assert st == 0 and ld == 0, f"kernel spills ({st} B stores, {ld} B loads, {regs} registers)"
     assert mega[0][0] <= 168          # 320 threads per CTA leave 168 registers per thread
+
+
+def test_packed_parameter_block_layout():
+    """Offsets of the reference's packed 12-layer parameter block (cpp/bert/bert_base_impl.cu:536-572): host-only
+    arithmetic, checked on a made-up base address."""
+    import ctypes as C
+    from souffle_models_b200 import _lib
+    lib = _lib.load()
+    w, mask, n = _lib.BertLayerWeights(), C.c_void_p(), C.c_size_t()
+    base, B, S, H, F = 0x10000, 1, 384, 768, 3072
+    assert lib.souffle_bert_packed_weights(base, B, S, H, F, C.byref(w), C.byref(mask), C.byref(n)) == 0
+    assert n.value == 7235328 * 2                      # the reference's model size in halves (bert_base_impl.cu:279)
+    assert mask.value == base
+    off = lambda p: (p - base) // 2
+    m = B * S * S
+    assert off(w.qkv_w) == m and off(w.proj_w) == m + 3 * H * H and off(w.fc1_w) == m + 4 * H * H
+    assert off(w.fc2_w) == m + 4 * H * H + H * F
+    v = m + 4 * H * H + 2 * H * F                      # thirteen vectors follow the twelve H x H blocks
+    assert [off(p) - v for p in (w.qkv_b, w.proj_b, w.ln1_g, w.ln1_b, w.fc1_b, w.fc2_b, w.ln2_g, w.ln2_b)] == \
+        [0, 3 * H, 4 * H, 5 * H, 6 * H, 6 * H + F, 7 * H + F, 8 * H + F]
+    assert lib.souffle_bert_packed_weights(base, 1, 3, H, F, None, None, None) != 0      # mask would break the alignment

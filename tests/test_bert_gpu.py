@@ -137,6 +137,25 @@ def test_stage_info_reports_the_tiling():
         enc.stage_info(7)
 
 
+def test_bert_base_entry_reads_the_packed_parameter_block():
+    """souffle_bert_base on the reference's packed block (cpp/bert/bert_base_impl.cu:536-572): twelve layers on one
+    parameter set, batch 1, seq 384, lengths from the block's mask."""
+    from souffle_models_b200 import bert
+    cfg = so.BertConfig(1, 384, 12, 64, 3072, "std")
+    w = so.make_bert_weights(cfg, 21, 1, zero_bias=False)[0]
+    x, _ = so.make_bert_input(cfg, 21)
+    kv = 300
+    mask = torch.zeros(1, 384, 384, dtype=torch.float16)
+    mask[:, :, :kv] = 1
+    order = ("qkv_w", "proj_w", "fc1_w", "fc2_w", "qkv_b", "proj_b", "ln1_g", "ln1_b", "fc1_b", "fc2_b", "ln2_g", "ln2_b")
+    blob = torch.cat([mask.reshape(-1)] + [w[k].reshape(-1) for k in order]).cuda()
+    assert blob.numel() == bert.packed_block_size(1, 384) == 7235328
+    y = bert.souffle_bert_base(blob, x.reshape(384, 768).cuda())
+    ref = so.bert_stack(cfg, x, [w] * 12, torch.tensor([kv], dtype=torch.int32))     # eps 1e-6 vs 1e-12: < 1e-6 apart
+    assert _err(y, ref) < TOL_STACK_FP32
+    assert bert.souffle_bert_base() == 0
+
+
 def test_host_buffer_entry_point():
     cfg = so.BertConfig(2, 128, 12, 64, 3072, "std")
     layers = so.make_bert_weights(cfg, 5, 1)
