@@ -231,11 +231,14 @@ int souffle_layernorm_forward(const float* partial, int32_t n_partial, const voi
                               void* workspace, size_t workspace_bytes, souffle_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
- * Swin transformer block (pre-LN, shifted-window attention with relative-position bias, MLP with tanh-GELU)
- * as one persistent launch of seven stages: LN1, QKV (+roll, window partition), window attention, proj
- * (+window reverse, roll back, residual), LN2, FC1+GELU, FC2+residual.  The reference has this block only as
- * TVM operator definitions (python/models/swin_transformer/swin_transformer_main.py:11-86) and, in C++, its MLP
- * GEMM pair; the relative-position bias and the shift mask follow the benchmark config.
+ * Swin transformer blocks (pre-LN, shifted-window attention with relative-position bias, MLP with tanh-GELU)
+ * as one persistent launch of eight stages per block: LN1, QKV (+roll, window partition), window attention, proj
+ * (+window reverse, roll back, residual), LN2, FC1+GELU, FC2 cut along K into fp32 planes, and the sum of the
+ * planes + bias + residual.  `n_blocks` blocks are chained inside the launch (a stage of the network: the
+ * reference needs 226 kernels for the model, python/models/tee:1); even-numbered blocks use `shift`, odd-numbered
+ * ones `shift_alt` (the usual pair: 0 and window / 2).  The reference has the block only as TVM operator
+ * definitions (python/models/swin_transformer/swin_transformer_main.py:11-86) and, in C++, its MLP GEMM pair; the
+ * relative-position bias and the shift mask follow the benchmark config.
  * ------------------------------------------------------------------------------------------ */
 typedef struct SouffleSwinDesc {
   int32_t batch;      /* images per call */
@@ -243,20 +246,23 @@ typedef struct SouffleSwinDesc {
   int32_t dim;        /* channels: 128, 256, 512, 768 or 1024 */
   int32_t heads;      /* dim / heads must be 32, heads even */
   int32_t window;     /* 7 or 8 */
-  int32_t shift;      /* cyclic shift, 0 <= shift < window */
+  int32_t shift;      /* cyclic shift of blocks 0, 2, ...; 0 <= shift < window */
   int32_t mlp_ratio;  /* hidden = dim * mlp_ratio */
   float eps;          /* LayerNorm epsilon */
   int32_t timeout_ms; /* device-side wait limit, 0 = 2000 ms */
+  int32_t n_blocks;   /* blocks chained in one launch, 1..18; 0 = 1 */
+  int32_t shift_alt;  /* cyclic shift of blocks 1, 3, ... */
 } SouffleSwinDesc;
 /* fp16 device pointers; matrices [K][N] row-major; rel_bias is [(2*window-1)^2][heads]. */
 typedef struct SouffleSwinWeights {
   const void *ln1_g, *ln1_b, *qkv_w, *qkv_b, *rel_bias, *proj_w, *proj_b, *ln2_g, *ln2_b, *fc1_w, *fc1_b, *fc2_w, *fc2_b;
 } SouffleSwinWeights;
 typedef struct SouffleSwinPlan SouffleSwinPlan;
+/* `weights` is a host array of n_blocks records. */
 int souffle_swin_block_plan_create(const SouffleSwinDesc* desc, const SouffleSwinWeights* weights,
                                    SouffleSwinPlan** plan_out);
 int souffle_swin_block_plan_destroy(SouffleSwinPlan* plan);
-/* y[batch*res*res][dim] = block(x); fp16 device buffers; asynchronous on `stream`. */
+/* y[batch*res*res][dim] = block_{n-1}(... block_0(x)); fp16 device buffers; asynchronous on `stream`. */
 int souffle_swin_block_forward(SouffleSwinPlan* plan, const void* x, void* y, souffle_stream_t stream);
 int souffle_swin_block_plan_status(SouffleSwinPlan* plan);
 

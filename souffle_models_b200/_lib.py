@@ -34,7 +34,7 @@ class BertLayerWeights(C.Structure):
 
 class SwinDesc(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("batch", "res", "dim", "heads", "window", "shift", "mlp_ratio")] + \
-               [("eps", C.c_float), ("timeout_ms", C.c_int32)]
+               [("eps", C.c_float), ("timeout_ms", C.c_int32), ("n_blocks", C.c_int32), ("shift_alt", C.c_int32)]
 
 
 class SwinWeights(C.Structure):

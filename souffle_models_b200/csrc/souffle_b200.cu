@@ -934,7 +934,7 @@ static int finish_plan(SouffleBertPlan* p, int sms) {
   return SOUFFLE_OK;
 }
 
-static int build_swin_plan(SouffleSwinPlan* sp, const SouffleSwinWeights& w) {
+static int build_swin_plan(SouffleSwinPlan* sp, const SouffleSwinWeights* blocks) {
   SouffleBertPlan* p = &sp->base;
   const SouffleSwinDesc& d = sp->desc;
   DeviceInfo* di = nullptr;
@@ -944,31 +944,34 @@ static int build_swin_plan(SouffleSwinPlan* sp, const SouffleSwinWeights& w) {
   const int sms = di->sms < di->max_ctas ? di->sms : di->max_ctas;
   const int R = d.res, C = d.dim, Hh = d.heads, ws = d.window, F = C * d.mlp_ratio;
   const int T = d.batch * R * R, nWt = d.batch * (R / ws) * (R / ws), Mw = nWt * 64;
-  __half *y1, *qkvw, *ctxw, *x1, *y2, *hid;
+  const int n_blocks = d.n_blocks > 0 ? d.n_blocks : 1;
+  // FC2 has few output tiles and the longest K of the block: it is cut along K into fp32 planes, and a sum-only
+  // LayerNorm stage adds them, the bias and the residual (the block's output).
+  const TileChoice t_qkv = choose_tiles(T, 3 * C, C, sms, false, false, 2), t_proj = choose_tiles(Mw, C, C, sms, false, false, 2),
+                   t_fc1 = choose_tiles(T, F, C, sms, false, false, 0), t_fc2 = choose_tiles(T, C, F, sms, true, false, 0);
+  // activations, shared by all blocks of the chain (stages run one after the other)
+  __half *y1, *qkvw, *ctxw, *x1, *y2, *hid, *xbuf[2] = {nullptr, nullptr};
+  float* planes;
   if ((rc = plan_alloc(p, (void**)&y1, (size_t)T * C * 2))) return rc;
   if ((rc = plan_alloc(p, (void**)&qkvw, (size_t)3 * Mw * C * 2))) return rc;
   if ((rc = plan_alloc(p, (void**)&ctxw, (size_t)Mw * C * 2))) return rc;
   if ((rc = plan_alloc(p, (void**)&x1, (size_t)T * C * 2))) return rc;
   if ((rc = plan_alloc(p, (void**)&y2, (size_t)T * C * 2))) return rc;
   if ((rc = plan_alloc(p, (void**)&hid, (size_t)T * F * 2))) return rc;
+  if ((rc = plan_alloc(p, (void**)&planes, (size_t)t_fc2.split * T * C * 4))) return rc;
+  for (int i = 0; i < 2 && i < n_blocks - 1; ++i)
+    if ((rc = plan_alloc(p, (void**)&xbuf[i], (size_t)T * C * 2))) return rc;
   if ((rc = plan_alloc(p, (void**)&p->d_sync, 64))) return rc;
   if ((rc = plan_alloc(p, (void**)&p->d_status, 64))) return rc;
   SF_CUDA(cudaMemset(p->d_sync, 0, 64));
   SF_CUDA(cudaMemset(p->d_status, 0, 64));
   SF_CUDA(cudaMemset(qkvw, 0, (size_t)3 * Mw * C * 2));     // padding slots stay zero for ever
   SF_CUDA(cudaMemset(ctxw, 0, (size_t)Mw * C * 2));
-  // weights: repack [K][N] -> [N][K]
-  __half *wqkv_t, *wo_t, *w1_t, *w2_t;
-  if ((rc = plan_alloc(p, (void**)&wqkv_t, (size_t)3 * C * C * 2))) return rc;
-  if ((rc = plan_alloc(p, (void**)&wo_t, (size_t)C * C * 2))) return rc;
-  if ((rc = plan_alloc(p, (void**)&w1_t, (size_t)C * F * 2))) return rc;
-  if ((rc = plan_alloc(p, (void**)&w2_t, (size_t)F * C * 2))) return rc;
-  const dim3 tb(32, 8);
-  transpose_kn_to_nk<<<dim3(3 * C / 32, C / 32), tb>>>(reinterpret_cast<const __half*>(w.qkv_w), wqkv_t, C, 3 * C);
-  transpose_kn_to_nk<<<dim3(C / 32, C / 32), tb>>>(reinterpret_cast<const __half*>(w.proj_w), wo_t, C, C);
-  transpose_kn_to_nk<<<dim3(F / 32, C / 32), tb>>>(reinterpret_cast<const __half*>(w.fc1_w), w1_t, C, F);
-  transpose_kn_to_nk<<<dim3(C / 32, F / 32), tb>>>(reinterpret_cast<const __half*>(w.fc2_w), w2_t, F, C);
-  SF_CUDA(cudaGetLastError());
+  int m_y1, m_ctx, m_y2, m_hid, m_qkv;
+  if ((rc = add_map(p, y1, T, C, t_qkv.bm, &m_y1)) || (rc = add_map(p, ctxw, Mw, C, t_proj.bm, &m_ctx)) ||
+      (rc = add_map(p, y2, T, C, t_fc1.bm, &m_y2)) || (rc = add_map(p, hid, T, F, t_fc2.bm, &m_hid)) ||
+      (rc = add_map(p, qkvw, (uint64_t)3 * Mw, C, 128, &m_qkv)))
+    return rc;
   auto copy_vec = [&](const void* src, size_t n, const void** dst) -> int {
     *dst = nullptr;
     if (!src) return SOUFFLE_OK;
@@ -979,54 +982,75 @@ static int build_swin_plan(SouffleSwinPlan* sp, const SouffleSwinWeights& w) {
     *dst = v;
     return SOUFFLE_OK;
   };
-  const void *ln1_g, *ln1_b, *qkv_b, *relb, *proj_b, *ln2_g, *ln2_b, *fc1_b, *fc2_b;
   const int tbl = (2 * ws - 1) * (2 * ws - 1);
-  if ((rc = copy_vec(w.ln1_g, C, &ln1_g)) || (rc = copy_vec(w.ln1_b, C, &ln1_b)) || (rc = copy_vec(w.qkv_b, 3 * C, &qkv_b)) ||
-      (rc = copy_vec(w.rel_bias, (size_t)tbl * Hh, &relb)) || (rc = copy_vec(w.proj_b, C, &proj_b)) ||
-      (rc = copy_vec(w.ln2_g, C, &ln2_g)) || (rc = copy_vec(w.ln2_b, C, &ln2_b)) || (rc = copy_vec(w.fc1_b, F, &fc1_b)) ||
-      (rc = copy_vec(w.fc2_b, C, &fc2_b)))
-    return rc;
-  if (!relb) return fail(SOUFFLE_BAD_POINTER, "rel_bias must be given");
-  if ((ln1_g == nullptr) != (ln1_b == nullptr) || (ln2_g == nullptr) != (ln2_b == nullptr))
-    return fail(SOUFFLE_BAD_ARGUMENT, "gamma and beta must be given together");
+  const dim3 tb(32, 8);
 
-  const TileChoice t_qkv = choose_tiles(T, 3 * C, C, sms, false, false, 2), t_proj = choose_tiles(Mw, C, C, sms, false, false, 2),
-                   t_fc1 = choose_tiles(T, F, C, sms, false, false, 0), t_fc2 = choose_tiles(T, C, F, sms, false, false, 0);
-  int m_y1, m_ctx, m_y2, m_hid, m_qkv, m_wqkv, m_wo, m_w1, m_w2;
-  if ((rc = add_map(p, y1, T, C, t_qkv.bm, &m_y1)) || (rc = add_map(p, ctxw, Mw, C, t_proj.bm, &m_ctx)) ||
-      (rc = add_map(p, y2, T, C, t_fc1.bm, &m_y2)) || (rc = add_map(p, hid, T, F, t_fc2.bm, &m_hid)) ||
-      (rc = add_map(p, qkvw, (uint64_t)3 * Mw, C, 128, &m_qkv)) || (rc = add_map(p, wqkv_t, 3 * C, C, t_qkv.bn, &m_wqkv)) ||
-      (rc = add_map(p, wo_t, C, C, t_proj.bn, &m_wo)) || (rc = add_map(p, w1_t, F, C, t_fc1.bn, &m_w1)) ||
-      (rc = add_map(p, w2_t, C, F, t_fc2.bn, &m_w2)))
-    return rc;
+  for (int bi = 0; bi < n_blocks; ++bi) {
+    const SouffleSwinWeights& w = blocks[bi];
+    const int shift = (bi & 1) ? d.shift_alt : d.shift;
+    if (!w.qkv_w || !w.proj_w || !w.fc1_w || !w.fc2_w || !w.rel_bias)
+      return fail(SOUFFLE_BAD_POINTER, "block %d: qkv_w, proj_w, fc1_w, fc2_w and rel_bias must be given", bi);
+    // weights: repack [K][N] -> [N][K]
+    __half *wqkv_t, *wo_t, *w1_t, *w2_t;
+    if ((rc = plan_alloc(p, (void**)&wqkv_t, (size_t)3 * C * C * 2))) return rc;
+    if ((rc = plan_alloc(p, (void**)&wo_t, (size_t)C * C * 2))) return rc;
+    if ((rc = plan_alloc(p, (void**)&w1_t, (size_t)C * F * 2))) return rc;
+    if ((rc = plan_alloc(p, (void**)&w2_t, (size_t)F * C * 2))) return rc;
+    transpose_kn_to_nk<<<dim3(3 * C / 32, C / 32), tb>>>(reinterpret_cast<const __half*>(w.qkv_w), wqkv_t, C, 3 * C);
+    transpose_kn_to_nk<<<dim3(C / 32, C / 32), tb>>>(reinterpret_cast<const __half*>(w.proj_w), wo_t, C, C);
+    transpose_kn_to_nk<<<dim3(F / 32, C / 32), tb>>>(reinterpret_cast<const __half*>(w.fc1_w), w1_t, C, F);
+    transpose_kn_to_nk<<<dim3(C / 32, F / 32), tb>>>(reinterpret_cast<const __half*>(w.fc2_w), w2_t, F, C);
+    SF_CUDA(cudaGetLastError());
+    const void *ln1_g, *ln1_b, *qkv_b, *relb, *proj_b, *ln2_g, *ln2_b, *fc1_b, *fc2_b;
+    if ((rc = copy_vec(w.ln1_g, C, &ln1_g)) || (rc = copy_vec(w.ln1_b, C, &ln1_b)) || (rc = copy_vec(w.qkv_b, 3 * C, &qkv_b)) ||
+        (rc = copy_vec(w.rel_bias, (size_t)tbl * Hh, &relb)) || (rc = copy_vec(w.proj_b, C, &proj_b)) ||
+        (rc = copy_vec(w.ln2_g, C, &ln2_g)) || (rc = copy_vec(w.ln2_b, C, &ln2_b)) || (rc = copy_vec(w.fc1_b, F, &fc1_b)) ||
+        (rc = copy_vec(w.fc2_b, C, &fc2_b)))
+      return rc;
+    if ((ln1_g == nullptr) != (ln1_b == nullptr) || (ln2_g == nullptr) != (ln2_b == nullptr))
+      return fail(SOUFFLE_BAD_ARGUMENT, "gamma and beta must be given together");
+    int m_wqkv, m_wo, m_w1, m_w2;
+    if ((rc = add_map(p, wqkv_t, 3 * C, C, t_qkv.bn, &m_wqkv)) || (rc = add_map(p, wo_t, C, C, t_proj.bn, &m_wo)) ||
+        (rc = add_map(p, w1_t, F, C, t_fc1.bn, &m_w1)) || (rc = add_map(p, w2_t, C, F, t_fc2.bn, &m_w2)))
+      return rc;
+    // the block's input (also the residual of its attention half) and output
+    const int in_sel = bi == 0 ? PTR_CALL_X : PTR_PLAN;
+    const __half* xin = bi == 0 ? nullptr : xbuf[(bi - 1) & 1];
+    const bool last = bi == n_blocks - 1;
 
-  Stage s = blank_stage(STAGE_LN);                       // LN1(x)
-  s.M = T; s.N = C; s.ldo = C; s.n_partial = 0; s.resid_sel = PTR_CALL_X; s.out = y1; s.gamma = ln1_g; s.beta = ln1_b; s.eps = d.eps;
-  p->stages.push_back(s);
-  s = blank_stage(STAGE_GEMM);                           // QKV, rolled and scattered window-major
-  s.tm_a = m_y1; s.tm_b = m_wqkv; s.M = T; s.N = 3 * C; s.K = C; s.bm = t_qkv.bm; s.bn = t_qkv.bn; s.epi = EPI_SWIN_QKV;
-  s.bias = qkv_b; s.out = qkvw; s.ldo = C; s.batch = d.batch; s.heads = Hh; s.head_dim = 32; s.seq = R; s.win = ws; s.shift = d.shift;
-  p->stages.push_back(s);
-  s = blank_stage(STAGE_ATTN_SWIN);                      // window attention
-  s.tm_qkv = m_qkv; s.batch = d.batch; s.heads = Hh; s.head_dim = 32; s.seq = R; s.win = ws; s.shift = d.shift; s.ldo = C;
-  s.scale = 1.0f / sqrtf(32.0f); s.rel_bias = relb; s.out = ctxw;
-  p->stages.push_back(s);
-  s = blank_stage(STAGE_GEMM);                           // proj, window reverse, roll back, + x
-  s.tm_a = m_ctx; s.tm_b = m_wo; s.M = Mw; s.N = C; s.K = C; s.bm = t_proj.bm; s.bn = t_proj.bn; s.epi = EPI_SWIN_PROJ;
-  s.bias = proj_b; s.resid_sel = PTR_CALL_X; s.out = x1; s.ldo = C; s.batch = d.batch; s.heads = Hh; s.head_dim = 32; s.seq = R;
-  s.win = ws; s.shift = d.shift;
-  p->stages.push_back(s);
-  s = blank_stage(STAGE_LN);                             // LN2(x1)
-  s.M = T; s.N = C; s.ldo = C; s.n_partial = 0; s.resid = x1; s.out = y2; s.gamma = ln2_g; s.beta = ln2_b; s.eps = d.eps;
-  p->stages.push_back(s);
-  s = blank_stage(STAGE_GEMM);                           // FC1 + GELU
-  s.tm_a = m_y2; s.tm_b = m_w1; s.M = T; s.N = F; s.K = C; s.bm = t_fc1.bm; s.bn = t_fc1.bn; s.epi = EPI_F16; s.act = ACT_GELU;
-  s.bias = fc1_b; s.out = hid; s.ldo = F;
-  p->stages.push_back(s);
-  s = blank_stage(STAGE_GEMM);                           // FC2 + x1
-  s.tm_a = m_hid; s.tm_b = m_w2; s.M = T; s.N = C; s.K = F; s.bm = t_fc2.bm; s.bn = t_fc2.bn; s.epi = EPI_F16; s.bias = fc2_b;
-  s.resid = x1; s.out_sel = PTR_CALL_Y; s.ldo = C;
-  p->stages.push_back(s);
+    Stage s = blank_stage(STAGE_LN);                       // LN1(x)
+    s.M = T; s.N = C; s.ldo = C; s.n_partial = 0; s.resid_sel = in_sel; s.resid = xin; s.out = y1; s.gamma = ln1_g; s.beta = ln1_b;
+    s.eps = d.eps;
+    p->stages.push_back(s);
+    s = blank_stage(STAGE_GEMM);                           // QKV, rolled and scattered window-major
+    s.tm_a = m_y1; s.tm_b = m_wqkv; s.M = T; s.N = 3 * C; s.K = C; s.bm = t_qkv.bm; s.bn = t_qkv.bn; s.epi = EPI_SWIN_QKV;
+    s.bias = qkv_b; s.out = qkvw; s.ldo = C; s.batch = d.batch; s.heads = Hh; s.head_dim = 32; s.seq = R; s.win = ws; s.shift = shift;
+    p->stages.push_back(s);
+    s = blank_stage(STAGE_ATTN_SWIN);                      // window attention
+    s.tm_qkv = m_qkv; s.batch = d.batch; s.heads = Hh; s.head_dim = 32; s.seq = R; s.win = ws; s.shift = shift; s.ldo = C;
+    s.scale = 1.0f / sqrtf(32.0f); s.rel_bias = relb; s.out = ctxw;
+    p->stages.push_back(s);
+    s = blank_stage(STAGE_GEMM);                           // proj, window reverse, roll back, + x
+    s.tm_a = m_ctx; s.tm_b = m_wo; s.M = Mw; s.N = C; s.K = C; s.bm = t_proj.bm; s.bn = t_proj.bn; s.epi = EPI_SWIN_PROJ;
+    s.bias = proj_b; s.resid_sel = in_sel; s.resid = xin; s.out = x1; s.ldo = C; s.batch = d.batch; s.heads = Hh; s.head_dim = 32;
+    s.seq = R; s.win = ws; s.shift = shift;
+    p->stages.push_back(s);
+    s = blank_stage(STAGE_LN);                             // LN2(x1)
+    s.M = T; s.N = C; s.ldo = C; s.n_partial = 0; s.resid = x1; s.out = y2; s.gamma = ln2_g; s.beta = ln2_b; s.eps = d.eps;
+    p->stages.push_back(s);
+    s = blank_stage(STAGE_GEMM);                           // FC1 + GELU
+    s.tm_a = m_y2; s.tm_b = m_w1; s.M = T; s.N = F; s.K = C; s.bm = t_fc1.bm; s.bn = t_fc1.bn; s.epi = EPI_F16; s.act = ACT_GELU;
+    s.bias = fc1_b; s.out = hid; s.ldo = F;
+    p->stages.push_back(s);
+    s = blank_stage(STAGE_GEMM);                           // FC2 -> fp32 planes
+    s.tm_a = m_hid; s.tm_b = m_w2; s.M = T; s.N = C; s.K = F; s.bm = t_fc2.bm; s.bn = t_fc2.bn; s.splitk = t_fc2.split;
+    s.epi = EPI_PARTIAL; s.partial = planes; s.ldo = C;
+    p->stages.push_back(s);
+    s = blank_stage(STAGE_LN);                             // planes + bias + x1 -> block output (no normalisation)
+    s.M = T; s.N = C; s.ldo = C; s.partial = planes; s.n_partial = t_fc2.split; s.bias = fc2_b; s.resid = x1; s.eps = -1.0f;
+    if (last) s.out_sel = PTR_CALL_Y; else s.out = xbuf[bi & 1];
+    p->stages.push_back(s);
+  }
   return finish_plan(p, sms);
 }
 
@@ -1037,16 +1061,19 @@ int souffle_swin_block_plan_create(const SouffleSwinDesc* desc, const SouffleSwi
   if (d.batch < 1 || d.res < 1) return fail(SOUFFLE_BAD_SHAPE, "batch and res must be >= 1");
   if (d.window != 7 && d.window != 8) return fail(SOUFFLE_BAD_SHAPE, "window must be 7 or 8 (got %d)", d.window);
   if (d.res % d.window) return fail(SOUFFLE_BAD_SHAPE, "res %d is not a multiple of the window %d", d.res, d.window);
-  if (d.shift < 0 || d.shift >= d.window) return fail(SOUFFLE_BAD_SHAPE, "shift must be in [0, window)");
+  if (d.shift < 0 || d.shift >= d.window || d.shift_alt < 0 || d.shift_alt >= d.window)
+    return fail(SOUFFLE_BAD_SHAPE, "shift and shift_alt must be in [0, window)");
+  if (d.n_blocks < 0 || d.n_blocks > 18) return fail(SOUFFLE_BAD_SHAPE, "n_blocks must be in 1..18 (0 = 1), got %d", d.n_blocks);
   if (d.dim != 128 && d.dim != 256 && d.dim != 512 && d.dim != 768 && d.dim != 1024)
     return fail(SOUFFLE_BAD_SHAPE, "dim %d must be 128, 256, 512, 768 or 1024", d.dim);
   if (d.heads < 2 || d.heads % 2 || d.heads * 32 != d.dim) return fail(SOUFFLE_BAD_SHAPE, "heads must be even with dim / heads == 32");
   if (d.mlp_ratio < 1 || d.dim * d.mlp_ratio > 4096) return fail(SOUFFLE_BAD_SHAPE, "dim * mlp_ratio must be in (0, 4096]");
-  if (!aligned16(weights->qkv_w) || !aligned16(weights->proj_w) || !aligned16(weights->fc1_w) || !aligned16(weights->fc2_w))
-    return fail(SOUFFLE_BAD_POINTER, "weight matrices must be non-null and 16-byte aligned");
+  for (int i = 0; i < (d.n_blocks > 0 ? d.n_blocks : 1); ++i)
+    if (!aligned16(weights[i].qkv_w) || !aligned16(weights[i].proj_w) || !aligned16(weights[i].fc1_w) || !aligned16(weights[i].fc2_w))
+      return fail(SOUFFLE_BAD_POINTER, "block %d: weight matrices must be non-null and 16-byte aligned", i);
   SouffleSwinPlan* sp = new SouffleSwinPlan();
   sp->desc = d;
-  int rc = build_swin_plan(sp, *weights);
+  int rc = build_swin_plan(sp, weights);
   if (rc) {
     const std::string keep = g_last_error;
     souffle_swin_block_plan_destroy(sp);

@@ -74,8 +74,8 @@ struct Stage {
 // q = n / d for n * d < 2^32 as one multiply-high: mg = ceil(2^32 / d); d == 1 has no 32-bit multiplier.
 inline uint32_t fast_div_magic(uint32_t d) { return d <= 1 ? 0u : (uint32_t)((0x100000000ull + d - 1) / d); }
 
-constexpr int kMaxTensorMaps = 80;
-constexpr int kMaxStages = 96;
+constexpr int kMaxTensorMaps = 96;
+constexpr int kMaxStages = 160;
 constexpr int kProfSlots = 16;   // int64 words per (stage, CTA) record of the in-kernel profile
 
 }  // namespace souffle

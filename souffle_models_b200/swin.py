@@ -127,25 +127,30 @@ def layernorm(partial: torch.Tensor, resid=None, bias=None, gamma=None, beta=Non
 
 
 class SwinBlock:
-    """Plan for one Swin block (see SouffleSwinDesc in the header): weights dict with the keys of
-    oracle.souffle_oracle.make_swin_params, fp16 CUDA tensors, matrices [K][N]."""
+    """Plan for one Swin block, or for a chain of blocks run as one launch (see SouffleSwinDesc in the header).
+    `params` is a weights dict with the keys of oracle.souffle_oracle.make_swin_params (fp16 CUDA tensors, matrices
+    [K][N]) or a list of such dicts, one per block; even-numbered blocks use `shift`, odd-numbered ones `shift_alt`."""
 
     KEYS = ("ln1_g", "ln1_b", "qkv_w", "qkv_b", "rel_bias", "proj_w", "proj_b", "ln2_g", "ln2_b", "fc1_w", "fc1_b",
             "fc2_w", "fc2_b")
 
     def __init__(self, batch: int, res: int, dim: int, heads: int, window: int, shift: int, params, mlp_ratio: int = 4,
-                 eps: float = 1e-5):
+                 eps: float = 1e-5, shift_alt: int = 0):
         lib = _lib.load()
         self.batch, self.res, self.dim = batch, res, dim
-        d = _lib.SwinDesc(batch=batch, res=res, dim=dim, heads=heads, window=window, shift=shift, mlp_ratio=mlp_ratio, eps=eps)
-        w = _lib.SwinWeights()
-        for k in self.KEYS:
-            t = params.get(k)
-            if t is not None:
-                _check_f16_cuda(t, k)
-            setattr(w, k, t.data_ptr() if t is not None else None)
+        blocks = list(params) if isinstance(params, (list, tuple)) else [params]
+        d = _lib.SwinDesc(batch=batch, res=res, dim=dim, heads=heads, window=window, shift=shift, mlp_ratio=mlp_ratio, eps=eps,
+                          n_blocks=len(blocks), shift_alt=shift_alt)
+        ws = (_lib.SwinWeights * len(blocks))()
+        self._keep = blocks
+        for w, blk in zip(ws, blocks):
+            for k in self.KEYS:
+                t = blk.get(k)
+                if t is not None:
+                    _check_f16_cuda(t, k)
+                setattr(w, k, t.data_ptr() if t is not None else None)
         self._h = C.c_void_p()
-        _lib.check(lib.souffle_swin_block_plan_create(C.byref(d), C.byref(w), C.byref(self._h)))
+        _lib.check(lib.souffle_swin_block_plan_create(C.byref(d), ws, C.byref(self._h)))
         self._lib = lib
 
     def close(self) -> None:

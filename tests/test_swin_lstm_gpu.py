@@ -106,6 +106,21 @@ def test_swin_block_matches_oracle(shift):
     assert torch.equal(y, y2)
 
 
+def test_swin_shifted_pair_as_one_launch():
+    """Benchmark config 4 as it is stated: the pair of blocks (shift 0, then shift 3), chained inside one launch."""
+    from souffle_models_b200 import swin
+    cfg = so.SwinConfig()
+    ps = [so.make_swin_params(cfg, 300 + i, zero_bias=False) for i in range(2)]
+    x = _rand((196, 512), 31)
+    pair = swin.SwinBlock(1, 14, 512, 16, 7, 0, [{k: v.cuda() for k, v in p.items()} for p in ps], shift_alt=3)
+    y = pair.forward(x.cuda())
+    pair.status()
+    mid = so.swin_block(cfg, x, ps[0], 0)
+    want = so.swin_block(cfg, mid.half().float(), ps[1], 3)       # the block boundary is an fp16 tensor on the GPU
+    err = (y.float().cpu() - want).abs()
+    assert err.max() < 3e-2 and err.pow(2).mean().sqrt() < 4e-3
+
+
 def test_swin_block_batch2_window8():
     from souffle_models_b200 import swin
     cfg = so.SwinConfig(res=16, dim=256, heads=8, window=8)
