@@ -30,6 +30,7 @@ sys.path.insert(0, ROOT)
 
 BATCH, SEQ, HEADS, HEAD_DIM, FFN, LAYERS = 64, 128, 12, 64, 3072, 12
 HIDDEN = HEADS * HEAD_DIM
+DRAM_BYTES_PER_LAUNCH_B64 = 459_977_728 + 2_045_136_384      # read + write, measured with ncu (see profiles/)
 METRIC = "bert_base_12layer_seq128_batch64_sequences_per_second"
 SEED = 1239
 
@@ -250,7 +251,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "gpu_launches": args.steps * info["launches"],
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
                      "frac": achieved / peaks["tflops"], "frac_of_sustained_peak": achieved / peaks["tflops_sustained"],
-                     "peak_source": peaks["src"] + " (cuBLAS bf16 burst)", "traffic": None,
+                     "peak_source": peaks["src"] + " (cuBLAS bf16 burst)",
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one 64-sequence, 12-layer launch from a one-pass ncu
+                     # capture (profiles/megakernel_bert_b64_bench_launches.md); not captured for the smaller per-GPU shards
+                     "traffic": DRAM_BYTES_PER_LAUNCH_B64 if per == BATCH else None,
                      "kernel": "souffle_megakernel", "flops_per_launch": flops_step_gpu},
         "clocks": clocks,
         "latency_us": lat,
