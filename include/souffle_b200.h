@@ -122,6 +122,14 @@ int souffle_bert_forward(SouffleBertPlan* plan, const void* x, const int32_t* se
 /* Same with HOST buffers (pinned or pageable): copies x in, runs, copies y out, synchronises. */
 int souffle_bert_forward_host(SouffleBertPlan* plan, const void* x_host, const int32_t* seq_lens_host,
                               void* y_host, souffle_stream_t stream);
+/* The same without the final synchronisation: y_host is complete once `stream` has caught up (the call makes
+ * `stream` wait for the copy-out).  Consecutive calls are pipelined over the plan's own copy-in, compute and
+ * copy-out streams and two sets of device buffers: the copy-in of call i+1 and the copy-out of call i-1 run while
+ * the kernel of call i does.  x_host must be ready when the call is made (the copy-in does not wait for `stream`)
+ * and stay unchanged, and y_host untouched, until `stream` has caught up;
+ * pinned buffers are needed for the copies to overlap.  (The reference's entry points take device tensors only.) */
+int souffle_bert_forward_host_async(SouffleBertPlan* plan, const void* x_host, const int32_t* seq_lens_host,
+                                    void* y_host, souffle_stream_t stream);
 
 /* The stage outputs the reference binding returns (cpp/bert/bert_binding.cu:534), for the
  * LAST layer of the plan.  Valid after a forward call has completed. */

@@ -54,6 +54,7 @@ SIGNATURES = {
     "souffle_bert_plan_destroy": (C.c_int, [C.c_void_p]),
     "souffle_bert_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "souffle_bert_forward_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "souffle_bert_forward_host_async": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "souffle_bert_plan_buffer": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_void_p), C.POINTER(C.c_size_t)]),
     "souffle_bert_plan_copy_buffer": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]),
     "souffle_bert_plan_status": (C.c_int, [C.c_void_p]),

@@ -90,11 +90,14 @@ class BertEncoder:
         _lib.check(self._lib.souffle_bert_forward(self._h, x.data_ptr(), lens_ptr, out.data_ptr(), _stream_ptr()))
         return out
 
-    def forward_host(self, x_host: torch.Tensor, seq_lens_host: Optional[torch.Tensor], y_host: torch.Tensor) -> None:
-        """Host buffers in and out (pinned preferred); synchronous."""
+    def forward_host(self, x_host: torch.Tensor, seq_lens_host: Optional[torch.Tensor], y_host: torch.Tensor,
+                     wait: bool = True) -> None:
+        """Host buffers in and out (pinned preferred).  With wait=False the call returns at once and consecutive
+        calls overlap their copies with one another's compute; y_host is complete once the current stream has
+        caught up (x_host and y_host must be left alone until then)."""
         lens_ptr = seq_lens_host.data_ptr() if seq_lens_host is not None else None
-        _lib.check(self._lib.souffle_bert_forward_host(self._h, x_host.data_ptr(), lens_ptr, y_host.data_ptr(),
-                                                       _stream_ptr()))
+        fn = self._lib.souffle_bert_forward_host if wait else self._lib.souffle_bert_forward_host_async
+        _lib.check(fn(self._h, x_host.data_ptr(), lens_ptr, y_host.data_ptr(), _stream_ptr()))
 
     def status(self) -> None:
         """Synchronises and raises SouffleError if a device-side wait expired."""

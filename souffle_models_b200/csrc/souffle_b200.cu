@@ -299,8 +299,13 @@ struct SouffleBertPlan {
   __half *qkv = nullptr, *ctx = nullptr, *ln1 = nullptr, *fc1 = nullptr, *probs = nullptr, *act[2] = {nullptr, nullptr};
   float* partial = nullptr;
   // host-buffer path
-  __half *x_dev = nullptr, *y_dev = nullptr;
-  int* lens_dev = nullptr;
+  // host-buffer path: two sets of device buffers and three streams, so that consecutive calls overlap their
+  // copies with one another's compute (copy-in of call i+1 and copy-out of call i-1 run under the kernel of call i)
+  __half *x_dev[2] = {nullptr, nullptr}, *y_dev[2] = {nullptr, nullptr};
+  int* lens_dev[2] = {nullptr, nullptr};
+  cudaStream_t s_in = nullptr, s_cmp = nullptr, s_out = nullptr;
+  cudaEvent_t ev_in[2] = {nullptr, nullptr}, ev_k[2] = {nullptr, nullptr}, ev_out[2] = {nullptr, nullptr};
+  unsigned host_calls = 0;
   // per-call map cache for x
   const void* last_x = nullptr;
   CUtensorMap x_map;
@@ -562,9 +567,17 @@ int souffle_bert_plan_destroy(SouffleBertPlan* plan) {
   if (!plan) return SOUFFLE_OK;
   cudaDeviceSynchronize();
   for (void* a : plan->allocs) cudaFree(a);
-  if (plan->x_dev) cudaFree(plan->x_dev);
-  if (plan->y_dev) cudaFree(plan->y_dev);
-  if (plan->lens_dev) cudaFree(plan->lens_dev);
+  for (int i = 0; i < 2; ++i) {
+    if (plan->x_dev[i]) cudaFree(plan->x_dev[i]);
+    if (plan->y_dev[i]) cudaFree(plan->y_dev[i]);
+    if (plan->lens_dev[i]) cudaFree(plan->lens_dev[i]);
+    if (plan->ev_in[i]) cudaEventDestroy(plan->ev_in[i]);
+    if (plan->ev_k[i]) cudaEventDestroy(plan->ev_k[i]);
+    if (plan->ev_out[i]) cudaEventDestroy(plan->ev_out[i]);
+  }
+  if (plan->s_in) cudaStreamDestroy(plan->s_in);
+  if (plan->s_cmp) cudaStreamDestroy(plan->s_cmp);
+  if (plan->s_out) cudaStreamDestroy(plan->s_out);
   delete plan;
   return SOUFFLE_OK;
 }
@@ -607,24 +620,55 @@ int souffle_bert_forward(SouffleBertPlan* plan, const void* x, const int32_t* se
   return SOUFFLE_OK;
 }
 
-int souffle_bert_forward_host(SouffleBertPlan* plan, const void* x_host, const int32_t* seq_lens_host,
-                              void* y_host, souffle_stream_t stream) {
+int souffle_bert_forward_host_async(SouffleBertPlan* plan, const void* x_host, const int32_t* seq_lens_host,
+                                    void* y_host, souffle_stream_t stream) {
   if (!plan || !x_host || !y_host) return fail(SOUFFLE_BAD_ARGUMENT, "null argument");
   const SouffleBertDesc& d = plan->desc;
   const size_t bytes = (size_t)d.batch * d.seq * d.heads * d.head_dim * 2;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (!plan->x_dev) {
-    SF_CUDA(cudaMalloc((void**)&plan->x_dev, bytes));
-    SF_CUDA(cudaMalloc((void**)&plan->y_dev, bytes));
-    SF_CUDA(cudaMalloc((void**)&plan->lens_dev, (size_t)d.batch * 4));
+  if (!plan->s_in) {
+    for (int i = 0; i < 2; ++i) {
+      SF_CUDA(cudaMalloc((void**)&plan->x_dev[i], bytes));
+      SF_CUDA(cudaMalloc((void**)&plan->y_dev[i], bytes));
+      SF_CUDA(cudaMalloc((void**)&plan->lens_dev[i], (size_t)d.batch * 4));
+      SF_CUDA(cudaEventCreateWithFlags(&plan->ev_in[i], cudaEventDisableTiming));
+      SF_CUDA(cudaEventCreateWithFlags(&plan->ev_k[i], cudaEventDisableTiming));
+      SF_CUDA(cudaEventCreateWithFlags(&plan->ev_out[i], cudaEventDisableTiming));
+    }
+    SF_CUDA(cudaStreamCreateWithFlags(&plan->s_cmp, cudaStreamNonBlocking));
+    SF_CUDA(cudaStreamCreateWithFlags(&plan->s_out, cudaStreamNonBlocking));
+    SF_CUDA(cudaStreamCreateWithFlags(&plan->s_in, cudaStreamNonBlocking));
   }
-  SF_CUDA(cudaMemcpyAsync(plan->x_dev, x_host, bytes, cudaMemcpyHostToDevice, st));
+  const int b = (int)(plan->host_calls++ & 1u);
+  // copy-in: once the kernel of the call before last has read this input buffer (an event that was never
+  // recorded does not block).  It does not wait for `stream`, which is itself waiting for earlier copy-outs:
+  // x_host has to be ready when the call is made.
+  SF_CUDA(cudaStreamWaitEvent(plan->s_in, plan->ev_k[b], 0));
+  SF_CUDA(cudaMemcpyAsync(plan->x_dev[b], x_host, bytes, cudaMemcpyHostToDevice, plan->s_in));
   if (seq_lens_host)
-    SF_CUDA(cudaMemcpyAsync(plan->lens_dev, seq_lens_host, (size_t)d.batch * 4, cudaMemcpyHostToDevice, st));
-  int rc = souffle_bert_forward(plan, plan->x_dev, seq_lens_host ? plan->lens_dev : nullptr, plan->y_dev, stream);
+    SF_CUDA(cudaMemcpyAsync(plan->lens_dev[b], seq_lens_host, (size_t)d.batch * 4, cudaMemcpyHostToDevice, plan->s_in));
+  SF_CUDA(cudaEventRecord(plan->ev_in[b], plan->s_in));
+  // compute: launches of one plan run one after the other on the plan's own stream; the output buffer must
+  // have been copied out by the call before last
+  SF_CUDA(cudaStreamWaitEvent(plan->s_cmp, plan->ev_in[b], 0));
+  SF_CUDA(cudaStreamWaitEvent(plan->s_cmp, plan->ev_out[b], 0));
+  int rc = souffle_bert_forward(plan, plan->x_dev[b], seq_lens_host ? plan->lens_dev[b] : nullptr, plan->y_dev[b],
+                                reinterpret_cast<souffle_stream_t>(plan->s_cmp));
   if (rc) return rc;
-  SF_CUDA(cudaMemcpyAsync(y_host, plan->y_dev, bytes, cudaMemcpyDeviceToHost, st));
-  SF_CUDA(cudaStreamSynchronize(st));
+  SF_CUDA(cudaEventRecord(plan->ev_k[b], plan->s_cmp));
+  // copy-out, and the caller's stream waits for it
+  SF_CUDA(cudaStreamWaitEvent(plan->s_out, plan->ev_k[b], 0));
+  SF_CUDA(cudaMemcpyAsync(y_host, plan->y_dev[b], bytes, cudaMemcpyDeviceToHost, plan->s_out));
+  SF_CUDA(cudaEventRecord(plan->ev_out[b], plan->s_out));
+  SF_CUDA(cudaStreamWaitEvent(st, plan->ev_out[b], 0));
+  return SOUFFLE_OK;
+}
+
+int souffle_bert_forward_host(SouffleBertPlan* plan, const void* x_host, const int32_t* seq_lens_host,
+                              void* y_host, souffle_stream_t stream) {
+  const int rc = souffle_bert_forward_host_async(plan, x_host, seq_lens_host, y_host, stream);
+  if (rc) return rc;
+  SF_CUDA(cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(stream)));
   return SOUFFLE_OK;
 }
 

@@ -167,6 +167,27 @@ def test_host_buffer_entry_point():
     assert _err(yh.reshape(256, 768), so.bert_layer(cfg, x, layers[0], lens)["out"]) < TOL_LAYER
 
 
+def test_pipelined_host_calls_match_the_synchronous_ones():
+    """Three asynchronous host-buffer calls in a row (different inputs, overlapping copies and kernels) give what
+    three synchronous calls give."""
+    cfg = so.BertConfig(4, 128, 12, 64, 3072, "std")
+    layers = so.make_bert_weights(cfg, 9, 2)
+    enc = _encoder(cfg, layers)
+    xs = [so.make_bert_input(cfg, 40 + i, ragged=True) for i in range(3)]
+    want = []
+    for x, lens in xs:
+        xh, yh = x.pin_memory(), torch.empty_like(x).pin_memory()
+        enc.forward_host(xh, lens.pin_memory(), yh)
+        want.append(yh.clone())
+    bufs = [(x.pin_memory(), lens.pin_memory(), torch.empty_like(x).pin_memory()) for x, lens in xs]
+    for xh, lh, yh in bufs:
+        enc.forward_host(xh, lh, yh, wait=False)
+    torch.cuda.current_stream().synchronize()
+    enc.status()
+    for (_, _, yh), w in zip(bufs, want):
+        assert torch.equal(yh, w)
+
+
 def test_device_side_wait_limit_reports_status_without_hanging():
     """Failure detection without a GPU fault: one CTA leaves at the first grid barrier without
     arriving (test hook), the others give up after the 20 ms wait limit, the launch ends by itself,
