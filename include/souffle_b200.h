@@ -12,6 +12,7 @@
  *   cpp/swin_transformer/swin_transformer_binding.cu:155-209  swin_fused_feed_mlp      -> souffle_swin_mlp_forward
  *   cpp/swin_transformer/swin_transformer_binding.cu:62-100   swin_ffn                 -> souffle_gemm_f16
  *   cpp/swin_transformer/swin_trans_fc2_binding.cu:19-55      swin_trans_fc2           -> souffle_gemm_f16
+ *   cpp/efficientnet/efficientnet_se_module_binding.cu:164-227  SE module (opt_level 2)  -> souffle_se_module_forward
  *   cpp/souffle_utils/cuda_utils.h:11-19,86-98  checkCuda / check_compatability        -> status codes + souffle_last_error
  */
 #ifndef SOUFFLE_B200_H_
@@ -273,6 +274,22 @@ int souffle_swin_block_plan_destroy(SouffleSwinPlan* plan);
 /* y[batch*res*res][dim] = block_{n-1}(... block_0(x)); fp16 device buffers; asynchronous on `stream`. */
 int souffle_swin_block_forward(SouffleSwinPlan* plan, const void* x, void* y, souffle_stream_t stream);
 int souffle_swin_block_plan_status(SouffleSwinPlan* plan);
+
+/* ------------------------------------------------------------------------------------------
+ * Squeeze-and-excite module, fp32, NCHW, one launch with one grid barrier.  Replaces
+ * torch_dispatch_efficientnet_se_module_v2_short_cut_fused at its opt_level 2
+ * (cpp/efficientnet/efficientnet_se_module_binding.cu:164-227; kernel
+ * cpp/efficientnet/kernels/se_module_global_fused.cu:316-444) for any shape:
+ *   pooled[c] = mean_hw input[b][c][:];  r[j] = s * sigmoid(s), s = sum_c pooled[c] * w_reduce[j][c];
+ *   gate[c] = sigmoid(sum_j r[j] * w_expand[c][j]);  out[b][c][hw] = input[b][c][hw] + gate[c]
+ * (the reference ADDS the gate to the input, :434-436).  `pooled` (optional, [batch][channels]) receives the channel
+ * means, which the reference returns as well (:160).  `workspace`: souffle_se_module_workspace_bytes() bytes,
+ * same rules as for souffle_gemm_f16.  Asynchronous on `stream`.
+ * ------------------------------------------------------------------------------------------ */
+size_t souffle_se_module_workspace_bytes(int32_t batch, int32_t channels, int32_t height, int32_t width);
+int souffle_se_module_forward(const float* input, const float* w_reduce, const float* w_expand, float* out, float* pooled,
+                              int32_t batch, int32_t channels, int32_t height, int32_t width, int32_t reduce, void* workspace,
+                              size_t workspace_bytes, souffle_stream_t stream);
 
 /* Blocks until `stream` is idle, then decodes the status words in `workspace`. */
 int souffle_workspace_status(void* workspace, souffle_stream_t stream);

@@ -333,3 +333,17 @@ def swin_block(cfg: SwinConfig, x: torch.Tensor, p: Dict[str, torch.Tensor], shi
     y2 = layer_norm(X, p["ln2_g"], p["ln2_b"], cfg.eps)
     a = gelu_tanh(y2 @ p["fc1_w"].float() + p["fc1_b"].float())
     return X + a @ p["fc2_w"].float() + p["fc2_b"].float()
+
+
+def se_module(x: torch.Tensor, w_reduce: torch.Tensor, w_expand: torch.Tensor):
+    """EfficientNet squeeze-and-excite as the reference's fused kernel computes it
+    (cpp/efficientnet/kernels/se_module_global_fused.cu:316-444): channel means (:360-372), reduce GEMV with
+    s * sigmoid(s) (:375-398), expand GEMV with sigmoid (:401-425), and the gate ADDED to the input (:428-436).
+    x [B, C, H, W], w_reduce [R, C], w_expand [C, R], fp32.  Returns (pooled [B, C], out [B, C, H, W]).
+    Parity unpinned: the reference's test only prints (cpp/efficientnet/test_efficientnet_se_module.py:5-10)."""
+    x = x.double()
+    pooled = x.mean(dim=(2, 3))
+    s = pooled @ w_reduce.double().t()
+    r = s * torch.sigmoid(s)
+    gate = torch.sigmoid(r @ w_expand.double().t())
+    return pooled.float(), (x + gate[:, :, None, None]).float()

@@ -82,6 +82,9 @@ SIGNATURES = {
     "souffle_swin_block_plan_destroy": (C.c_int, [C.c_void_p]),
     "souffle_swin_block_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "souffle_swin_block_plan_status": (C.c_int, [C.c_void_p]),
+    "souffle_se_module_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
+    "souffle_se_module_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
+                                            C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_size_t, C.c_void_p]),
     "souffle_workspace_status": (C.c_int, [C.c_void_p, C.c_void_p]),
 }
 

@@ -22,6 +22,7 @@
 #include "megakernel.cu"
 #include "lstm_kernel.cu"
 #include "lstm_static.cu"
+#include "se_module.cu"
 
 namespace souffle {
 
@@ -1300,6 +1301,79 @@ int souffle_lstm_forward_static(const SouffleLstmDesc* desc, const void* w_in, c
   void* kargs[] = {&lp};
   SF_CUDA(cudaLaunchCooperativeKernel((const void*)souffle_lstm_wavefront, dim3(d.layers * kLstmParts), dim3(kLstmThreads),
                                       kargs, smem, st));
+  return SOUFFLE_OK;
+}
+
+// ======================================================================================
+// squeeze-and-excite module
+// ======================================================================================
+static void se_geometry(int batch, int channels, int hw, int sms, SeParams* p) {
+  // cut a channel image into slices until every warp of the grid has one, but not below 512 floats a slice
+  const int warps = sms * (kSeThreads / 32);
+  int slices = 1;
+  const int chans = batch * channels;
+  while (chans * slices < warps && hw / (slices * 2) >= 512) slices *= 2;
+  int slice_len = (hw + slices - 1) / slices;
+  slice_len = (slice_len + 3) & ~3;
+  slices = (hw + slice_len - 1) / slice_len;
+  p->slices = slices;
+  p->slice_len = slice_len;
+  p->items = chans * slices;
+}
+
+size_t souffle_se_module_workspace_bytes(int32_t batch, int32_t channels, int32_t height, int32_t width) {
+  if (batch < 1 || channels < 1 || height < 1 || width < 1) return 256;
+  const int hw = height * width;
+  const int max_slices = hw / 512 > 1 ? hw / 512 : 1;        // whatever the SM count, a slice has >= 512 floats
+  return 256 + (size_t)batch * channels * max_slices * sizeof(float);
+}
+
+int souffle_se_module_forward(const float* input, const float* w_reduce, const float* w_expand, float* out, float* pooled,
+                              int32_t batch, int32_t channels, int32_t height, int32_t width, int32_t reduce, void* workspace,
+                              size_t workspace_bytes, souffle_stream_t stream) {
+  if (!input || !w_reduce || !w_expand || !out) return fail(SOUFFLE_BAD_ARGUMENT, "null argument");
+  if (batch < 1 || channels < 1 || channels > kSeMaxChannels || height < 1 || width < 1 || reduce < 1 || reduce > kSeMaxReduce)
+    return fail(SOUFFLE_BAD_SHAPE, "SE module needs batch, height, width >= 1, 1 <= channels <= %d and 1 <= reduce <= %d",
+                kSeMaxChannels, kSeMaxReduce);
+  if ((long long)batch * channels * height * width >= (1ll << 31)) return fail(SOUFFLE_BAD_SHAPE, "input too large");
+  int dev = 0, sms = 0, cc = 0;
+  SF_CUDA(cudaGetDevice(&dev));
+  SF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  SF_CUDA(cudaDeviceGetAttribute(&cc, cudaDevAttrComputeCapabilityMajor, dev));
+  if (cc != 10) return fail(SOUFFLE_BAD_DEVICE, "device %d has compute capability %d.x; this library needs sm_100", dev, cc);
+  SeParams p;
+  memset(&p, 0, sizeof(p));
+  se_geometry(batch, channels, height * width, sms, &p);
+  const size_t need = 256 + (size_t)batch * channels * p.slices * sizeof(float);
+  if (!aligned16(workspace) || workspace_bytes < need)
+    return fail(SOUFFLE_BAD_POINTER, "workspace must be 16-byte aligned and hold %zu bytes", need);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  {
+    std::lock_guard<std::mutex> lock(g_ws_mutex);          // first sight of this workspace: clear its control words
+    if (g_ws_launches.find(workspace) == g_ws_launches.end()) {
+      SF_CUDA(cudaMemsetAsync(workspace, 0, 128, st));
+      g_ws_launches.emplace(workspace, 0u);
+    }
+  }
+  const size_t smem = (size_t)(kSeCacheFloats + kSeMaxChannels + kSeMaxReduce) * sizeof(float);
+  static bool attr_set[16] = {};
+  if (dev < 16 && !attr_set[dev]) {
+    SF_CUDA(cudaFuncSetAttribute(souffle_se_module, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr_set[dev] = true;
+  }
+  const int warps_per_cta = kSeThreads / 32;
+  const int ctas = (p.items + warps_per_cta - 1) / warps_per_cta;
+  const int grid = ctas < sms ? ctas : sms;
+  const int per_warp = (p.items + grid * warps_per_cta - 1) / (grid * warps_per_cta);
+  p.input = input; p.w_reduce = w_reduce; p.w_expand = w_expand; p.out = out; p.pooled = pooled;
+  p.sync = reinterpret_cast<unsigned*>(workspace) + 8;        // words 8, 9: the SE barrier (the GEMM entries use 0..3)
+  p.status = reinterpret_cast<int*>(reinterpret_cast<char*>(workspace) + 64);
+  p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + 256);
+  p.batch = batch; p.channels = channels; p.hw = height * width; p.reduce = reduce;
+  p.cache = (long long)per_warp * p.slice_len <= kSeCacheFloats / warps_per_cta ? 1 : 0;
+  p.timeout_ns = 2000ull * 1000000ull;
+  void* kargs[] = {&p};
+  SF_CUDA(cudaLaunchCooperativeKernel((const void*)souffle_se_module, dim3(grid), dim3(kSeThreads), kargs, smem, st));
   return SOUFFLE_OK;
 }
 

@@ -119,3 +119,16 @@ def test_swin_mlp_and_gemm():
     w2 = torch.randn(128, 64, generator=g).half()
     h, o = so.swin_mlp(a, w1, w2)
     assert torch.allclose(h, a.float() @ w1.float()) and torch.allclose(o, h @ w2.float())
+
+
+def test_se_module_hand_computed():
+    """One channel pair, 2 x 2 image: every number of the squeeze-and-excite chain by hand."""
+    import math
+    x = torch.tensor([[[[1.0, 2.0], [3.0, 4.0]], [[0.0, 0.0], [0.0, 8.0]]]])       # means 2.5 and 2.0
+    wr = torch.tensor([[1.0, -1.0]])                                                 # s = 0.5
+    we = torch.tensor([[2.0], [0.0]])
+    pooled, out = so.se_module(x, wr, we)
+    assert torch.allclose(pooled, torch.tensor([[2.5, 2.0]]))
+    r = 0.5 / (1.0 + math.exp(-0.5))
+    g0, g1 = 1.0 / (1.0 + math.exp(-2.0 * r)), 0.5
+    assert torch.allclose(out[0, 0], x[0, 0] + g0, atol=1e-6) and torch.allclose(out[0, 1], x[0, 1] + g1, atol=1e-6)
