@@ -180,7 +180,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     so, cfg, layers, x, lens = make_workload(per)
     xs, ls = sharding.shard_batch(x, lens, rank, world)
     dev_layers = [{k: v.cuda() for k, v in w.items()} for w in layers]
-    enc = bert.BertEncoder(per, SEQ, HEADS, HEAD_DIM, FFN, dev_layers)
+    enc = bert.BertEncoder(per, SEQ, HEADS, HEAD_DIM, FFN, dev_layers, tuning={"autotune": 1})
     x_d, l_d = xs.cuda(), ls.cuda()
     y_d = torch.empty_like(x_d)
     full = torch.empty(BATCH, SEQ, HIDDEN, dtype=torch.float16, device="cuda") if world > 1 else None
@@ -275,6 +275,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                    "sequences_per_gpu": per, "parallelism": f"replicas x{world}, output all-gather" if world > 1 else "single GPU",
                    "l2": "no flush: 170 MB of weights per step exceed the 126 MB L2", "grid": info["grid"],
                    "stages_per_launch": info["stages"],
+                   "tiles": "timed at plan creation (desc.autotune): " + ", ".join(
+                       "%dx%d/%d" % (t["bm"], t["bn"], t["splitk"]) for t in (enc.stage_info(i) for i in (0, 2, 4, 5))),
                    "e2e": ("pinned host in/out per step; steps pipelined over copy-in, compute and copy-out streams"
                            if world == 1 else "pinned host shard in, gathered result out per step; steps pipelined over three streams")},
         "e2e": {"value": BATCH / (ms_e2e * 1e-3), "unit": "sequences/s",

@@ -75,6 +75,10 @@ typedef struct SouffleBertDesc {
   int32_t debug_skip_arrival; /* failure-detection test hook, 0 = off: CTA (value-1) leaves at the first grid
                                  barrier without arriving, so the others run into the wait limit and the
                                  launch ends with SOUFFLE_DEVICE_TIMEOUT (nothing is in flight at that point) */
+  int32_t autotune;   /* 1: plan creation times the likeliest tilings of every GEMM stage on the device (a few
+                         launches each on the plan's own buffers, tens of milliseconds in all) and keeps the
+                         fastest; stages with an explicit bm_ / bn_ / split_ setting are left alone.  0: tiles come
+                         from the cycle model alone.  Two plans of one shape may then differ in summation order. */
 } SouffleBertDesc;
 
 /* Device pointers to one layer's parameters, fp16.  Matrices use the reference's [K][N]

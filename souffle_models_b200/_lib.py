@@ -24,7 +24,7 @@ class BertDesc(C.Structure):
                                          "keep_probs")] + [("eps", C.c_float)] + \
                [(n, C.c_int32) for n in ("bn_qkv", "bn_fc1", "bn_proj", "split_proj", "bn_fc2", "split_fc2",
                                          "max_ctas", "timeout_ms", "profile", "bm_qkv", "bm_fc1", "bm_proj",
-                                         "bm_fc2", "debug_max_slots", "debug_skip_arrival")]
+                                         "bm_fc2", "debug_max_slots", "debug_skip_arrival", "autotune")]
 
 
 class BertLayerWeights(C.Structure):

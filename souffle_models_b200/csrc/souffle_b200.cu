@@ -12,6 +12,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
+#include <algorithm>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -139,7 +140,12 @@ __global__ void transpose_kn_to_nk(const __half* __restrict__ src, __half* __res
 struct TileChoice {
   int bm = 128, bn = 0, split = 1;
 };
-static TileChoice choose_tiles(int M, int N, int K, int sms, bool allow_split, bool b_mn, int head_split = 0) {
+struct RankedTile {
+  double cost;
+  TileChoice t;
+};
+static TileChoice choose_tiles(int M, int N, int K, int sms, bool allow_split, bool b_mn, int head_split = 0,
+                               std::vector<RankedTile>* ranked = nullptr) {
   const int kch = K / 64;
   double best = 1e300;
   TileChoice bt;
@@ -163,6 +169,11 @@ static TileChoice choose_tiles(int M, int N, int K, int sms, bool allow_split, b
         const double tile = (kch / split) * chunk + (bm == 256 ? 0.7 : 0.45) * epilogue + 1500.0;
         double cost = waves * tile;
         if (allow_split) cost += (double)split * M * N * 8.0 / sms / 12.0;
+        if (ranked) {
+          RankedTile r;
+          r.cost = cost; r.t.bm = bm; r.t.bn = bn; r.t.split = split;
+          ranked->push_back(r);
+        }
         if (cost < best - 1e-9) {
           best = cost;
           bt.bm = bm; bt.bn = bn; bt.split = split;
@@ -170,6 +181,7 @@ static TileChoice choose_tiles(int M, int N, int K, int sms, bool allow_split, b
       }
     }
   }
+  if (ranked) std::stable_sort(ranked->begin(), ranked->end(), [](const RankedTile& a, const RankedTile& b) { return a.cost < b.cost; });
   return bt;
 }
 
@@ -341,6 +353,71 @@ static Stage blank_stage(int type) {
   return s;
 }
 
+// Times the likeliest tilings of one GEMM stage on the device and returns the fastest.  `proto` is the stage as
+// the plan will build it (shape, epilogue, output pointers) without tile fields; its operands are read through
+// per-call tensor maps over `a` ([M][K]) and `w` ([N][K]), whose contents do not matter for the timing.  A stage
+// that writes split-K planes is timed together with the LayerNorm stage that sums them (`ln_proto`), since more
+// planes make that one slower.  Failures of any kind leave `*choice` as the cycle model set it.
+static void autotune_gemm(const Stage& proto, const Stage* ln_proto, const void* a, const void* w, int sms, bool allow_split,
+                          int head_split, int max_split, void* tune_ws, TileChoice* choice) {
+  std::vector<RankedTile> ranked;
+  choose_tiles(proto.M, proto.N, proto.K, sms, allow_split, false, head_split, &ranked);
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) return;
+  float best_ms = 1e30f;
+  int measured = 0;
+  for (size_t ci = 0; ci < ranked.size() && measured < 16; ++ci) {
+    const TileChoice t = ranked[ci].t;
+    if (t.split > max_split) continue;
+    CallArgs args;
+    memset(&args, 0, sizeof(args));
+    Stage& g = args.inline_stages[0];
+    g = proto;
+    g.tm_a = -1; g.tm_b = -2; g.bm = t.bm; g.bn = t.bn; g.splitk = t.split;
+    if (finalize_stage(g, 0, 1)) continue;
+    if (make_map_uncached(&args.call_maps[0], a, (uint64_t)proto.M, (uint64_t)proto.K, (uint32_t)t.bm)) continue;
+    if (make_map_uncached(&args.call_maps[1], w, (uint64_t)proto.N, (uint64_t)proto.K, (uint32_t)t.bn)) continue;
+    int items = stage_items(g);
+    args.p.n_stages = 1;
+    if (ln_proto) {
+      Stage& ln = args.inline_stages[1];
+      ln = *ln_proto;
+      ln.n_partial = t.split;
+      const int li = stage_items(ln);
+      if (li > items) items = li;
+      args.p.n_stages = 2;
+    }
+    const int grid = items < sms ? items : sms;
+    if (ln_proto && finalize_stage(args.inline_stages[1], 0, grid)) continue;
+    args.p.sync = reinterpret_cast<unsigned*>(tune_ws);
+    args.p.sync_next = args.p.sync + 2;
+    args.p.status = reinterpret_cast<int*>(reinterpret_cast<char*>(tune_ws) + 64);
+    args.p.timeout_ns = 200ull * 1000000ull;
+    bool ok = true;
+    for (int it = 0; it < 26 && ok; ++it) {                // two warm-up launches, twenty-four timed ones
+      ok = cudaMemsetAsync(tune_ws, 0, 128, nullptr) == cudaSuccess;
+      if (it == 2) ok = ok && cudaEventRecord(e0, nullptr) == cudaSuccess;
+      ok = ok && launch_mega(args, grid, nullptr, kFamilyBert) == SOUFFLE_OK;
+    }
+    float ms = 0.0f;
+    int h[4] = {0, 0, 0, 0};
+    ok = ok && cudaEventRecord(e1, nullptr) == cudaSuccess && cudaEventSynchronize(e1) == cudaSuccess &&
+         cudaEventElapsedTime(&ms, e0, e1) == cudaSuccess &&
+         cudaMemcpy(h, reinterpret_cast<char*>(tune_ws) + 64, sizeof(h), cudaMemcpyDeviceToHost) == cudaSuccess && h[0] == DEV_OK;
+    if (!ok) {
+      cudaGetLastError();
+      continue;
+    }
+    ++measured;
+    if (ms < best_ms) {
+      best_ms = ms;
+      *choice = t;
+    }
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+}
+
 static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* layers) {
   const SouffleBertDesc& d = p->desc;
   DeviceInfo* di = nullptr;
@@ -384,6 +461,47 @@ static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* la
   if (d.bm_fc2) t_fc2.bm = d.bm_fc2;
   if (d.bn_fc2) t_fc2.bn = d.bn_fc2;
   if (d.split_fc2) t_fc2.split = d.split_fc2;
+  if (d.autotune) {
+    // Scratch for the measurements: a weight-shaped operand, as many fp32 planes as the deepest split tried
+    // (capped at 256 MB), barrier words.  Activation-shaped operands are the plan's own buffers.
+    const size_t w_bytes = (size_t)(3 * H > F ? 3 * H : F) * H * 2;
+    int max_split = (int)((256ull << 20) / ((size_t)M * H * 4));
+    max_split = max_split > 16 ? 16 : (max_split < 1 ? 1 : max_split);
+    void *w_tmp = nullptr, *planes = nullptr, *tune_ws = nullptr;
+    if (cudaMalloc(&w_tmp, w_bytes) == cudaSuccess && cudaMalloc(&planes, (size_t)max_split * M * H * 4) == cudaSuccess &&
+        cudaMalloc(&tune_ws, 256) == cudaSuccess && cudaMemset(w_tmp, 0, w_bytes) == cudaSuccess) {
+      Stage ln = blank_stage(STAGE_LN);
+      ln.M = M; ln.N = H; ln.ldo = H; ln.partial = reinterpret_cast<float*>(planes); ln.resid = p->ctx; ln.out = p->ln1;
+      ln.eps = d.eps;
+      Stage g = blank_stage(STAGE_GEMM);
+      g.M = M; g.batch = B; g.heads = Hh; g.seq = S; g.head_dim = hd;
+      if (!d.bm_qkv && !d.bn_qkv) {
+        Stage q = g;
+        q.N = 3 * H; q.K = H; q.epi = EPI_QKV; q.out = p->qkv; q.ldo = H;
+        autotune_gemm(q, nullptr, p->ln1, w_tmp, sms, false, 1, 1, tune_ws, &t_qkv);
+      }
+      if (!d.bm_fc1 && !d.bn_fc1) {
+        Stage f = g;
+        f.N = F; f.K = H; f.epi = EPI_F16; f.act = std_variant ? ACT_GELU : ACT_RELU; f.out = p->fc1; f.ldo = F;
+        autotune_gemm(f, nullptr, p->ln1, w_tmp, sms, false, 0, 1, tune_ws, &t_fc1);
+      }
+      if (!d.bm_proj && !d.bn_proj && !d.split_proj) {
+        Stage f = g;
+        f.N = H; f.K = H; f.epi = EPI_PARTIAL; f.partial = reinterpret_cast<float*>(planes); f.ldo = H;
+        autotune_gemm(f, &ln, p->ctx, w_tmp, sms, true, 0, max_split, tune_ws, &t_proj);
+      }
+      if (!d.bm_fc2 && !d.bn_fc2 && !d.split_fc2) {
+        Stage f = g;
+        f.N = H; f.K = F; f.epi = EPI_PARTIAL; f.partial = reinterpret_cast<float*>(planes); f.ldo = H;
+        autotune_gemm(f, &ln, p->fc1, w_tmp, sms, true, 0, max_split, tune_ws, &t_fc2);
+      }
+    }
+    cudaDeviceSynchronize();
+    cudaGetLastError();
+    if (w_tmp) cudaFree(w_tmp);
+    if (planes) cudaFree(planes);
+    if (tune_ws) cudaFree(tune_ws);
+  }
   auto bad_tile = [](const TileChoice& t, int N) {
     return (t.bm != 128 && t.bm != 256) || t.bn < 16 || t.bn > 256 || t.bn % 16 || N % t.bn ||
            196608 / ((t.bm + t.bn) * 128) < 2;

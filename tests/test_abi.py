@@ -36,7 +36,7 @@ def test_every_declared_symbol_is_exported_and_bound():
 
 
 def test_struct_layout_matches_header():
-    assert C.sizeof(_lib.BertDesc) == 4 * 24
+    assert C.sizeof(_lib.BertDesc) == 4 * 25
     assert C.sizeof(_lib.BertLayerWeights) == 8 * 12
     assert C.sizeof(_lib.LstmDesc) == 4 * 5
     assert C.sizeof(_lib.SwinDesc) == 4 * 11 and C.sizeof(_lib.SwinWeights) == 8 * 13

@@ -124,6 +124,22 @@ def test_tile_overrides_agree():
     assert (y0 - y1).abs().max() < 4e-3
 
 
+def test_autotuned_plan_matches_the_oracle():
+    """desc.autotune: tilings picked by timing them at plan creation; any of them is the same product."""
+    cfg = so.BertConfig(4, 128, 12, 64, 3072, "std")
+    layers = so.make_bert_weights(cfg, 13, 1, zero_bias=False)
+    x, lens = so.make_bert_input(cfg, 13, ragged=True)
+    enc = _encoder(cfg, layers, tuning=dict(autotune=1))
+    y = enc.forward(x.cuda(), lens.cuda())
+    enc.status()
+    assert _err(y, so.bert_layer(cfg, x, layers[0], lens)["out"]) < TOL_LAYER
+    for i in (0, 2, 4, 5):
+        t = enc.stage_info(i)
+        assert t["type"] == 0 and t["bm"] in (128, 256) and 16 <= t["bn"] <= 256 and t["splitk"] >= 1
+    fixed = _encoder(cfg, layers, tuning=dict(autotune=1, bm_fc1=128, bn_fc1=64))       # explicit settings win
+    assert (fixed.stage_info(4)["bm"], fixed.stage_info(4)["bn"]) == (128, 64)
+
+
 def test_stage_info_reports_the_tiling():
     cfg = so.BertConfig(2, 128, 12, 64, 3072, "std")
     layers = so.make_bert_weights(cfg, 5, 1)
