@@ -1336,27 +1336,31 @@ __device__ __forceinline__ void ln_rows2(const float* pl0, const float* pl1, int
     vb += __shfl_xor_sync(0xffffffffu, vb, o);
   }
   const float rstd0 = rsqrtf(va * inv_n + eps), rstd1 = rsqrtf(vb * inv_n + eps);
+  // (z - mean) * rstd in fp32 (one FMA), rounded to fp16 pairs; gamma and beta are applied on the pairs (one packed
+  // FMA per two elements, no conversions).  With gamma = 1, beta = 0 that last step is exact.
+  const float nm0 = -mean0 * rstd0, nm1 = -mean1 * rstd1;
 #pragma unroll
   for (int j = 0; j < NJ; ++j) {
-    float g[4] = {1.f, 1.f, 1.f, 1.f}, bt[4] = {0.f, 0.f, 0.f, 0.f};
+    uint2 ug = make_uint2(0u, 0u), ub = make_uint2(0u, 0u);
     if (gamma) {
-      const uint2 ug = *reinterpret_cast<const uint2*>(gamma + (lane + 32 * j) * 4);
-      const uint2 ub = *reinterpret_cast<const uint2*>(beta + (lane + 32 * j) * 4);
-      const float2 g0 = __half22float2(*reinterpret_cast<const __half2*>(&ug.x));
-      const float2 g1 = __half22float2(*reinterpret_cast<const __half2*>(&ug.y));
-      const float2 b0 = __half22float2(*reinterpret_cast<const __half2*>(&ub.x));
-      const float2 b1 = __half22float2(*reinterpret_cast<const __half2*>(&ub.y));
-      g[0] = g0.x; g[1] = g0.y; g[2] = g1.x; g[3] = g1.y;
-      bt[0] = b0.x; bt[1] = b0.y; bt[2] = b1.x; bt[3] = b1.y;
+      ug = *reinterpret_cast<const uint2*>(gamma + (lane + 32 * j) * 4);
+      ub = *reinterpret_cast<const uint2*>(beta + (lane + 32 * j) * 4);
     }
-    float y[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) y[i] = fmaf((z[0][j][i] - mean0) * rstd0, g[i], bt[i]);
-    *reinterpret_cast<uint2*>(out0 + (lane + 32 * j) * 4) = make_uint2(pack_h2(y[0], y[1]), pack_h2(y[2], y[3]));
-    if (two) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) y[i] = fmaf((z[1][j][i] - mean1) * rstd1, g[i], bt[i]);
-      *reinterpret_cast<uint2*>(out1 + (lane + 32 * j) * 4) = make_uint2(pack_h2(y[0], y[1]), pack_h2(y[2], y[3]));
+    for (int r = 0; r < 2; ++r) {
+      if (r == 1 && !two) break;
+      const float rs_ = r ? rstd1 : rstd0, nm = r ? nm1 : nm0;
+      uint32_t w0 = pack_h2(fmaf(z[r][j][0], rs_, nm), fmaf(z[r][j][1], rs_, nm));
+      uint32_t w1 = pack_h2(fmaf(z[r][j][2], rs_, nm), fmaf(z[r][j][3], rs_, nm));
+      if (gamma) {
+        const __half2 y0 = __hfma2(*reinterpret_cast<const __half2*>(&w0), *reinterpret_cast<const __half2*>(&ug.x),
+                                   *reinterpret_cast<const __half2*>(&ub.x));
+        const __half2 y1 = __hfma2(*reinterpret_cast<const __half2*>(&w1), *reinterpret_cast<const __half2*>(&ug.y),
+                                   *reinterpret_cast<const __half2*>(&ub.y));
+        w0 = *reinterpret_cast<const uint32_t*>(&y0);
+        w1 = *reinterpret_cast<const uint32_t*>(&y1);
+      }
+      *reinterpret_cast<uint2*>((r ? out1 : out0) + (lane + 32 * j) * 4) = make_uint2(w0, w1);
     }
   }
 }
