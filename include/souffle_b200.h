@@ -274,6 +274,17 @@ typedef struct SouffleSwinPlan SouffleSwinPlan;
 /* `weights` is a host array of n_blocks records. */
 int souffle_swin_block_plan_create(const SouffleSwinDesc* desc, const SouffleSwinWeights* weights,
                                    SouffleSwinPlan** plan_out);
+/* The same with the patch merging that ends a stage of the network run inside the launch
+ * (python/models/swin_transformer/swin_patch_merge.py:1-17: tokens (2h,2w), (2h+1,2w), (2h,2w+1), (2h+1,2w+1)
+ * concatenated to 4*dim channels, LayerNorm over them, reduction to 2*dim without bias): three more stages, the
+ * gather done by the LayerNorm stage's copies.  `merge` null = blocks only; dim <= 512 and res even with it.
+ * y is then [batch*(res/2)^2][2*dim]. */
+typedef struct SouffleSwinMerge {
+  const void *norm_g, *norm_b; /* fp16 [4*dim], both or neither */
+  const void* reduction_w;     /* fp16 [4*dim][2*dim], [K][N] row-major */
+} SouffleSwinMerge;
+int souffle_swin_stage_plan_create(const SouffleSwinDesc* desc, const SouffleSwinWeights* weights,
+                                   const SouffleSwinMerge* merge, SouffleSwinPlan** plan_out);
 int souffle_swin_block_plan_destroy(SouffleSwinPlan* plan);
 /* y[batch*res*res][dim] = block_{n-1}(... block_0(x)); fp16 device buffers; asynchronous on `stream`. */
 int souffle_swin_block_forward(SouffleSwinPlan* plan, const void* x, void* y, souffle_stream_t stream);

@@ -335,6 +335,27 @@ def swin_block(cfg: SwinConfig, x: torch.Tensor, p: Dict[str, torch.Tensor], shi
     return X + a @ p["fc2_w"].float() + p["fc2_b"].float()
 
 
+def make_swin_merge_params(cfg: SwinConfig, seed: int, zero_bias=True):
+    g = torch.Generator().manual_seed(seed)
+    C4 = 4 * cfg.dim
+    if zero_bias:
+        ng, nb = torch.ones(C4).half(), torch.zeros(C4).half()
+    else:
+        ng, nb = (1.0 + torch.randn(C4, generator=g) * 0.05).half(), (torch.randn(C4, generator=g) * 0.05).half()
+    return dict(norm_g=ng, norm_b=nb, reduction_w=(torch.randn(C4, 2 * cfg.dim, generator=g) * 0.02).half())
+
+
+def swin_patch_merge(cfg: SwinConfig, x: torch.Tensor, m: Dict[str, torch.Tensor]) -> torch.Tensor:
+    """Patch merging on [res*res, C] -> [(res/2)^2, 2C]: channel block q of merged token (h, w) is input token
+    (2h + q % 2, 2w + q // 2) (python/models/swin_transformer/swin_patch_merge.py:4-9 and the index expression at
+    :39-44), LayerNorm over the 4C channels (:11, :103-118), reduction 4C -> 2C without bias (:12, :121-123)."""
+    R, C = cfg.res, cfg.dim
+    X = x.float().reshape(R, R, C)
+    merged = torch.cat([X[0::2, 0::2], X[1::2, 0::2], X[0::2, 1::2], X[1::2, 1::2]], -1).reshape(-1, 4 * C)
+    y = layer_norm(merged, m["norm_g"], m["norm_b"], cfg.eps)
+    return y @ m["reduction_w"].float()
+
+
 def se_module(x: torch.Tensor, w_reduce: torch.Tensor, w_expand: torch.Tensor):
     """EfficientNet squeeze-and-excite as the reference's fused kernel computes it
     (cpp/efficientnet/kernels/se_module_global_fused.cu:316-444): channel means (:360-372), reduce GEMV with

@@ -37,6 +37,10 @@ class SwinDesc(C.Structure):
                [("eps", C.c_float), ("timeout_ms", C.c_int32), ("n_blocks", C.c_int32), ("shift_alt", C.c_int32)]
 
 
+class SwinMerge(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("norm_g", "norm_b", "reduction_w")]
+
+
 class SwinWeights(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in ("ln1_g", "ln1_b", "qkv_w", "qkv_b", "rel_bias", "proj_w", "proj_b", "ln2_g",
                                           "ln2_b", "fc1_w", "fc1_b", "fc2_w", "fc2_b")]
@@ -79,6 +83,8 @@ SIGNATURES = {
                                             C.c_void_p, C.c_int32, C.c_int32, C.c_float, C.c_void_p, C.c_size_t,
                                             C.c_void_p]),
     "souffle_swin_block_plan_create": (C.c_int, [C.POINTER(SwinDesc), C.POINTER(SwinWeights), C.POINTER(C.c_void_p)]),
+    "souffle_swin_stage_plan_create": (C.c_int, [C.POINTER(SwinDesc), C.POINTER(SwinWeights), C.POINTER(SwinMerge),
+                                                 C.POINTER(C.c_void_p)]),
     "souffle_swin_block_plan_destroy": (C.c_int, [C.c_void_p]),
     "souffle_swin_block_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "souffle_swin_block_plan_status": (C.c_int, [C.c_void_p]),

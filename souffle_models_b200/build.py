@@ -59,8 +59,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 
 def resource_usage() -> dict:
-    """Compiles without linking and returns {kernel: (registers, spill_store_bytes, spill_load_bytes)} from
-    `ptxas -v`.  The persistent kernels must not spill: a spilling epilogue cost 10-25% end to end."""
+    """Compiles without linking and returns {function: (registers, spill_store_bytes, spill_load_bytes)} from
+    `ptxas -v`: the kernels, and the out-of-line device functions they call (registers 0 for those: ptxas reports
+    none per function).  The persistent kernels must not spill in their stages: a spilling epilogue cost 10-25%
+    end to end."""
     import re
     import tempfile
     with tempfile.TemporaryDirectory() as tmp:
@@ -69,15 +71,20 @@ def resource_usage() -> dict:
         res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
-    out, name = {}, None
+    out, name, func = {}, None, None
     spills = (0, 0)
     for line in res.stderr.splitlines():
         m = re.search(r"Compiling entry function '(\w+)'", line)
         if m:
             name = m.group(1)
+        m = re.search(r"Function properties for (\w+)", line)
+        if m:
+            func = m.group(1)
         m = re.search(r"(\d+) bytes spill stores, (\d+) bytes spill loads", line)
         if m:
             spills = (int(m.group(1)), int(m.group(2)))
+            if func != name:                      # an out-of-line device function of the kernel being compiled
+                out.setdefault(func, (0,) + spills)
         m = re.search(r"Used (\d+) registers", line)
         if m and name:
             out[name] = (int(m.group(1)),) + spills

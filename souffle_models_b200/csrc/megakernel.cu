@@ -1365,6 +1365,72 @@ __device__ __forceinline__ void ln_rows2(const float* pl0, const float* pl1, int
   }
 }
 
+// Patch-merging gather (one lane): row (img, h, w) of the merged matrix = tokens (2h, 2w), (2h+1, 2w), (2h, 2w+1),
+// (2h+1, 2w+1) of a [batch][R][R][N/4] fp16 grid side by side, one bulk copy each.
+__device__ __noinline__ void ln_gather_rows(uint32_t dst, const __half* src, int row0, int rows, int N, int R, uint32_t bar) {
+  const int R2 = R >> 1, Cq = N >> 2;
+  for (int r = 0; r < rows; ++r) {
+    const int gr = row0 + r, img = gr / (R2 * R2), rem = gr - img * R2 * R2, h2 = rem / R2, w2 = rem - h2 * R2;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const size_t token = (size_t)img * R * R + (size_t)(2 * h2 + (q & 1)) * R + (2 * w2 + (q >> 1));
+      bulk_load(dst + (uint32_t)(r * N + q * Cq) * 2u, src + token * Cq, (uint32_t)(Cq * 2), bar);
+    }
+  }
+}
+
+// LayerNorm of one fp16 row of 2048 columns held in shared memory (the merged rows of a C = 512 stage): too wide
+// for the two-rows-per-warp routine's registers.  Same arithmetic: two-pass fp32 statistics, packed-half affine.
+__device__ __noinline__ void ln_row_wide(const __half* row, const __half* gamma, const __half* beta, float eps, __half* out, int lane) {
+  constexpr int NJ = 16;
+  float z[NJ][4];
+  float sa = 0.0f;
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) {
+    const uint2 u = *reinterpret_cast<const uint2*>(row + (lane + 32 * j) * 4);
+    const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
+    const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+    z[j][0] = f0.x; z[j][1] = f0.y; z[j][2] = f1.x; z[j][3] = f1.y;
+    sa += (f0.x + f0.y) + (f1.x + f1.y);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sa += __shfl_xor_sync(0xffffffffu, sa, o);
+  const float inv_n = 1.0f / (float)(NJ * 128), mean = sa * inv_n;
+  float va = 0.0f;
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float d0 = z[j][i] - mean;
+      va = fmaf(d0, d0, va);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) va += __shfl_xor_sync(0xffffffffu, va, o);
+  const float rstd = rsqrtf(va * inv_n + eps), nm = -mean * rstd;
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) {
+    uint32_t w0 = pack_h2(fmaf(z[j][0], rstd, nm), fmaf(z[j][1], rstd, nm));
+    uint32_t w1 = pack_h2(fmaf(z[j][2], rstd, nm), fmaf(z[j][3], rstd, nm));
+    if (gamma) {
+      const uint2 ug = __ldg(reinterpret_cast<const uint2*>(gamma + (lane + 32 * j) * 4));
+      const uint2 ub = __ldg(reinterpret_cast<const uint2*>(beta + (lane + 32 * j) * 4));
+      const __half2 y0 = __hfma2(*reinterpret_cast<const __half2*>(&w0), *reinterpret_cast<const __half2*>(&ug.x),
+                                 *reinterpret_cast<const __half2*>(&ub.x));
+      const __half2 y1 = __hfma2(*reinterpret_cast<const __half2*>(&w1), *reinterpret_cast<const __half2*>(&ug.y),
+                                 *reinterpret_cast<const __half2*>(&ub.y));
+      w0 = *reinterpret_cast<const uint32_t*>(&y0);
+      w1 = *reinterpret_cast<const uint32_t*>(&y1);
+    }
+    *reinterpret_cast<uint2*>(out + (lane + 32 * j) * 4) = make_uint2(w0, w1);
+  }
+}
+
+// kMerge builds add the patch-merging form (Swin, python/models/swin_transformer/swin_patch_merge.py:1-17): with
+// st.seq = R > 0 the fp16 input is a [batch][R][R][N/4] token grid and row (b, h, w) of the normalised matrix is the
+// concatenation of tokens (2h, 2w), (2h+1, 2w), (2h, 2w+1), (2h+1, 2w+1), fetched as four bulk copies; rows of 2048
+// columns are normalised one per warp and call.
+template <bool kMerge>
 __device__ __forceinline__ void ln_stage(const Stage& st, const MegaParams& p, SmemCtl& cs, uint32_t ring, uint8_t* ring_ptr,
                                          __half* vec_s, RoleState& rs, const WaitCtl& ctl, int warp, int lane) {
   const int N = st.N, M = st.M, P = st.n_partial;
@@ -1398,6 +1464,12 @@ __device__ __forceinline__ void ln_stage(const Stage& st, const MegaParams& p, S
         const uint32_t bar = full0 + 8 * buf;
         const uint32_t dst = ring + buf * batch_bytes;
         mbar_expect_tx(bar, (uint32_t)(rows * row_bytes));
+        if (kMerge && st.seq > 0) {
+          ln_gather_rows(dst, resid, row0, rows, N, st.seq, bar);
+          bits ^= 1u << buf;
+          buf = buf + 1 == nbuf ? 0 : buf + 1;
+          continue;
+        }
         for (int pl = 0; pl < P; ++pl)
           bulk_load(dst + pl * rb * N * 4, st.partial + ((size_t)pl * M + row0) * N, (uint32_t)(rows * N * 4), bar);
         if (resid) bulk_load(dst + P * rb * N * 4, resid + (size_t)row0 * N, (uint32_t)(rows * N * 2), bar);
@@ -1452,6 +1524,12 @@ __device__ __forceinline__ void ln_stage(const Stage& st, const MegaParams& p, S
           case 2: ln_rows2<2>(pl0, pl1, P, rb * N, ra, rb2, bias, gamma, beta, st.eps, o0, o1, lane); break;
           case 4: ln_rows2<4>(pl0, pl1, P, rb * N, ra, rb2, bias, gamma, beta, st.eps, o0, o1, lane); break;
           case 6: ln_rows2<6>(pl0, pl1, P, rb * N, ra, rb2, bias, gamma, beta, st.eps, o0, o1, lane); break;
+          case 16:
+            if constexpr (kMerge) {
+              ln_row_wide(ra, gamma, beta, st.eps, o0, lane);
+              if (two) ln_row_wide(rb2, gamma, beta, st.eps, o1, lane);
+            }
+            break;
           default: ln_rows2<8>(pl0, pl1, P, rb * N, ra, rb2, bias, gamma, beta, st.eps, o0, o1, lane); break;
         }
       }
@@ -1501,7 +1579,7 @@ __device__ __noinline__ void gemm_stage_ool(const Stage& st, const CallArgs& ca,
 }
 __device__ __noinline__ void ln_stage_ool(const Stage& st, const MegaParams& p, SmemCtl& cs, uint32_t ring, uint8_t* ring_ptr,
                                           __half* vec_s, RoleState& rs, const WaitCtl& ctl, int warp, int lane) {
-  ln_stage(st, p, cs, ring, ring_ptr, vec_s, rs, ctl, warp, lane);
+  ln_stage<true>(st, p, cs, ring, ring_ptr, vec_s, rs, ctl, warp, lane);
 }
 
 template <int kFamily>
@@ -1592,7 +1670,7 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
         if constexpr (kFamily == kFamilyBert) attn_stage_pp(st, ca, cs, ring, ring_ptr, stage_s, rs, ctl, warp, lane);
         else attn_stage(st, ca, cs, ring, ring_ptr, stage_s, rs, ctl, warp, lane);
       } else if (st.type == STAGE_LN) {
-        ln_stage(st, p, cs, ring, ring_ptr, vec_s, rs, ctl, warp, lane);
+        ln_stage<false>(st, p, cs, ring, ring_ptr, vec_s, rs, ctl, warp, lane);
       }
     }
     if (si + 1 < p.n_stages) {

@@ -1053,6 +1053,8 @@ int souffle_layernorm_forward(const float* partial, int32_t n_partial, const voi
 struct SouffleSwinPlan {
   SouffleBertPlan base;
   SouffleSwinDesc desc;
+  SouffleSwinMerge merge = {nullptr, nullptr, nullptr};
+  bool has_merge = false;
 };
 
 static int launch_plan(SouffleBertPlan* plan, const void* x, void* y, const int32_t* lens, int timeout_ms, cudaStream_t st) {
@@ -1124,6 +1126,8 @@ static int build_swin_plan(SouffleSwinPlan* sp, const SouffleSwinWeights* blocks
   if ((rc = plan_alloc(p, (void**)&planes, (size_t)t_fc2.split * T * C * 4))) return rc;
   for (int i = 0; i < 2 && i < n_blocks - 1; ++i)
     if ((rc = plan_alloc(p, (void**)&xbuf[i], (size_t)T * C * 2))) return rc;
+  __half* xlast = nullptr;          // output of the last block when patch merging follows inside the launch
+  if (sp->has_merge && (rc = plan_alloc(p, (void**)&xlast, (size_t)T * C * 2))) return rc;
   if ((rc = plan_alloc(p, (void**)&p->d_sync, 64))) return rc;
   if ((rc = plan_alloc(p, (void**)&p->d_status, 64))) return rc;
   SF_CUDA(cudaMemset(p->d_sync, 0, 64));
@@ -1211,13 +1215,48 @@ static int build_swin_plan(SouffleSwinPlan* sp, const SouffleSwinWeights* blocks
     p->stages.push_back(s);
     s = blank_stage(STAGE_LN);                             // planes + bias + x1 -> block output (no normalisation)
     s.M = T; s.N = C; s.ldo = C; s.partial = planes; s.n_partial = t_fc2.split; s.bias = fc2_b; s.resid = x1; s.eps = -1.0f;
-    if (last) s.out_sel = PTR_CALL_Y; else s.out = xbuf[bi & 1];
+    if (last && !sp->has_merge) s.out_sel = PTR_CALL_Y; else s.out = last ? xlast : xbuf[bi & 1];
+    p->stages.push_back(s);
+  }
+  if (sp->has_merge) {
+    // Patch merging (python/models/swin_transformer/swin_patch_merge.py:1-17): 2 x 2 neighbourhoods concatenated to
+    // 4C channels (gathered by the LayerNorm stage's copies), LayerNorm, reduction 4C -> 2C without bias.  The
+    // reduction has (R/2)^2 rows per image and K = 4C: it is cut along K, a sum-only stage adds the planes.
+    const int Tm = d.batch * (R / 2) * (R / 2), C4 = 4 * C, C2 = 2 * C;
+    const TileChoice t_red = choose_tiles(Tm, C2, C4, sms, true, false, 0);
+    __half *merged, *wr_t;
+    float* planes2;
+    if ((rc = plan_alloc(p, (void**)&merged, (size_t)Tm * C4 * 2))) return rc;
+    if ((rc = plan_alloc(p, (void**)&wr_t, (size_t)C4 * C2 * 2))) return rc;
+    if ((rc = plan_alloc(p, (void**)&planes2, (size_t)t_red.split * Tm * C2 * 4))) return rc;
+    transpose_kn_to_nk<<<dim3(C2 / 32, C4 / 32), tb>>>(reinterpret_cast<const __half*>(sp->merge.reduction_w), wr_t, C4, C2);
+    SF_CUDA(cudaGetLastError());
+    const void *mg, *mb;
+    if ((rc = copy_vec(sp->merge.norm_g, C4, &mg)) || (rc = copy_vec(sp->merge.norm_b, C4, &mb))) return rc;
+    if ((mg == nullptr) != (mb == nullptr)) return fail(SOUFFLE_BAD_ARGUMENT, "gamma and beta must be given together");
+    int m_merged, m_wr;
+    if ((rc = add_map(p, merged, Tm, C4, t_red.bm, &m_merged)) || (rc = add_map(p, wr_t, C2, C4, t_red.bn, &m_wr))) return rc;
+    Stage s = blank_stage(STAGE_LN);                         // gather + LayerNorm over 4C
+    s.M = Tm; s.N = C4; s.ldo = C4; s.n_partial = 0; s.resid = xlast; s.out = merged; s.gamma = mg; s.beta = mb; s.eps = d.eps;
+    s.seq = R; s.batch = d.batch;
+    p->stages.push_back(s);
+    s = blank_stage(STAGE_GEMM);                             // reduction -> fp32 planes
+    s.tm_a = m_merged; s.tm_b = m_wr; s.M = Tm; s.N = C2; s.K = C4; s.bm = t_red.bm; s.bn = t_red.bn; s.splitk = t_red.split;
+    s.epi = EPI_PARTIAL; s.partial = planes2; s.ldo = C2;
+    p->stages.push_back(s);
+    s = blank_stage(STAGE_LN);                               // sum of the planes -> y
+    s.M = Tm; s.N = C2; s.ldo = C2; s.partial = planes2; s.n_partial = t_red.split; s.eps = -1.0f; s.out_sel = PTR_CALL_Y;
     p->stages.push_back(s);
   }
   return finish_plan(p, sms);
 }
 
 int souffle_swin_block_plan_create(const SouffleSwinDesc* desc, const SouffleSwinWeights* weights, SouffleSwinPlan** plan_out) {
+  return souffle_swin_stage_plan_create(desc, weights, nullptr, plan_out);
+}
+
+int souffle_swin_stage_plan_create(const SouffleSwinDesc* desc, const SouffleSwinWeights* weights, const SouffleSwinMerge* merge,
+                                   SouffleSwinPlan** plan_out) {
   if (!desc || !weights || !plan_out) return fail(SOUFFLE_BAD_ARGUMENT, "null argument");
   *plan_out = nullptr;
   const SouffleSwinDesc& d = *desc;
@@ -1234,8 +1273,17 @@ int souffle_swin_block_plan_create(const SouffleSwinDesc* desc, const SouffleSwi
   for (int i = 0; i < (d.n_blocks > 0 ? d.n_blocks : 1); ++i)
     if (!aligned16(weights[i].qkv_w) || !aligned16(weights[i].proj_w) || !aligned16(weights[i].fc1_w) || !aligned16(weights[i].fc2_w))
       return fail(SOUFFLE_BAD_POINTER, "block %d: weight matrices must be non-null and 16-byte aligned", i);
+  if (merge) {
+    if (d.res % 2) return fail(SOUFFLE_BAD_SHAPE, "patch merging needs an even token grid (res %d)", d.res);
+    if (d.dim > 512) return fail(SOUFFLE_BAD_SHAPE, "patch merging normalises 4 * dim columns: dim must be 128, 256 or 512 (got %d)", d.dim);
+    if (!aligned16(merge->reduction_w)) return fail(SOUFFLE_BAD_POINTER, "reduction_w must be non-null and 16-byte aligned");
+  }
   SouffleSwinPlan* sp = new SouffleSwinPlan();
   sp->desc = d;
+  if (merge) {
+    sp->merge = *merge;
+    sp->has_merge = true;
+  }
   int rc = build_swin_plan(sp, weights);
   if (rc) {
     const std::string keep = g_last_error;

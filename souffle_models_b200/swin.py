@@ -129,15 +129,19 @@ def layernorm(partial: torch.Tensor, resid=None, bias=None, gamma=None, beta=Non
 class SwinBlock:
     """Plan for one Swin block, or for a chain of blocks run as one launch (see SouffleSwinDesc in the header).
     `params` is a weights dict with the keys of oracle.souffle_oracle.make_swin_params (fp16 CUDA tensors, matrices
-    [K][N]) or a list of such dicts, one per block; even-numbered blocks use `shift`, odd-numbered ones `shift_alt`."""
+    [K][N]) or a list of such dicts, one per block; even-numbered blocks use `shift`, odd-numbered ones `shift_alt`.
+    `merge` (dict with norm_g, norm_b [4*dim] and reduction_w [4*dim, 2*dim]) appends the patch merging that ends a
+    stage of the network (python/models/swin_transformer/swin_patch_merge.py:1-17) to the same launch; the output is
+    then [batch*(res/2)^2, 2*dim]."""
 
     KEYS = ("ln1_g", "ln1_b", "qkv_w", "qkv_b", "rel_bias", "proj_w", "proj_b", "ln2_g", "ln2_b", "fc1_w", "fc1_b",
             "fc2_w", "fc2_b")
 
     def __init__(self, batch: int, res: int, dim: int, heads: int, window: int, shift: int, params, mlp_ratio: int = 4,
-                 eps: float = 1e-5, shift_alt: int = 0):
+                 eps: float = 1e-5, shift_alt: int = 0, merge=None):
         lib = _lib.load()
         self.batch, self.res, self.dim = batch, res, dim
+        self.out_shape = (batch * res * res, dim) if merge is None else (batch * (res // 2) ** 2, 2 * dim)
         blocks = list(params) if isinstance(params, (list, tuple)) else [params]
         d = _lib.SwinDesc(batch=batch, res=res, dim=dim, heads=heads, window=window, shift=shift, mlp_ratio=mlp_ratio, eps=eps,
                           n_blocks=len(blocks), shift_alt=shift_alt)
@@ -149,8 +153,18 @@ class SwinBlock:
                 if t is not None:
                     _check_f16_cuda(t, k)
                 setattr(w, k, t.data_ptr() if t is not None else None)
+        mg = None
+        if merge is not None:
+            mg = _lib.SwinMerge()
+            for k in ("norm_g", "norm_b", "reduction_w"):
+                t = merge.get(k)
+                if t is not None:
+                    _check_f16_cuda(t, k)
+                setattr(mg, k, t.data_ptr() if t is not None else None)
+            self._keep = (blocks, merge)
         self._h = C.c_void_p()
-        _lib.check(lib.souffle_swin_block_plan_create(C.byref(d), ws, C.byref(self._h)))
+        _lib.check(lib.souffle_swin_stage_plan_create(C.byref(d), ws, C.byref(mg) if mg is not None else None,
+                                                      C.byref(self._h)))
         self._lib = lib
 
     def close(self) -> None:
@@ -169,9 +183,24 @@ class SwinBlock:
         _check_f16_cuda(x, "x")
         if x.numel() != self.batch * self.res * self.res * self.dim:
             raise ValueError("x has the wrong number of elements for this plan")
-        y = torch.empty_like(x)
+        y = torch.empty(self.out_shape, dtype=torch.float16, device=x.device)
         _lib.check(self._lib.souffle_swin_block_forward(self._h, x.data_ptr(), y.data_ptr(), _stream_ptr()))
         return y
 
     def status(self) -> None:
         _lib.check(self._lib.souffle_swin_block_plan_status(self._h))
+
+
+def swin_stage(x: torch.Tensor, blocks, merge=None, batch: int = 1, res: int = 14, heads: int = 16, window: int = 7,
+               shift: int = 3, mlp_ratio: int = 4, eps: float = 1e-5) -> torch.Tensor:
+    """A stage of the network as one launch: `blocks` (list of weight dicts) with shifts 0, `shift`, 0, ... and, with
+    `merge`, the patch merging after them.  The reference runs this part of the model as separate TVM kernels, 226 for
+    the whole model (python/models/tee:1)."""
+    plan = SwinBlock(batch, res, x.shape[-1], heads, window, 0, list(blocks), mlp_ratio=mlp_ratio, eps=eps, shift_alt=shift,
+                     merge=merge)
+    try:
+        y = plan.forward(x.reshape(-1, x.shape[-1]))
+        plan.status()
+    finally:
+        plan.close()
+    return y

@@ -77,12 +77,17 @@ def test_python_mirror_validates_before_calling():
 
 def test_persistent_kernels_do_not_spill():
     usage = build.resource_usage()
-    mega = [v for k, v in usage.items() if "souffle_megakernel" in k]
-    lstm = [v for k, v in usage.items() if "souffle_lstm_wavefront" in k]
-    assert mega and lstm
-    for regs, st, ld in mega + lstm:
-        assert st == 0 and ld == 0, f"kernel spills ({st} B stores, {ld} B loads, {regs} registers)"
-    assert mega[0][0] <= 168          # 320 threads per CTA leave 168 registers per thread
+    mega = {k: v for k, v in usage.items() if "souffle_megakernel" in k}
+    lstm = {k: v for k, v in usage.items() if "souffle_lstm_wavefront" in k}
+    stages = {k: v for k, v in usage.items() if any(n in k for n in ("gemm_stage_ool", "ln_stage_ool", "attn_swin_stage",
+                                                                     "ln_row_wide", "ln_gather_rows"))}
+    assert len(mega) == 3 and lstm and len(stages) == 5
+    for k, (regs, st, ld) in {**mega, **lstm, **stages}.items():
+        # The build whose stages are out of line (ILi2E) may keep a few words of its per-stage dispatcher on the
+        # stack across the calls: that code runs once per stage, the stage functions themselves must stay clean.
+        limit = 32 if "souffle_megakernelILi2E" in k else 0
+        assert st <= limit and ld <= limit, f"{k} spills ({st} B stores, {ld} B loads, {regs} registers)"
+    assert all(v[0] <= 168 for v in mega.values())    # 320 threads per CTA leave 168 registers per thread
 
 
 def test_packed_parameter_block_layout():

@@ -132,3 +132,20 @@ def test_se_module_hand_computed():
     r = 0.5 / (1.0 + math.exp(-0.5))
     g0, g1 = 1.0 / (1.0 + math.exp(-2.0 * r)), 0.5
     assert torch.allclose(out[0, 0], x[0, 0] + g0, atol=1e-6) and torch.allclose(out[0, 1], x[0, 1] + g1, atol=1e-6)
+
+
+def test_patch_merging_gathers_the_four_neighbours():
+    """Channel block q of merged token (h, w) is input token (2h + q % 2, 2w + q // 2)
+    (python/models/swin_transformer/swin_patch_merge.py:39-44); with an identity-like reduction and no affine the
+    result is the LayerNorm of that concatenation."""
+    cfg = so.SwinConfig(res=4, dim=2)
+    x = torch.arange(4 * 4 * 2, dtype=torch.float32).reshape(16, 2)
+    m = dict(norm_g=torch.ones(8), norm_b=torch.zeros(8), reduction_w=torch.eye(8)[:, :4])
+    got = so.swin_patch_merge(cfg, x, m)
+    assert got.shape == (4, 4)
+    X = x.reshape(4, 4, 2)
+    for h in range(2):
+        for w in range(2):
+            row = torch.cat([X[2 * h + q % 2, 2 * w + q // 2] for q in range(4)])
+            ln = (row - row.mean()) / torch.sqrt(row.var(unbiased=False) + cfg.eps)
+            assert torch.allclose(got[h * 2 + w], ln[:4], atol=1e-5)

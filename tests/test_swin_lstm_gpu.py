@@ -131,3 +131,44 @@ def test_swin_block_batch2_window8():
     blk.status()
     want = torch.cat([so.swin_block(cfg, x[:256], p, 4), so.swin_block(cfg, x[256:], p, 4)])
     assert (y.float().cpu() - want).abs().max() < 2e-2
+
+
+@pytest.mark.parametrize("batch,res,dim,heads,window", [(1, 14, 512, 16, 7), (2, 16, 256, 8, 8), (3, 14, 128, 4, 7)])
+def test_swin_stage_with_patch_merging(batch, res, dim, heads, window):
+    """A block followed by the patch merging that ends a stage, in one launch: 4*dim = 2048 (the wide-row LayerNorm),
+    1024 and 512; several images, so the gather crosses image boundaries."""
+    from souffle_models_b200 import swin
+    cfg = so.SwinConfig(res=res, dim=dim, heads=heads, window=window)
+    p = so.make_swin_params(cfg, 500 + dim, zero_bias=False)
+    m = so.make_swin_merge_params(cfg, 600 + dim, zero_bias=False)
+    T = res * res
+    x = _rand((batch * T, dim), 41)
+    shift = window // 2
+    plan = swin.SwinBlock(batch, res, dim, heads, window, shift, {k: v.cuda() for k, v in p.items()},
+                          merge={k: v.cuda() for k, v in m.items()})
+    y = plan.forward(x.cuda())
+    plan.status()
+    assert y.shape == (batch * (res // 2) ** 2, 2 * dim)
+    want = torch.cat([so.swin_patch_merge(cfg, so.swin_block(cfg, x[i * T:(i + 1) * T], p, shift).half().float(), m)
+                      for i in range(batch)])
+    err = (y.float().cpu() - want).abs()
+    assert err.max() < 2e-2 and err.pow(2).mean().sqrt() < 3e-3
+    y2 = plan.forward(x.cuda())
+    plan.status()
+    assert torch.equal(y, y2)
+
+
+def test_swin_stage_entry_and_merge_shape_errors():
+    from souffle_models_b200 import swin
+    cfg = so.SwinConfig()
+    ps = [so.make_swin_params(cfg, 700 + i) for i in range(2)]
+    m = so.make_swin_merge_params(cfg, 710)
+    x = _rand((196, 512), 43)
+    y = swin.swin_stage(x.cuda(), [{k: v.cuda() for k, v in p.items()} for p in ps], {k: v.cuda() for k, v in m.items()})
+    mid = so.swin_block(cfg, so.swin_block(cfg, x, ps[0], 0).half().float(), ps[1], 3)
+    want = so.swin_patch_merge(cfg, mid.half().float(), m)
+    assert y.shape == (49, 1024) and (y.float().cpu() - want).abs().max() < 3e-2
+    big = so.SwinConfig(dim=768, heads=24)
+    with pytest.raises(RuntimeError, match="patch merging"):
+        swin.SwinBlock(1, 14, 768, 24, 7, 0, {k: v.cuda() for k, v in so.make_swin_params(big, 1).items()},
+                       merge={k: v.cuda() for k, v in so.make_swin_merge_params(big, 2).items()})
