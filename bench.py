@@ -170,6 +170,33 @@ def latency_us(bert, so, n_layers: int, iters: int = 200) -> float:
     return ms * 1000.0
 
 
+def latency_cold_us(bert, so, iters: int = 30) -> float:
+    """Batch-1, seq-128, one layer with its weights cold: a 256 MB buffer is rewritten before every call (twice the
+    L2), one call between each pair of events, median over `iters` in microseconds.  This is the case the HBM floor
+    of a single layer applies to."""
+    cfg = so.BertConfig(1, SEQ, HEADS, HEAD_DIM, FFN, "std")
+    layers = [{k: v.cuda() for k, v in w.items()} for w in so.make_bert_weights(cfg, SEED + 1, 1)]
+    enc = bert.BertEncoder(1, SEQ, HEADS, HEAD_DIM, FFN, layers)
+    x = so.make_bert_input(cfg, SEED + 1)[0].cuda()
+    y = torch.empty_like(x)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(5):
+        enc.forward(x, None, y)
+    pairs = []
+    for i in range(iters):
+        flush.fill_(i & 0xFF)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        enc.forward(x, None, y)
+        e1.record()
+        pairs.append((e0, e1))
+    torch.cuda.synchronize()
+    enc.status()
+    enc.close()
+    ts = sorted(a.elapsed_time(b) for a, b in pairs)
+    return ts[len(ts) // 2] * 1000.0
+
+
 def run_ours(args, rank: int, world: int, local_rank: int):
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
@@ -261,7 +288,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     if world == 1:
         lat = {"bert_layer_b1_s128": latency_us(bert, so, 1), "bert_12layer_b1_s128": latency_us(bert, so, 12, 50)}
         hbm_floor_us = (layer_weight_bytes() + 2 * SEQ * HIDDEN * 2) / (peaks["hbm"] * 1e9) * 1e6
+        lat["bert_layer_b1_s128_cold_l2"] = latency_cold_us(bert, so)
         lat["hbm_floor_layer_us"] = hbm_floor_us
+        lat["hbm_frac_layer_cold_l2"] = hbm_floor_us / lat["bert_layer_b1_s128_cold_l2"]
         lat["hbm_frac_12layer"] = 12 * hbm_floor_us / lat["bert_12layer_b1_s128"]
         n_seq = 4
         v, dt, cores = cpu_sample(n_seq, 2, 1)

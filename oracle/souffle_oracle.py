@@ -207,6 +207,8 @@ def lstm_forward(x: torch.Tensor, w_in: torch.Tensor, w_st: torch.Tensor,
     `ref_input_delay=True` reproduces the reference kernel's feeding order, where layer 0 at
     wavefront step s consumes x[s-1] (zeros at s=0) and x[T-1] is never consumed
     (cpp/lstm/lstm_reuse_shared_memory.cu:324-326).  Returns the top layer's h per step [1,T,H].
+    Pinned in that form against the output of the reference kernel on a GPU
+    (tests/golden/ref_cuda_lstm_swin.npz: agreement to 2e-7).
     """
     T, Hd = x.shape[1], x.shape[2]
     L = w_in.shape[0] // 4
@@ -241,7 +243,8 @@ def gemm_kn(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 
 def swin_mlp(src: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, emulate_fp16=False):
     """fc1 -> fc2 with no bias, activation, norm or residual, exactly as
-    cpp/swin_transformer/kernels/swin_fused_ffn_m256n2048k512_m256n512k2048.cu:9-769."""
+    cpp/swin_transformer/kernels/swin_fused_ffn_m256n2048k512_m256n512k2048.cu:9-769.  Pinned against that
+    kernel's output on a GPU (tests/golden/ref_cuda_lstm_swin.npz; the kernel accumulates in fp16: within 1e-2)."""
     h1 = _r16(gemm_kn(src, w1), emulate_fp16)
     return h1, gemm_kn(h1, w2)
 

@@ -41,6 +41,24 @@ def test_ref_compat_matches_reference_cuda_kernels(golden_dir):
         assert abs(sa - want.double().abs().sum().item()) / max(1.0, sa) < 2e-3, k
 
 
+def test_lstm_and_swin_mlp_match_reference_cuda_kernels(golden_dir):
+    """Oracle vs outputs of the reference's own kernels run on a B200 (tests/golden/make_ref_cuda_golden.py):
+    lstm_reuse_shared_memory_v10_vec<1,10,256,100> on make_lstm_params() -- fp32 throughout, so the restatement with
+    the kernel's one-step input delay agrees to rounding, and the un-delayed form does not -- and the fused Swin MLP
+    (fp16 accumulation in the reference, hence its own 1e-2 tolerance)."""
+    g = np.load(f"{golden_dir}/ref_cuda_lstm_swin.npz")
+    x, w_in, w_st = so.make_lstm_params()
+    y = _t(g["lstm_y"])
+    assert (so.lstm_forward(x, w_in, w_st, ref_input_delay=True)[0] - y).abs().max() < 2e-6
+    assert (so.lstm_forward(x, w_in, w_st)[0] - y).abs().max() > 5e-5
+    gen = torch.Generator().manual_seed(1238)
+    src = torch.randn(256, 512, generator=gen).half()
+    w1, w2 = (torch.randn(512, 2048, generator=gen) * 0.02).half(), (torch.randn(2048, 512, generator=gen) * 0.02).half()
+    h1, o1 = so.swin_mlp(src, w1, w2, emulate_fp16=True)
+    assert (_t(g["swin_hidden_head"]).float() - h1[:32]).abs().max() < 1e-2
+    assert (_t(g["swin_out"]).float() - o1).abs().max() < 1.5e-2
+
+
 def test_gelu_and_layernorm_basics():
     x = torch.linspace(-6, 6, 101)
     assert (so.gelu_tanh(x) - torch.nn.functional.gelu(x, approximate="tanh")).abs().max() < 1e-6

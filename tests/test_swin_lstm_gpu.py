@@ -172,3 +172,24 @@ def test_swin_stage_entry_and_merge_shape_errors():
     with pytest.raises(RuntimeError, match="patch merging"):
         swin.SwinBlock(1, 14, 768, 24, 7, 0, {k: v.cuda() for k, v in so.make_swin_params(big, 1).items()},
                        merge={k: v.cuda() for k, v in so.make_swin_merge_params(big, 2).items()})
+
+
+def test_lstm_and_swin_mlp_match_reference_cuda_outputs(golden_dir):
+    """This library against what the reference's own kernels produced on a B200 (tests/golden/ref_cuda_lstm_swin.npz):
+    the LSTM in the reference's feeding order, and the fused MLP on its seeded inputs."""
+    import numpy as np
+    from souffle_models_b200 import lstm, swin
+    g = np.load(f"{golden_dir}/ref_cuda_lstm_swin.npz")
+    x, w_in, w_st = so.make_lstm_params()
+    plan = lstm.LstmStack(w_in.cuda(), w_st.cuda(), 100, ref_input_delay=True)
+    y = plan.forward(x.float().cuda())
+    plan.status()
+    want = torch.from_numpy(g["lstm_y"])
+    err = (y.cpu()[0] - want).abs()
+    assert err.max() < 5e-3 and (err <= 2e-5 + 1e-3 * want.abs()).all()
+    gen = torch.Generator().manual_seed(1238)
+    src = torch.randn(256, 512, generator=gen).half()
+    w1, w2 = (torch.randn(512, 2048, generator=gen) * 0.02).half(), (torch.randn(2048, 512, generator=gen) * 0.02).half()
+    hidden, out = swin.swin_fused_feed_mlp(src.cuda(), w1.cuda(), w2.cuda())
+    assert (hidden[:32].float().cpu() - torch.from_numpy(g["swin_hidden_head"]).float()).abs().max() < 1e-2
+    assert (out.float().cpu() - torch.from_numpy(g["swin_out"]).float()).abs().max() < 1.5e-2
