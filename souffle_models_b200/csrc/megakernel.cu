@@ -604,6 +604,67 @@ __device__ __forceinline__ void gemm_stage(const Stage& st, const CallArgs& ca, 
   }
 }
 
+// Parity output of the attention stages: normalised probabilities of one query row per thread, recomputed from the
+// scores in TMEM.  Out of line: only the parity configurations call them, and inlined their registers would be charged
+// to every attention item.
+// Row form: a thread writes its row's 64 bytes of every 32-key chunk as four 16-byte stores (S is a multiple of
+// 16).  `row` null = this thread's row is outside the matrix (it still takes part in the loads).
+__device__ __noinline__ void attn_store_probs_rows(uint32_t tmem, __half* row, int S, int kvl, float sl2, float mx, float inv) {
+  for (int c = 0; c * 32 < S; ++c) {
+    uint32_t r[32];
+    tmem_ld32(tmem + c * 32, r);
+    tmem_ld_wait(r);
+    if (row) {
+      uint4* dst = reinterpret_cast<uint4*>(row + c * 32);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int key0 = c * 32 + 8 * u;
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int key = key0 + 2 * i;
+          const float pa = key < kvl ? ex2_fast(fmaf(__uint_as_float(r[8 * u + 2 * i]), sl2, -mx)) * inv : 0.0f;
+          const float pb = key + 1 < kvl ? ex2_fast(fmaf(__uint_as_float(r[8 * u + 2 * i + 1]), sl2, -mx)) * inv : 0.0f;
+          w[i] = pack_h2(pa, pb);
+        }
+        if (key0 + 8 <= S) dst[u] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+  }
+}
+
+// Staged form (S <= 128, a warp owns rows row0 .. row0 + 31 of the [S][S] matrix at `mat`): whole 64-byte row pieces
+// go through the warp's staging buffer, so that a store instruction writes eight rows of 64 contiguous bytes.
+__device__ __noinline__ void attn_store_probs_staged(uint32_t ts, uint8_t* sbuf, __half* mat, int row0, int S, int kv_len,
+                                                     float sl2, float mask_l2, float mx, float inv, int lane) {
+  for (int c = 0; c * 32 < S; ++c) {
+    uint32_t r[32];
+    tmem_ld32(ts + c * 32, r);
+    tmem_ld_wait(r);
+    uint32_t w[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int key = c * 32 + 2 * i;
+      const float ta = __uint_as_float(r[2 * i]) * sl2 + (key >= kv_len ? mask_l2 : 0.0f);
+      const float tb = __uint_as_float(r[2 * i + 1]) * sl2 + (key + 1 >= kv_len ? mask_l2 : 0.0f);
+      w[i] = pack_h2(ex2_fast(ta - mx) * inv, ex2_fast(tb - mx) * inv);
+    }
+    if (c * 32 + 32 <= S) {
+      uint8_t* rowptr[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int rr = row0 + 8 * i + (lane >> 2);
+        rowptr[i] = rr < S ? reinterpret_cast<uint8_t*>(mat + (size_t)rr * S + c * 32) : nullptr;
+      }
+      staged_store_64B(sbuf, w, rowptr, lane);
+    } else if (row0 + lane < S) {                     // the last 16 keys of a row (S is a multiple of 16)
+      uint4* dst = reinterpret_cast<uint4*>(mat + (size_t)(row0 + lane) * S + c * 32);
+      dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+      dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------
 // attention stage: one work item = (sequence, head, 128-query tile); S <= 384, head_dim 64
 // ------------------------------------------------------------------------------------
@@ -783,23 +844,8 @@ __device__ __forceinline__ void attn_stage(const Stage& st, const CallArgs& ca, 
       named_barrier_sync(3, 256);
       const float inv = 1.0f / (red[256 + r_in] + red[384 + r_in]);
       const int qrow = qt * 128 + r_in;
-      if (probs && grp == 0) {
-        // parity output: normalised probabilities [B*heads][S][S]
-        for (int c = 0; c < n_kb * 4 && c * 32 < S; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tmem + c * 32, r);
-          tmem_ld_wait(r);
-          if (qrow < S) {
-            __half* dst = probs + ((size_t)(b * H + h) * S + qrow) * S + c * 32;
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int key = c * 32 + i;
-              const float pv = key < kvl ? ex2_fast(fmaf(__uint_as_float(r[i]), sl2, -mx)) * inv : 0.0f;
-              if (key < S) dst[i] = __float2half_rn(pv);
-            }
-          }
-        }
-      }
+      if (probs && grp == 0)      // parity output: normalised probabilities [B*heads][S][S], before group 0 releases the scores
+        attn_store_probs_rows(tmem, qrow < S ? probs + ((size_t)(b * H + h) * S + qrow) * S : nullptr, S, kvl, sl2, mx, inv);
       tc_fence_before_sync();
       if (grp == 0) mbar_arrive(p_full);                      // 128 arrivals: group 1's rows are behind the barrier above
       ok = mbar_wait_warp(o_full, rs.attn_bit, ctl, 521, lane);
@@ -1012,20 +1058,7 @@ __device__ __forceinline__ void attn_stage_pp(const Stage& st, const CallArgs& c
       }
       const float inv = 1.0f / ((s0 + s1) + (s2 + s3));
       if (probs) {                                            // parity output: normalised probabilities
-        for (int c = 0; c < n_chunks; ++c) {
-          uint32_t r[32];
-          tmem_ld32(ts + c * 32, r);
-          tmem_ld_wait(r);
-          if (r_in < S) {
-            __half* dst = probs + ((size_t)(b * H + h) * S + r_in) * S + c * 32;
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int key = c * 32 + i;
-              const float t = __uint_as_float(r[i]) * sl2 + (key >= kv_len ? mask_l2 : 0.0f);
-              if (key < S) dst[i] = __float2half_rn(ex2_fast(t - mx) * inv);
-            }
-          }
-        }
+        attn_store_probs_staged(ts, sbuf, probs + (size_t)(b * H + h) * S * S, q * 32, S, kv_len, sl2, mask_l2, mx, inv, lane);
       }
       fence_proxy_async_smem();
       tc_fence_before_sync();

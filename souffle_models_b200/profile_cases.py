@@ -10,7 +10,8 @@ python/models/tee:1-2).  The counterpart here:
 
 Every case builds its plan on seeded random parameters, makes 3 warm-up calls and 5 timed ones (CUDA events) and
 prints the mean time per call.  Cases: bert_layer (1 x 128, one layer), bert_base (1 x 128, 12 layers), bert_layer_s384
-(the reference's native shape, its numerical variant), lstm (10 x 256, 100 steps), swin_mlp (256 x 512 x 2048),
+(the reference's native shape and numerical variant through the blocking drop-in entry, which also returns the five
+intermediate tensors), bert_layer_s384_plan (the same launch called back to back), lstm (10 x 256, 100 steps), swin_mlp (256 x 512 x 2048),
 swin_pair (14 x 14 x 512, shifts 0 and 3), swin_stage (18 blocks + patch merging), se_module (the reference's ten
 shapes, one call each per round).
 """
@@ -67,6 +68,12 @@ def make_case(name: str):
         w = _bert_layers(1, 768, 3072, g, False)[0]
         x = _h((1, 384, 768), g)
         return (lambda: bert.souffle_bert_layer(x, w["qkv_w"], w["proj_w"], w["fc1_w"], w["fc2_w"], 4)), (lambda: None)
+    if name == "bert_layer_s384_plan":         # the launch behind the drop-in entry alone: no blocking, no copies out
+        w = _bert_layers(1, 768, 3072, g, False)[0]
+        enc = bert.BertEncoder(1, 384, 12, 64, 3072, [w], variant=bert.REF_COMPAT, keep_probs=True)
+        x = _h((1, 384, 768), g)
+        y = torch.empty_like(x)
+        return (lambda: enc.forward(x, None, y)), enc.status
     if name == "lstm":
         w_in = ((torch.rand(40, 256, 256, generator=g) - 0.5) / 8).cuda()
         w_st = ((torch.rand(40, 256, 256, generator=g) - 0.5) / 8).cuda()
