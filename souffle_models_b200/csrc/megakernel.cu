@@ -607,28 +607,26 @@ __device__ __forceinline__ void gemm_stage(const Stage& st, const CallArgs& ca, 
 // Parity output of the attention stages: normalised probabilities of one query row per thread, recomputed from the
 // scores in TMEM.  Out of line: only the parity configurations call them, and inlined their registers would be charged
 // to every attention item.
-// Row form: a thread writes its row's 64 bytes of every 32-key chunk as four 16-byte stores (S is a multiple of
-// 16).  `row` null = this thread's row is outside the matrix (it still takes part in the loads).
-__device__ __noinline__ void attn_store_probs_rows(uint32_t tmem, __half* row, int S, int kvl, float sl2, float mx, float inv) {
-  for (int c = 0; c * 32 < S; ++c) {
-    uint32_t r[32];
-    tmem_ld32(tmem + c * 32, r);
-    tmem_ld_wait(r);
-    if (row) {
-      uint4* dst = reinterpret_cast<uint4*>(row + c * 32);
+// Tile form (the cooperative attention stage): the unnormalised probabilities already sit in shared memory as the
+// fp16 A-operand tiles of P.V ([128 rows][64 keys] per tile, 128-byte rows with the 16-byte pieces XOR-swizzled by
+// row & 7); the 256 softmax threads copy them out scaled by 1 / rowsum: eight threads per row, 32 rows per pass, so a
+// store instruction writes four rows of 128 contiguous bytes.  `sums` = the two groups' partial row sums [2][128].
+__device__ __noinline__ void attn_copy_probs_tiles(const uint8_t* ptiles, const float* sums, __half* mat, int S, int rows, int t8) {
+  const int sub = t8 & 7, rsub = t8 >> 3;
+  for (int r = rsub; r < rows; r += 32) {
+    const float inv = 1.0f / (sums[r] + sums[128 + r]);
+    const uint8_t* src = ptiles + r * 128 + ((sub ^ (r & 7)) << 4);
+    __half* dst = mat + (size_t)r * S + sub * 8;
+    for (int tile = 0; tile * 64 + sub * 8 + 8 <= S; ++tile) {
+      const uint4 v = *reinterpret_cast<const uint4*>(src + tile * kATileBytes);
+      const uint32_t in[4] = {v.x, v.y, v.z, v.w};
+      uint32_t w[4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int key0 = c * 32 + 8 * u;
-        uint32_t w[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int key = key0 + 2 * i;
-          const float pa = key < kvl ? ex2_fast(fmaf(__uint_as_float(r[8 * u + 2 * i]), sl2, -mx)) * inv : 0.0f;
-          const float pb = key + 1 < kvl ? ex2_fast(fmaf(__uint_as_float(r[8 * u + 2 * i + 1]), sl2, -mx)) * inv : 0.0f;
-          w[i] = pack_h2(pa, pb);
-        }
-        if (key0 + 8 <= S) dst[u] = make_uint4(w[0], w[1], w[2], w[3]);
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&in[i]));
+        w[i] = pack_h2(f.x * inv, f.y * inv);
       }
+      *reinterpret_cast<uint4*>(dst + tile * 64) = make_uint4(w[0], w[1], w[2], w[3]);
     }
   }
 }
@@ -844,10 +842,15 @@ __device__ __forceinline__ void attn_stage(const Stage& st, const CallArgs& ca, 
       named_barrier_sync(3, 256);
       const float inv = 1.0f / (red[256 + r_in] + red[384 + r_in]);
       const int qrow = qt * 128 + r_in;
-      if (probs && grp == 0)      // parity output: normalised probabilities [B*heads][S][S], before group 0 releases the scores
-        attn_store_probs_rows(tmem, qrow < S ? probs + ((size_t)(b * H + h) * S + qrow) * S : nullptr, S, kvl, sl2, mx, inv);
       tc_fence_before_sync();
       if (grp == 0) mbar_arrive(p_full);                      // 128 arrivals: group 1's rows are behind the barrier above
+      if (probs) {
+        // parity output: normalised probabilities [B*heads][S][S], copied from the P tiles while P.V runs; nobody may
+        // start the next item's P rows or row sums before every thread has copied
+        attn_copy_probs_tiles(ring_ptr + p_off, red + 256, probs + ((size_t)(b * H + h) * S + qt * 128) * S, S,
+                              S - qt * 128 < 128 ? S - qt * 128 : 128, (int)threadIdx.x - 64);
+        named_barrier_sync(3, 256);
+      }
       ok = mbar_wait_warp(o_full, rs.attn_bit, ctl, 521, lane);
       if (!ok) break;
       tc_fence_after_sync();
