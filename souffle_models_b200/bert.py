@@ -167,10 +167,11 @@ def souffle_bert_layer(src: torch.Tensor, qkv_weight: torch.Tensor, attn_fc_weig
         enc = BertEncoder(B, S, heads, 64, F, [w], variant=REF_COMPAT, keep_probs=True)
         _layer_cache[key] = enc
     out = enc.forward(src).reshape(B * S, H)
-    torch.cuda.current_stream().synchronize()      # the reference call is blocking (bert_binding.cu:532)
-    enc.status()
-    return [enc.buffer("qkv").reshape(3 * B, heads, S, 64), enc.buffer("probs"), enc.buffer("ctx"),
+    # the copies of the intermediates are queued behind the launch while it runs; one wait at the end
+    outs = [enc.buffer("qkv").reshape(3 * B, heads, S, 64), enc.buffer("probs"), enc.buffer("ctx"),
             enc.buffer("ln1"), enc.buffer("fc1"), out]
+    enc.status()                                   # blocks, as the reference call does (bert_binding.cu:532)
+    return outs
 
 
 _PACKED_ORDER = ("qkv_w", "proj_w", "fc1_w", "fc2_w", "qkv_b", "proj_b", "ln1_g", "ln1_b", "fc1_b", "fc2_b", "ln2_g", "ln2_b")
