@@ -222,7 +222,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             sharding.gather_outputs(y_d, full)
 
     x_h, y_h, l_h = xs.pin_memory(), torch.empty_like(xs).pin_memory(), ls.pin_memory()
-    full_h = torch.empty(BATCH, SEQ, HIDDEN, dtype=torch.float16).pin_memory() if world > 1 else None
+    # every rank reads back its own slice of the gathered result: the whole result reaches host memory once per step,
+    # spread over the rank processes like the inputs
+    full_h = torch.empty(per, SEQ, HIDDEN, dtype=torch.float16).pin_memory() if world > 1 else None
     # multi-GPU end-to-end step: shard host -> device, encoder, gather over NVLink, gathered result -> host, as a
     # three-stream pipeline over two sets of device buffers (the single-GPU entry point does the same inside the library)
     pipe = None
@@ -252,7 +254,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         pipe["ev_k"][b] = cur.record_event()
         with torch.cuda.stream(pipe["s_out"]):
             pipe["s_out"].wait_event(pipe["ev_k"][b])
-            full_h.copy_(pipe["full"][b], non_blocking=True)
+            full_h.copy_(pipe["full"][b][rank * per:(rank + 1) * per], non_blocking=True)
             pipe["ev_out"][b] = pipe["s_out"].record_event()
 
     def drain_e2e():
@@ -307,10 +309,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                    "tiles": "timed at plan creation (desc.autotune): " + ", ".join(
                        "%dx%d/%d" % (t["bm"], t["bn"], t["splitk"]) for t in (enc.stage_info(i) for i in (0, 2, 4, 5))),
                    "e2e": ("pinned host in/out per step; steps pipelined over copy-in, compute and copy-out streams"
-                           if world == 1 else "pinned host shard in, gathered result out per step; steps pipelined over three streams")},
+                           if world == 1 else "pinned host shard in, all-gather on the device, every rank reads its slice of the gathered result back; steps pipelined over three streams")},
         "e2e": {"value": BATCH / (ms_e2e * 1e-3), "unit": "sequences/s",
-                "h2d_bytes_per_step": int(xs.numel() * 2 + ls.numel() * 4),
-                "d2h_bytes_per_step": int((BATCH if world > 1 else per) * SEQ * HIDDEN * 2)},
+                "h2d_bytes_per_step": int((xs.numel() * 2 + ls.numel() * 4) * world),      # whole job: all ranks' shards
+                "d2h_bytes_per_step": int(BATCH * SEQ * HIDDEN * 2)},
         "gpu_launches": args.steps * info["launches"],
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
                      "frac": achieved / peaks["tflops"], "frac_of_sustained_peak": achieved / peaks["tflops_sustained"],
