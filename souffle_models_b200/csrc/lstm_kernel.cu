@@ -5,14 +5,20 @@
 // reference's (python/models/lstm/tf_lstm.py:59-70; cpp/lstm/lstm_reuse_shared_memory.cu:309-318):
 // gates i, j, f, o;  c' = c*sigmoid(f+1) + sigmoid(i)*tanh(j);  h' = tanh(c')*sigmoid(o).
 //
-// Design: every layer is owned by kLstmParts CTAs; a CTA keeps its 4*U gate rows of both weight
-// matrices (fp16, [x;h] concatenated along K) in shared memory for the whole sequence and its
-// units' cell state in registers.  There is no grid-wide barrier: a cell (layer l, step t)
-// starts as soon as h(l-1,t) and h(l,t-1) are published, which is signalled by per-layer
-// arrival counters (release/acquire).  Hidden states of every (layer, step) have their own slot
-// in global memory, so a producer never overwrites data a slower consumer still needs (the
-// reference re-uses one slot per layer with no ordering between its readers and writers).
-// All waits are bounded; on expiry the CTA records a status word and leaves.
+// Design: every layer is owned by one thread-block cluster of kLstmParts CTAs; a CTA keeps its
+// 4*U gate rows of both weight matrices (fp16, [x;h] concatenated along K) in shared memory for
+// the whole sequence and its units' cell state in registers.  Every path through the (layer, step)
+// grid has steps-1 hops along time and layers-1 hops across layers, so the hop along time is the one
+// that has to be short: a CTA writes its units' new hidden state straight into the shared memory of
+// the eight CTAs of its cluster (distributed shared memory, st.async: the store itself counts as a
+// transfer on the receiver's mbarrier, no fence on either side) -- no trip through L2.  Only the hop to
+// the next layer goes through global memory: one slot per (layer, step) and per-layer arrival counters.
+// Two more warps keep that hop off the cell arithmetic's path: a fetch warp brings the layer's input
+// vectors into shared memory up to four steps ahead, and a publish warp pays for the release fence
+// behind the hidden states the cell warps have stored.
+// There is no grid-wide barrier.  All waits in the step loop are bounded; on expiry the CTA records a
+// status word, leaves the loop and waits for its cluster at the final cluster barrier (shared
+// memory must outlive the peers' remote stores).
 #pragma once
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -22,9 +28,11 @@
 
 namespace souffle {
 
-constexpr int kLstmThreads = 512;
-constexpr int kLstmParts = 8;              // CTAs per layer
+constexpr int kLstmThreads = 512;                  // threads of the cell arithmetic
+constexpr int kLstmBlock = kLstmThreads + 64;      // + the fetch warp and the publish warp
+constexpr int kLstmParts = 8;                      // CTAs per layer = cluster size
 constexpr int kLstmMaxHidden = 256;
+constexpr int kLstmXBufs = 4;                      // input vectors the fetch warp may run ahead
 
 struct LstmParams {
   const __half* w_in;     // [4*L][H][H], row = output unit, col = input
@@ -56,27 +64,68 @@ __device__ __forceinline__ bool wait_count(const unsigned* ctr, unsigned target,
   return true;
 }
 
-// Shared-memory layout: weights [rows = 4*U][2H halves] with a 64-byte pad per row, then the
-// fp32 input vector [2H], the gate pre-activations [4*U] and an abort word.
-__global__ void __launch_bounds__(kLstmThreads, 1) souffle_lstm_wavefront(const LstmParams p) {
+// Bounded wait on an mbarrier whose arrivals come from other CTAs of the cluster.
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, const WaitCtl& c, int where) {
+  uint32_t spins = 0;
+  while (!mbar_try_wait_cluster(bar, parity)) {
+    if (((++spins) & 0xFF) == 0) {
+      if (*c.abort_smem) return false;
+      if (globaltimer_ns() > c.deadline_ns) {
+        record_timeout(c, DEV_TIMEOUT_MBAR, where);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+// Shared memory of a CTA, in this order: weights [rows = 4*U][2H halves, 64-byte pad per row]; input vectors
+// [kLstmXBufs][H] fp32; hidden vectors [2][H] fp32 (written by the whole cluster); gate pre-activations
+// [2][rows] fp32; mbarriers xfull[kLstmXBufs], xempty[kLstmXBufs], hfull[2]; abort, verdict and produced words.
+__host__ __device__ inline size_t lstm_smem_bytes(int H) {
+  const int rows = 4 * (H / kLstmParts);
+  return (size_t)rows * (2 * H * 2 + 64) + (size_t)(kLstmXBufs * H + 2 * H + 2 * rows) * 4 + (2 * kLstmXBufs + 2) * 8 + 16;
+}
+
+__global__ void __launch_bounds__(kLstmBlock, 1) souffle_lstm_wavefront(const LstmParams p) {
   extern __shared__ __align__(16) uint8_t lsm[];
   const int H = p.hidden, L = p.layers, T = p.steps;
   const int U = H / kLstmParts;                 // units owned by this CTA
   const int rows = 4 * U;                       // gate rows, row = unit*4 + gate
   const int row_bytes = 2 * H * 2 + 64;
   __half* w_s = reinterpret_cast<__half*>(lsm);
-  float* v_s = reinterpret_cast<float*>(lsm + (size_t)rows * row_bytes);
-  float* g_s = v_s + 2 * H;
-  int* abort_s = reinterpret_cast<int*>(g_s + rows);
-  const int layer = blockIdx.x / kLstmParts, part = blockIdx.x % kLstmParts;
+  float* x_s = reinterpret_cast<float*>(lsm + (size_t)rows * row_bytes);      // [kLstmXBufs][H]
+  float* h_s = x_s + kLstmXBufs * H;                                          // [2][H]
+  float* g_s = h_s + 2 * H;                                                   // [2][rows]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(g_s + 2 * rows);
+  int* abort_s = reinterpret_cast<int*>(bars + 2 * kLstmXBufs + 2);
+  int* verdict_s = abort_s + 1;
+  const uint32_t produced_a = smem_u32(abort_s + 2);       // steps whose hidden states this CTA has stored to global memory
+  const uint32_t xfull0 = smem_u32(bars), xempty0 = smem_u32(bars + kLstmXBufs), hfull0 = smem_u32(bars + 2 * kLstmXBufs);
+  const int layer = blockIdx.x / kLstmParts;
+  const int part = (int)cluster_cta_rank();     // == blockIdx.x % kLstmParts for clusters along x
   const int tid = threadIdx.x;
 
-  if (tid == 0) *abort_s = 0;
+  if (tid == 0) {
+    *abort_s = 0;
+    *verdict_s = 1;
+    abort_s[2] = 0;
+    for (int i = 0; i < kLstmXBufs; ++i) {
+      mbar_init(xfull0 + 8 * i, 32);            // the 32 lanes of the fetch warp
+      mbar_init(xempty0 + 8 * i, 1);
+    }
+    for (int i = 0; i < 2; ++i) {               // h(0) and h(1): one local arrival that announces H * 4 bytes
+      mbar_init(hfull0 + 8 * i, 1);
+      mbar_expect_tx(hfull0 + 8 * i, (uint32_t)H * 4u);
+    }
+    fence_mbar_init();
+  }
   if (blockIdx.x == 0 && tid < L) p.done_next[tid] = 0u;
+  for (int i = tid; i < 2 * H; i += kLstmBlock) h_s[i] = 0.0f;               // h before the first step
   // ---- weights -> shared memory (once) ----
   {
     const int chunks_per_row = 2 * H / 8;       // 16-byte chunks: first H/8 from w_in, rest from w_state
-    for (int i = tid; i < rows * chunks_per_row; i += kLstmThreads) {
+    for (int i = tid; i < rows * chunks_per_row; i += kLstmBlock) {
       const int r = i / chunks_per_row, ch = i % chunks_per_row;
       const int unit = part * U + r / 4, gate = r % 4;
       const bool st = ch >= H / 8;
@@ -86,79 +135,133 @@ __global__ void __launch_bounds__(kLstmThreads, 1) souffle_lstm_wavefront(const 
     }
   }
   __syncthreads();
+  cluster_sync_all();                           // every CTA's barriers exist before anyone arrives on them
 
   WaitCtl ctl;
   ctl.abort_smem = abort_s;
   ctl.status_g = p.status;
   ctl.deadline_ns = globaltimer_ns() + p.timeout_ns;
 
-  // thread -> (row, quarter): 4 threads share a row and interleave its 16-byte chunks
-  const int tpr = kLstmThreads / rows;          // threads per row (4 for H=256)
-  const int row = tid / tpr, q = tid % tpr;
-  const int n_chunks = 2 * H / 8 / tpr;         // chunks per thread
-  float c_state = 0.0f;                         // cell state of unit `tid` (tid < U)
-  const float bias_u = (p.bias && tid < U) ? p.bias[layer * H + part * U + tid] : 0.0f;
-
-  for (int t = 0; t < T; ++t) {
-    // ---- wait for h(layer-1, t) and h(layer, t-1) ----
-    if (tid == 0) {
-      bool ok = true;
-      if (layer > 0) ok = wait_count(p.done + layer - 1, (unsigned)kLstmParts * (t + 1), ctl, 700 + layer);
-      if (ok && t > 0) wait_count(p.done + layer, (unsigned)kLstmParts * t, ctl, 800 + layer);
-    }
-    __syncthreads();
-    if (*abort_s) break;
-    // ---- [x ; h_prev] -> shared memory (L2-coherent loads: written by other SMs) ----
-    for (int i = tid; i < 2 * H / 4; i += kLstmThreads) {
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      const int e = i * 4;
-      if (e < H) {
-        if (layer == 0) {
-          const int tx = p.ref_input_delay ? t - 1 : t;
-          if (tx >= 0) v = __ldcg(reinterpret_cast<const float4*>(p.x + (size_t)tx * H + e));
-        } else {
-          v = __ldcg(reinterpret_cast<const float4*>(p.h_all + ((size_t)(layer - 1) * T + t) * H + e));
+  if (tid >= kLstmThreads + 32) {
+    // ---------------- publish warp: makes the stored hidden states visible to the next layer ----------------
+    if (tid == kLstmThreads + 32) {
+      uint32_t published = 0, spins = 0;
+      while (published < (uint32_t)T) {
+        const uint32_t n = ld_acquire_cta_shared_u32(produced_a);
+        if (n > published) {
+          red_add_release_u32(p.done + layer, n - published);
+          published = n;
+        } else if (((++spins) & 0xFF) == 0) {
+          if (*ctl.abort_smem) break;
+          if (globaltimer_ns() > ctl.deadline_ns) {
+            record_timeout(ctl, DEV_TIMEOUT_FLAG, 950);
+            break;
+          }
         }
-      } else if (t > 0) {
-        v = __ldcg(reinterpret_cast<const float4*>(p.h_all + ((size_t)layer * T + t - 1) * H + (e - H)));
       }
-      *reinterpret_cast<float4*>(v_s + e) = v;
     }
-    __syncthreads();
-    // ---- gate pre-activations: fp16 weights x fp32 vector, fp32 accumulate ----
-    if (row < rows) {
-      const uint8_t* wr = reinterpret_cast<const uint8_t*>(w_s) + (size_t)row * row_bytes;
-      float acc = 0.0f;
+    __syncwarp();
+  } else if (tid >= kLstmThreads) {
+    // ---------------- fetch warp: the layer's input vector of every step -> shared memory ----------------
+    const int lane = tid - kLstmThreads;
+    for (int t = 0; t < T; ++t) {
+      const int xb = t % kLstmXBufs, use = t / kLstmXBufs;
+      int ok = 1;
+      if (lane == 0) {
+        if (use > 0) ok = mbar_wait(xempty0 + 8 * xb, (uint32_t)(use - 1) & 1u, ctl, 900) ? 1 : 0;
+        if (ok && layer > 0) ok = wait_count(p.done + layer - 1, (unsigned)kLstmParts * (t + 1), ctl, 700 + layer) ? 1 : 0;
+        if (!ok) *abort_s = 1;
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      const float* src = nullptr;
+      if (layer == 0) {
+        const int tx = p.ref_input_delay ? t - 1 : t;
+        if (tx >= 0) src = p.x + (size_t)tx * H;
+      } else {
+        src = p.h_all + ((size_t)(layer - 1) * T + t) * H;
+      }
+      for (int i = lane; i < H / 4; i += 32) {
+        const float4 v = src ? __ldcg(reinterpret_cast<const float4*>(src) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        *reinterpret_cast<float4*>(x_s + xb * H + i * 4) = v;
+      }
+      mbar_arrive(xfull0 + 8 * xb);             // release: this lane's stores are visible to whoever waits
+    }
+  } else {
+    // ---------------- cell arithmetic ----------------
+    // thread -> (row, quarter): tpr threads share a row and interleave its 16-byte chunks
+    const int tpr = kLstmThreads / rows;        // threads per row (4 for H = 256)
+    const int row = tid / tpr, q = tid % tpr;
+    const int n_chunks = 2 * H / 8 / tpr;       // chunks per thread
+    float c_state = 0.0f;                       // cell state of unit `tid` (tid < U)
+    const float bias_u = (p.bias && tid < U) ? p.bias[layer * H + part * U + tid] : 0.0f;
+    uint32_t peer_h[kLstmParts], peer_bar[kLstmParts];
+#pragma unroll
+    for (int r = 0; r < kLstmParts; ++r) {
+      peer_h[r] = map_shared_rank(smem_u32(h_s), (uint32_t)r);
+      peer_bar[r] = map_shared_rank(hfull0, (uint32_t)r);
+    }
+    for (int t = 0; t < T; ++t) {
+      const int xb = t % kLstmXBufs, hb = t & 1;            // h(t) goes to h_s[hb]; h(t-1) is in h_s[hb ^ 1]
+      // ---- one thread waits for x(t) and h(t-1); its verdict is the CTA's ----
+      if (tid == 0) {
+        bool ok = mbar_wait(xfull0 + 8 * xb, (uint32_t)(t / kLstmXBufs) & 1u, ctl, 910);
+        if (ok && t > 0) {
+          ok = mbar_wait_cluster(hfull0 + 8 * (hb ^ 1), (uint32_t)((t - 1) >> 1) & 1u, ctl, 800 + layer);
+          // that barrier's next phase receives h(t+1); nobody sends it before having this CTA's h(t)
+          if (ok && t + 1 < T) mbar_expect_tx(hfull0 + 8 * (hb ^ 1), (uint32_t)H * 4u);
+        }
+        if (!ok) {
+          *abort_s = 1;
+          *verdict_s = 0;
+        }
+      }
+      named_barrier_sync(1, kLstmThreads);
+      if (*verdict_s == 0) break;
+      // ---- gate pre-activations: fp16 weights x fp32 vector, fp32 accumulate ----
+      {
+        const float* xv = x_s + xb * H;
+        const float* hv = h_s + (hb ^ 1) * H;
+        const uint8_t* wr = reinterpret_cast<const uint8_t*>(w_s) + (size_t)row * row_bytes;
+        float acc = 0.0f;
 #pragma unroll 4
-      for (int j = 0; j < n_chunks; ++j) {
-        const int ch = j * tpr + q;
-        const uint4 u = *reinterpret_cast<const uint4*>(wr + ch * 16);
-        const float4 a = *reinterpret_cast<const float4*>(v_s + ch * 8);
-        const float4 b = *reinterpret_cast<const float4*>(v_s + ch * 8 + 4);
-        const __half2* h2 = reinterpret_cast<const __half2*>(&u);
-        const float2 w0 = __half22float2(h2[0]), w1 = __half22float2(h2[1]), w2 = __half22float2(h2[2]),
-                     w3 = __half22float2(h2[3]);
-        acc = fmaf(w0.x, a.x, acc); acc = fmaf(w0.y, a.y, acc); acc = fmaf(w1.x, a.z, acc); acc = fmaf(w1.y, a.w, acc);
-        acc = fmaf(w2.x, b.x, acc); acc = fmaf(w2.y, b.y, acc); acc = fmaf(w3.x, b.z, acc); acc = fmaf(w3.y, b.w, acc);
+        for (int j = 0; j < n_chunks; ++j) {
+          const int ch = j * tpr + q;
+          const uint4 u = *reinterpret_cast<const uint4*>(wr + ch * 16);
+          const float* v = ch < H / 8 ? xv + ch * 8 : hv + (ch - H / 8) * 8;
+          const float4 a = *reinterpret_cast<const float4*>(v);
+          const float4 b = *reinterpret_cast<const float4*>(v + 4);
+          const __half2* h2 = reinterpret_cast<const __half2*>(&u);
+          const float2 w0 = __half22float2(h2[0]), w1 = __half22float2(h2[1]), w2 = __half22float2(h2[2]),
+                       w3 = __half22float2(h2[3]);
+          acc = fmaf(w0.x, a.x, acc); acc = fmaf(w0.y, a.y, acc); acc = fmaf(w1.x, a.z, acc); acc = fmaf(w1.y, a.w, acc);
+          acc = fmaf(w2.x, b.x, acc); acc = fmaf(w2.y, b.y, acc); acc = fmaf(w3.x, b.z, acc); acc = fmaf(w3.y, b.w, acc);
+        }
+        for (int o = tpr >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (q == 0) g_s[hb * rows + row] = acc;
       }
-      for (int o = tpr >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (q == 0) g_s[row] = acc;
+      named_barrier_sync(1, kLstmThreads);
+      if (tid == 0) mbar_arrive(xempty0 + 8 * xb);          // every thread has read x(t): the slot may be refilled
+      // ---- cell update for the U owned units; h(t) -> the whole cluster and the next layer ----
+      if (tid < U) {
+        const float* g = g_s + hb * rows + tid * 4;
+        const float gi = g[0] + bias_u, gj = g[1] + bias_u, gf = g[2] + bias_u, go = g[3] + bias_u;
+        c_state = c_state * sigmoid_f(gf + 1.0f) + sigmoid_f(gi) * tanhf(gj);
+        const float h = tanhf(c_state) * sigmoid_f(go);
+        const int unit = part * U + tid;
+        const uint32_t off = (uint32_t)(hb * H + unit) * 4u;
+#pragma unroll
+        for (int r = 0; r < kLstmParts; ++r) st_async_b32(peer_h[r] + off, __float_as_uint(h), peer_bar[r] + 8u * (uint32_t)hb);
+        __stcg(p.h_all + ((size_t)layer * T + t) * H + unit, h);
+        if (layer == L - 1) p.y[(size_t)t * H + unit] = h;
+        __syncwarp(U >= 32 ? 0xffffffffu : ((1u << U) - 1u));
+        if (tid == 0) st_release_cta_shared_u32(produced_a, (uint32_t)(t + 1));   // the publish warp takes it from here
+      }
     }
-    __syncthreads();
-    // ---- cell update for the U owned units, publish h ----
-    if (tid < U) {
-      const float gi = g_s[tid * 4 + 0] + bias_u, gj = g_s[tid * 4 + 1] + bias_u, gf = g_s[tid * 4 + 2] + bias_u,
-                  go = g_s[tid * 4 + 3] + bias_u;
-      c_state = c_state * sigmoid_f(gf + 1.0f) + sigmoid_f(gi) * tanhf(gj);
-      const float h = tanhf(c_state) * sigmoid_f(go);
-      const int unit = part * U + tid;
-      __stcg(p.h_all + ((size_t)layer * T + t) * H + unit, h);
-      if (layer == L - 1) p.y[(size_t)t * H + unit] = h;
-      __threadfence();
-    }
-    __syncthreads();
-    if (tid == 0) atom_add_release_u32(p.done + layer, 1u);
   }
+  // Nobody leaves while a peer may still store into its shared memory.
+  __syncthreads();
+  cluster_sync_all();
 }
 
 }  // namespace souffle

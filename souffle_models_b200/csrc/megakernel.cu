@@ -966,7 +966,6 @@ __device__ __forceinline__ void attn_stage_pp(const Stage& st, const CallArgs& c
     uint8_t* sbuf = stage_s + (warp - 2) * kStageWarp;
     uint8_t* pbase = ring_ptr + g * kPipeBytes + 3 * kATileBytes + r_in * 128;
     uint32_t bit = g ? rs.attn_bit1 : rs.attn_bit;
-    const int n_chunks = (S + 31) >> 5;
     const bool prof = p.prof != nullptr;
     long long t_ws = 0, t_sm = 0, t_wo = 0, t_ep = 0, t_p1 = 0;
     for (int k = g; k < my_items; k += 2) {
@@ -1286,7 +1285,19 @@ constexpr int kLnMaxBufs = 4;
 
 // Two rows per call (the second optional): their instruction streams interleave, which hides the
 // shared-memory, shuffle and MUFU latencies a single row's dependent chain exposes.
-template <int NJ>
+// kCg: the rows are read straight from global memory (L2: they were written by other SMs a stage ago).
+template <bool kCg>
+__device__ __forceinline__ float4 ln_ld4(const float* p) {
+  if constexpr (kCg) return __ldcg(reinterpret_cast<const float4*>(p));
+  else return *reinterpret_cast<const float4*>(p);
+}
+template <bool kCg>
+__device__ __forceinline__ uint2 ln_ld2(const __half* p) {
+  if constexpr (kCg) return __ldcg(reinterpret_cast<const uint2*>(p));
+  else return *reinterpret_cast<const uint2*>(p);
+}
+
+template <int NJ, bool kCg = false>
 __device__ __forceinline__ void ln_rows2(const float* pl0, const float* pl1, int n_partial, int plane_stride,
                                          const __half* res0, const __half* res1, const __half* bias,
                                          const __half* gamma, const __half* beta, float eps, __half* out0, __half* out1,
@@ -1296,18 +1307,18 @@ __device__ __forceinline__ void ln_rows2(const float* pl0, const float* pl1, int
 #pragma unroll
   for (int j = 0; j < NJ; ++j) {
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
-    const float4 a = n_partial > 0 ? *reinterpret_cast<const float4*>(pl0 + (lane + 32 * j) * 4) : zero4;
-    const float4 b = (two && n_partial > 0) ? *reinterpret_cast<const float4*>(pl1 + (lane + 32 * j) * 4) : zero4;
+    const float4 a = n_partial > 0 ? ln_ld4<kCg>(pl0 + (lane + 32 * j) * 4) : zero4;
+    const float4 b = (two && n_partial > 0) ? ln_ld4<kCg>(pl1 + (lane + 32 * j) * 4) : zero4;
     z[0][j][0] = a.x; z[0][j][1] = a.y; z[0][j][2] = a.z; z[0][j][3] = a.w;
     z[1][j][0] = b.x; z[1][j][1] = b.y; z[1][j][2] = b.z; z[1][j][3] = b.w;
   }
   for (int pl = 1; pl < n_partial; ++pl) {
 #pragma unroll
     for (int j = 0; j < NJ; ++j) {
-      const float4 a = *reinterpret_cast<const float4*>(pl0 + (size_t)pl * plane_stride + (lane + 32 * j) * 4);
+      const float4 a = ln_ld4<kCg>(pl0 + (size_t)pl * plane_stride + (lane + 32 * j) * 4);
       z[0][j][0] += a.x; z[0][j][1] += a.y; z[0][j][2] += a.z; z[0][j][3] += a.w;
       if (two) {
-        const float4 b = *reinterpret_cast<const float4*>(pl1 + (size_t)pl * plane_stride + (lane + 32 * j) * 4);
+        const float4 b = ln_ld4<kCg>(pl1 + (size_t)pl * plane_stride + (lane + 32 * j) * 4);
         z[1][j][0] += b.x; z[1][j][1] += b.y; z[1][j][2] += b.z; z[1][j][3] += b.w;
       }
     }
@@ -1326,7 +1337,7 @@ __device__ __forceinline__ void ln_rows2(const float* pl0, const float* pl1, int
       const __half* res = r ? res1 : res0;
       float rr[4] = {0.f, 0.f, 0.f, 0.f};
       if (res && (r == 0 || two)) {
-        const uint2 u = *reinterpret_cast<const uint2*>(res + (lane + 32 * j) * 4);
+        const uint2 u = ln_ld2<kCg>(res + (lane + 32 * j) * 4);
         const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
         const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
         rr[0] = f0.x; rr[1] = f0.y; rr[2] = f1.x; rr[3] = f1.y;
@@ -1462,6 +1473,33 @@ __device__ __noinline__ void ln_row_wide(const __half* row, const __half* gamma,
   }
 }
 
+// Direct form of the LayerNorm stage (the host picks it when a CTA has at most one row per normalising warp): every
+// warp reads its row from global memory itself -- one round trip to L2 instead of copy issue, copy latency and a
+// barrier wait.  Out of line: its registers are not charged to the stage interpreter.
+__device__ __noinline__ void ln_stage_direct(const Stage& st, const MegaParams& p, int warp, int lane) {
+  const int N = st.N, M = st.M, P = st.n_partial, rb = st.bm, n_batches = st.items;
+  if (warp == 0 || warp - 1 >= rb) return;
+  const __half* resid = reinterpret_cast<const __half*>(sel_ptr(st.resid_sel, st.resid, p));
+  __half* out = reinterpret_cast<__half*>(const_cast<void*>(sel_ptr(st.out_sel, st.out, p)));
+  const __half* bias = reinterpret_cast<const __half*>(st.bias);
+  const __half* gamma = reinterpret_cast<const __half*>(st.gamma);
+  const __half* beta = reinterpret_cast<const __half*>(st.beta);
+  for (int blk = blockIdx.x; blk < n_batches; blk += gridDim.x) {
+    const int row = blk * rb + warp - 1;
+    if (row >= M) break;
+    const float* pl0 = st.partial + (size_t)row * N;
+    const __half* ra = resid ? resid + (size_t)row * N : nullptr;
+    __half* o0 = out + (size_t)row * N;
+    switch (N >> 7) {
+      case 1: ln_rows2<1, true>(pl0, nullptr, P, M * N, ra, nullptr, bias, gamma, beta, st.eps, o0, nullptr, lane); break;
+      case 2: ln_rows2<2, true>(pl0, nullptr, P, M * N, ra, nullptr, bias, gamma, beta, st.eps, o0, nullptr, lane); break;
+      case 4: ln_rows2<4, true>(pl0, nullptr, P, M * N, ra, nullptr, bias, gamma, beta, st.eps, o0, nullptr, lane); break;
+      case 6: ln_rows2<6, true>(pl0, nullptr, P, M * N, ra, nullptr, bias, gamma, beta, st.eps, o0, nullptr, lane); break;
+      default: ln_rows2<8, true>(pl0, nullptr, P, M * N, ra, nullptr, bias, gamma, beta, st.eps, o0, nullptr, lane); break;
+    }
+  }
+}
+
 // kMerge builds add the patch-merging form (Swin, python/models/swin_transformer/swin_patch_merge.py:1-17): with
 // st.seq = R > 0 the fp16 input is a [batch][R][R][N/4] token grid and row (b, h, w) of the normalised matrix is the
 // concatenation of tokens (2h, 2w), (2h+1, 2w), (2h, 2w+1), (2h+1, 2w+1), fetched as four bulk copies; rows of 2048
@@ -1482,6 +1520,10 @@ __device__ __forceinline__ void ln_stage(const Stage& st, const MegaParams& p, S
   // in flight, at most two rows per warp, and few enough that every CTA gets work -- buffers, batch count.
   const int row_bytes = (P * 4 + (resid ? 2 : 0)) * N;
   const int rb = st.bm, batch_bytes = st.slot_bytes, nbuf = st.nslots, n_batches = st.items;
+  if (nbuf == 0) {          // direct form: see ln_stage_direct
+    ln_stage_direct(st, p, warp, lane);
+    return;
+  }
   const bool stage_vecs = st.kchunks != 0;   // bias | gamma | beta side by side in shared memory
   const int my_batches = n_batches > (int)blockIdx.x ? (n_batches - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
   const uint32_t full0 = smem_u32(&cs.ln_full[0]), empty0 = smem_u32(&cs.ln_empty[0]);

@@ -258,6 +258,14 @@ static int finalize_stage(Stage& s, int max_slots, int grid) {
     s.nslots = 196608 / s.slot_bytes > 4 ? 4 : 196608 / s.slot_bytes;
     s.items = (s.M + rb - 1) / rb;
     s.kchunks = (3 * s.N * 2 <= 8192) ? 1 : 0;
+    // At most one row per normalising warp and CTA: the warps read their rows themselves (no staging ring).
+    if (per_cta <= comp && s.seq == 0 && s.N <= 1024) {
+      s.bm = per_cta;
+      s.items = (s.M + per_cta - 1) / per_cta;
+      s.nslots = 0;
+      s.kchunks = 0;
+      return SOUFFLE_OK;
+    }
     if (s.nslots < 1) return fail(SOUFFLE_BAD_SHAPE, "LayerNorm rows of %d bytes do not fit the staging ring", row_bytes);
     return SOUFFLE_OK;
   }
@@ -1317,6 +1325,52 @@ int souffle_swin_block_plan_status(SouffleSwinPlan* sp) {
 // ======================================================================================
 // LSTM plan
 // ======================================================================================
+// One cluster of kLstmParts CTAs per layer.  The launch is also asked to be cooperative (all clusters resident at
+// once, which the cross-layer waits assume); a driver that refuses the two attributes together gets the cluster
+// launch alone -- lstm_check_resident() has then already established that every cluster fits, and every wait in
+// the kernel is bounded.
+static int g_lstm_coop = 1;
+static void lstm_launch_config(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* at, int layers, size_t smem, cudaStream_t st, bool coop) {
+  memset(cfg, 0, sizeof(*cfg));
+  cfg->gridDim = dim3(layers * kLstmParts);
+  cfg->blockDim = dim3(kLstmBlock);
+  cfg->dynamicSmemBytes = smem;
+  cfg->stream = st;
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = kLstmParts;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  at[1].id = cudaLaunchAttributeCooperative;
+  at[1].val.cooperative = 1;
+  cfg->attrs = at;
+  cfg->numAttrs = coop ? 2 : 1;
+}
+static int lstm_check_resident(int layers, size_t smem) {
+  cudaLaunchConfig_t cfg;
+  cudaLaunchAttribute at[2];
+  lstm_launch_config(&cfg, at, layers, smem, nullptr, false);
+  int clusters = 0;
+  SF_CUDA(cudaOccupancyMaxActiveClusters(&clusters, (const void*)souffle_lstm_wavefront, &cfg));
+  if (clusters < layers)
+    return fail(SOUFFLE_NOT_CORESIDENT, "%d clusters of %d CTAs needed, %d can be resident", layers, kLstmParts, clusters);
+  return SOUFFLE_OK;
+}
+static int lstm_launch(const LstmParams& lp, size_t smem, cudaStream_t st) {
+  void* kargs[] = {const_cast<LstmParams*>(&lp)};
+  cudaLaunchConfig_t cfg;
+  cudaLaunchAttribute at[2];
+  if (g_lstm_coop) {
+    lstm_launch_config(&cfg, at, lp.layers, smem, st, true);
+    const cudaError_t e = cudaLaunchKernelExC(&cfg, (const void*)souffle_lstm_wavefront, kargs);
+    if (e == cudaSuccess) return SOUFFLE_OK;
+    cudaGetLastError();          // a refused launch configuration is not sticky
+    g_lstm_coop = 0;
+  }
+  lstm_launch_config(&cfg, at, lp.layers, smem, st, false);
+  SF_CUDA(cudaLaunchKernelExC(&cfg, (const void*)souffle_lstm_wavefront, kargs));
+  return SOUFFLE_OK;
+}
+
 struct SouffleLstmPlan {
   SouffleLstmDesc desc;
   __half *w_in = nullptr, *w_state = nullptr;
@@ -1344,15 +1398,13 @@ int souffle_lstm_plan_create(const SouffleLstmDesc* desc, const void* w_in, cons
   if (cc != 10) return fail(SOUFFLE_BAD_DEVICE, "device %d is not sm_100", dev);
   SouffleLstmPlan* p = new SouffleLstmPlan();
   p->desc = d;
-  const int H = d.hidden, rows = 4 * (H / kLstmParts);
-  p->smem = (size_t)rows * (2 * H * 2 + 64) + (size_t)(2 * H + rows) * 4 + 16;
+  const int H = d.hidden;
+  p->smem = lstm_smem_bytes(H);
   const size_t wbytes = (size_t)4 * d.layers * H * H * 2;
-  cudaError_t e = cudaFuncSetAttribute(souffle_lstm_wavefront, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p->smem);
-  int per_sm = 0;
-  if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, souffle_lstm_wavefront, kLstmThreads, p->smem);
-  if (e == cudaSuccess && per_sm * sms < d.layers * kLstmParts) {
+  cudaError_t e = cudaFuncSetAttribute(souffle_lstm_wavefront, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lstm_smem_bytes(kLstmMaxHidden));
+  if (e == cudaSuccess && lstm_check_resident(d.layers, p->smem) != SOUFFLE_OK) {
     delete p;
-    return fail(SOUFFLE_NOT_CORESIDENT, "%d CTAs needed, %d can be resident", d.layers * kLstmParts, per_sm * sms);
+    return SOUFFLE_NOT_CORESIDENT;
   }
   if (e == cudaSuccess) e = cudaMalloc((void**)&p->w_in, wbytes);
   if (e == cudaSuccess) e = cudaMalloc((void**)&p->w_state, wbytes);
@@ -1393,9 +1445,8 @@ int souffle_lstm_forward(SouffleLstmPlan* plan, const float* x, float* y, souffl
   lp.status = plan->status;
   lp.layers = d.layers; lp.hidden = d.hidden; lp.steps = d.steps; lp.ref_input_delay = d.ref_input_delay;
   lp.timeout_ns = (unsigned long long)(d.timeout_ms > 0 ? d.timeout_ms : 2000) * 1000000ull;
-  void* kargs[] = {&lp};
-  SF_CUDA(cudaLaunchCooperativeKernel((const void*)souffle_lstm_wavefront, dim3(d.layers * kLstmParts), dim3(kLstmThreads),
-                                      kargs, plan->smem, reinterpret_cast<cudaStream_t>(stream)));
+  const int rc = lstm_launch(lp, plan->smem, reinterpret_cast<cudaStream_t>(stream));
+  if (rc) return rc;
   plan->launch_id++;
   return SOUFFLE_OK;
 }
@@ -1430,8 +1481,7 @@ int souffle_lstm_forward_static(const SouffleLstmDesc* desc, const void* w_in, c
   int dev = 0;
   SF_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 16) return fail(SOUFFLE_BAD_DEVICE, "device index %d out of range", dev);
-  const int H = d.hidden, rows = 4 * (H / kLstmParts);
-  const size_t smem = (size_t)rows * (2 * H * 2 + 64) + (size_t)(2 * H + rows) * 4 + 16;
+  const size_t smem = lstm_smem_bytes(d.hidden);
   StaticLstmDevice& sd = g_static_lstm[dev];
   if (!sd.ready) {
     int cc = 0;
@@ -1444,11 +1494,11 @@ int souffle_lstm_forward_static(const SouffleLstmDesc* desc, const void* w_in, c
     sd.ready = true;
   }
   // allow the largest shared-memory request any shape makes (a plan may have lowered the limit since)
-  SF_CUDA(cudaFuncSetAttribute(souffle_lstm_wavefront, cudaFuncAttributeMaxDynamicSharedMemorySize, 141840));
-  int per_sm = 0;
-  SF_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, souffle_lstm_wavefront, kLstmThreads, smem));
-  if (per_sm * sd.sms < d.layers * kLstmParts)
-    return fail(SOUFFLE_NOT_CORESIDENT, "%d CTAs needed, %d can be resident", d.layers * kLstmParts, per_sm * sd.sms);
+  SF_CUDA(cudaFuncSetAttribute(souffle_lstm_wavefront, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lstm_smem_bytes(kLstmMaxHidden)));
+  {
+    const int rc = lstm_check_resident(d.layers, smem);
+    if (rc) return rc;
+  }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   unsigned char* ctl = sd.scratch + kStaticHiddenFloats * 4;
   // counters and status must start at zero; the hidden-state slots are all written before they are read
@@ -1464,10 +1514,7 @@ int souffle_lstm_forward_static(const SouffleLstmDesc* desc, const void* w_in, c
   lp.status = device_status ? reinterpret_cast<int*>(device_status) : reinterpret_cast<int*>(ctl + 256);
   lp.layers = d.layers; lp.hidden = d.hidden; lp.steps = d.steps; lp.ref_input_delay = d.ref_input_delay;
   lp.timeout_ns = (unsigned long long)(d.timeout_ms > 0 ? d.timeout_ms : 2000) * 1000000ull;
-  void* kargs[] = {&lp};
-  SF_CUDA(cudaLaunchCooperativeKernel((const void*)souffle_lstm_wavefront, dim3(d.layers * kLstmParts), dim3(kLstmThreads),
-                                      kargs, smem, st));
-  return SOUFFLE_OK;
+  return lstm_launch(lp, smem, st);
 }
 
 // ======================================================================================
