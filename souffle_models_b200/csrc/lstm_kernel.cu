@@ -79,6 +79,11 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
   return true;
 }
 
+// Position of element e of an input or hidden vector in shared memory: the vector is cut into chunks of eight
+// elements (the columns one 16-byte chunk of fp16 weights multiplies); the first halves of all chunks come first, the
+// second halves after them, so that the sixteen threads of a unit read 16 contiguous bytes each.
+__host__ __device__ inline int lstm_vec_index(int e, int H) { return ((e >> 3) << 2) + (e & 3) + ((e & 4) ? H / 2 : 0); }
+
 // Shared memory of a CTA, in this order: weights [rows = 4*U][2H halves, 64-byte pad per row]; input vectors
 // [kLstmXBufs][H] fp32; hidden vectors [2][H] fp32 (written by the whole cluster); gate pre-activations
 // [2][rows] fp32; mbarriers xfull[kLstmXBufs], xempty[kLstmXBufs], hfull[2]; abort, verdict and produced words.
@@ -112,7 +117,7 @@ __global__ void __launch_bounds__(kLstmBlock, 1) souffle_lstm_wavefront(const Ls
     abort_s[2] = 0;
     for (int i = 0; i < kLstmXBufs; ++i) {
       mbar_init(xfull0 + 8 * i, 32);            // the 32 lanes of the fetch warp
-      mbar_init(xempty0 + 8 * i, 1);
+      mbar_init(xempty0 + 8 * i, (uint32_t)(16 * U));   // every thread of the cell arithmetic
     }
     for (int i = 0; i < 2; ++i) {               // h(0) and h(1): one local arrival that announces H * 4 bytes
       mbar_init(hfull0 + 8 * i, 1);
@@ -147,7 +152,7 @@ __global__ void __launch_bounds__(kLstmBlock, 1) souffle_lstm_wavefront(const Ls
     if (tid == kLstmThreads + 32) {
       uint32_t published = 0, spins = 0;
       while (published < (uint32_t)T) {
-        const uint32_t n = ld_acquire_cta_shared_u32(produced_a);
+        const uint32_t n = ld_acquire_cta_shared_u32(produced_a) / (uint32_t)U;     // whole steps only
         if (n > published) {
           red_add_release_u32(p.done + layer, n - published);
           published = n;
@@ -181,81 +186,98 @@ __global__ void __launch_bounds__(kLstmBlock, 1) souffle_lstm_wavefront(const Ls
       } else {
         src = p.h_all + ((size_t)(layer - 1) * T + t) * H;
       }
-      for (int i = lane; i < H / 4; i += 32) {
+      for (int i = lane; i < H / 4; i += 32) {     // elements 4i .. 4i+3 = one half of chunk i / 2 (see lstm_vec_index)
         const float4 v = src ? __ldcg(reinterpret_cast<const float4*>(src) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-        *reinterpret_cast<float4*>(x_s + xb * H + i * 4) = v;
+        *reinterpret_cast<float4*>(x_s + xb * H + (i & 1) * (H / 2) + (i >> 1) * 4) = v;
       }
       mbar_arrive(xfull0 + 8 * xb);             // release: this lane's stores are visible to whoever waits
     }
   } else {
     // ---------------- cell arithmetic ----------------
-    // thread -> (row, quarter): tpr threads share a row and interleave its 16-byte chunks
-    const int tpr = kLstmThreads / rows;        // threads per row (4 for H = 256)
-    const int row = tid / tpr, q = tid % tpr;
-    const int n_chunks = 2 * H / 8 / tpr;       // chunks per thread
-    float c_state = 0.0f;                       // cell state of unit `tid` (tid < U)
-    const float bias_u = (p.bias && tid < U) ? p.bias[layer * H + part * U + tid] : 0.0f;
-    uint32_t peer_h[kLstmParts], peer_bar[kLstmParts];
+    // Sixteen threads share a unit: thread (u, q) multiplies the four gate rows of unit u with the 16-byte chunks
+    // q, q + 16, ... of [x ; h], so a chunk of the vector is read once for four rows; the sixteen partial sums meet
+    // by shuffles, and lane q = 0 ends up with the unit's four gate pre-activations in registers -- no second trip
+    // through shared memory, no barrier between the products and the cell update.
+    const int n_act = 16 * U;                   // 128, 256 or 512 threads
+    if (tid < n_act) {
+      const int u = tid >> 4, q = tid & 15;
+      const int nj = H / 64;                    // chunks per thread: 1, 2 or 4
+      float c_state = 0.0f;                     // cell state of unit u (kept by q == 0)
+      const int unit = part * U + u;
+      const float bias_u = (p.bias && q == 0) ? p.bias[layer * H + unit] : 0.0f;
+      uint32_t peer_h[kLstmParts], peer_bar[kLstmParts];
 #pragma unroll
-    for (int r = 0; r < kLstmParts; ++r) {
-      peer_h[r] = map_shared_rank(smem_u32(h_s), (uint32_t)r);
-      peer_bar[r] = map_shared_rank(hfull0, (uint32_t)r);
-    }
-    for (int t = 0; t < T; ++t) {
-      const int xb = t % kLstmXBufs, hb = t & 1;            // h(t) goes to h_s[hb]; h(t-1) is in h_s[hb ^ 1]
-      // ---- one thread waits for x(t) and h(t-1); its verdict is the CTA's ----
-      if (tid == 0) {
-        bool ok = mbar_wait(xfull0 + 8 * xb, (uint32_t)(t / kLstmXBufs) & 1u, ctl, 910);
-        if (ok && t > 0) {
-          ok = mbar_wait_cluster(hfull0 + 8 * (hb ^ 1), (uint32_t)((t - 1) >> 1) & 1u, ctl, 800 + layer);
-          // that barrier's next phase receives h(t+1); nobody sends it before having this CTA's h(t)
-          if (ok && t + 1 < T) mbar_expect_tx(hfull0 + 8 * (hb ^ 1), (uint32_t)H * 4u);
-        }
-        if (!ok) {
-          *abort_s = 1;
-          *verdict_s = 0;
-        }
+      for (int r = 0; r < kLstmParts; ++r) {
+        peer_h[r] = map_shared_rank(smem_u32(h_s), (uint32_t)r);
+        peer_bar[r] = map_shared_rank(hfull0, (uint32_t)r);
       }
-      named_barrier_sync(1, kLstmThreads);
-      if (*verdict_s == 0) break;
-      // ---- gate pre-activations: fp16 weights x fp32 vector, fp32 accumulate ----
-      {
+      const uint8_t* wu = reinterpret_cast<const uint8_t*>(w_s) + (size_t)(4 * u) * row_bytes;
+      for (int t = 0; t < T; ++t) {
+        const int xb = t % kLstmXBufs, hb = t & 1;          // h(t) goes to h_s[hb]; h(t-1) is in h_s[hb ^ 1]
+        // ---- one thread waits for x(t) and h(t-1); its verdict is the CTA's ----
+        if (tid == 0) {
+          bool ok = mbar_wait(xfull0 + 8 * xb, (uint32_t)(t / kLstmXBufs) & 1u, ctl, 910);
+          if (ok && t > 0) {
+            ok = mbar_wait_cluster(hfull0 + 8 * (hb ^ 1), (uint32_t)((t - 1) >> 1) & 1u, ctl, 800 + layer);
+            // that barrier's next phase receives h(t+1); nobody sends it before having this CTA's h(t)
+            if (ok && t + 1 < T) mbar_expect_tx(hfull0 + 8 * (hb ^ 1), (uint32_t)H * 4u);
+          }
+          if (!ok) {
+            *abort_s = 1;
+            *verdict_s = 0;
+          }
+        }
+        named_barrier_sync(1, n_act);
+        if (*verdict_s == 0) break;
+        // ---- gate pre-activations: fp16 weights x fp32 vector, fp32 accumulate ----
         const float* xv = x_s + xb * H;
         const float* hv = h_s + (hb ^ 1) * H;
-        const uint8_t* wr = reinterpret_cast<const uint8_t*>(w_s) + (size_t)row * row_bytes;
-        float acc = 0.0f;
-#pragma unroll 4
-        for (int j = 0; j < n_chunks; ++j) {
-          const int ch = j * tpr + q;
-          const uint4 u = *reinterpret_cast<const uint4*>(wr + ch * 16);
-          const float* v = ch < H / 8 ? xv + ch * 8 : hv + (ch - H / 8) * 8;
-          const float4 a = *reinterpret_cast<const float4*>(v);
-          const float4 b = *reinterpret_cast<const float4*>(v + 4);
-          const __half2* h2 = reinterpret_cast<const __half2*>(&u);
-          const float2 w0 = __half22float2(h2[0]), w1 = __half22float2(h2[1]), w2 = __half22float2(h2[2]),
-                       w3 = __half22float2(h2[3]);
-          acc = fmaf(w0.x, a.x, acc); acc = fmaf(w0.y, a.y, acc); acc = fmaf(w1.x, a.z, acc); acc = fmaf(w1.y, a.w, acc);
-          acc = fmaf(w2.x, b.x, acc); acc = fmaf(w2.y, b.y, acc); acc = fmaf(w3.x, b.z, acc); acc = fmaf(w3.y, b.w, acc);
-        }
-        for (int o = tpr >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        if (q == 0) g_s[hb * rows + row] = acc;
-      }
-      named_barrier_sync(1, kLstmThreads);
-      if (tid == 0) mbar_arrive(xempty0 + 8 * xb);          // every thread has read x(t): the slot may be refilled
-      // ---- cell update for the U owned units; h(t) -> the whole cluster and the next layer ----
-      if (tid < U) {
-        const float* g = g_s + hb * rows + tid * 4;
-        const float gi = g[0] + bias_u, gj = g[1] + bias_u, gf = g[2] + bias_u, go = g[3] + bias_u;
-        c_state = c_state * sigmoid_f(gf + 1.0f) + sigmoid_f(gi) * tanhf(gj);
-        const float h = tanhf(c_state) * sigmoid_f(go);
-        const int unit = part * U + tid;
-        const uint32_t off = (uint32_t)(hb * H + unit) * 4u;
+        float acc[4][2];
 #pragma unroll
-        for (int r = 0; r < kLstmParts; ++r) st_async_b32(peer_h[r] + off, __float_as_uint(h), peer_bar[r] + 8u * (uint32_t)hb);
-        __stcg(p.h_all + ((size_t)layer * T + t) * H + unit, h);
-        if (layer == L - 1) p.y[(size_t)t * H + unit] = h;
-        __syncwarp(U >= 32 ? 0xffffffffu : ((1u << U) - 1u));
-        if (tid == 0) st_release_cta_shared_u32(produced_a, (uint32_t)(t + 1));   // the publish warp takes it from here
+        for (int g = 0; g < 4; ++g) acc[g][0] = acc[g][1] = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (j < nj) {
+            const int ch = j * 16 + q;                      // chunk of [x ; h]
+            const bool is_h = ch >= H / 8;
+            const float* vec = is_h ? hv : xv;
+            const int cl = is_h ? ch - H / 8 : ch;
+            const float4 a = *reinterpret_cast<const float4*>(vec + cl * 4);
+            const float4 b = *reinterpret_cast<const float4*>(vec + H / 2 + cl * 4);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const uint4 w = *reinterpret_cast<const uint4*>(wu + (size_t)g * row_bytes + ch * 16);
+              const __half2* h2 = reinterpret_cast<const __half2*>(&w);
+              const float2 w0 = __half22float2(h2[0]), w1 = __half22float2(h2[1]), w2 = __half22float2(h2[2]),
+                           w3 = __half22float2(h2[3]);
+              acc[g][0] = fmaf(w0.x, a.x, acc[g][0]); acc[g][1] = fmaf(w0.y, a.y, acc[g][1]);
+              acc[g][0] = fmaf(w1.x, a.z, acc[g][0]); acc[g][1] = fmaf(w1.y, a.w, acc[g][1]);
+              acc[g][0] = fmaf(w2.x, b.x, acc[g][0]); acc[g][1] = fmaf(w2.y, b.y, acc[g][1]);
+              acc[g][0] = fmaf(w3.x, b.z, acc[g][0]); acc[g][1] = fmaf(w3.y, b.w, acc[g][1]);
+            }
+          }
+        }
+        mbar_arrive(xempty0 + 8 * xb);                      // this thread has read x(t)
+        float gsum[4];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          float v = acc[g][0] + acc[g][1];
+#pragma unroll
+          for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+          gsum[g] = v;
+        }
+        // ---- cell update of unit u; h(t) -> the whole cluster and the next layer ----
+        if (q == 0) {
+          const float gi = gsum[0] + bias_u, gj = gsum[1] + bias_u, gf = gsum[2] + bias_u, go = gsum[3] + bias_u;
+          c_state = c_state * sigmoid_f(gf + 1.0f) + sigmoid_f(gi) * tanhf(gj);
+          const float h = tanhf(c_state) * sigmoid_f(go);
+          const uint32_t off = (uint32_t)(hb * H + lstm_vec_index(unit, H)) * 4u;
+#pragma unroll
+          for (int r = 0; r < kLstmParts; ++r) st_async_b32(peer_h[r] + off, __float_as_uint(h), peer_bar[r] + 8u * (uint32_t)hb);
+          __stcg(p.h_all + ((size_t)layer * T + t) * H + unit, h);
+          if (layer == L - 1) p.y[(size_t)t * H + unit] = h;
+          red_add_release_cta_shared_u32(produced_a, 1u);     // the publish warp takes it from here
+        }
       }
     }
   }

@@ -305,6 +305,9 @@ __device__ __forceinline__ void st_async_b32(uint32_t cluster_addr, uint32_t v, 
 __device__ __forceinline__ void st_release_cta_shared_u32(uint32_t addr, uint32_t v) {
   asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
+__device__ __forceinline__ void red_add_release_cta_shared_u32(uint32_t addr, uint32_t v) {
+  asm volatile("red.release.cta.shared::cta.add.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
 __device__ __forceinline__ uint32_t ld_acquire_cta_shared_u32(uint32_t addr) {
   uint32_t v;
   asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
