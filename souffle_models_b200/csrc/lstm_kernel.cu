@@ -6,8 +6,9 @@
 // gates i, j, f, o;  c' = c*sigmoid(f+1) + sigmoid(i)*tanh(j);  h' = tanh(c')*sigmoid(o).
 //
 // Design: every layer is owned by one thread-block cluster of kLstmParts CTAs; a CTA keeps its
-// 4*U gate rows of both weight matrices (fp16, [x;h] concatenated along K) in shared memory for
-// the whole sequence and its units' cell state in registers.  Every path through the (layer, step)
+// 4*U gate rows of both weight matrices (fp16, [x;h] concatenated along K) on chip for the whole
+// sequence -- three quarters in the registers of its 512 cell threads (48 each at hidden 256: what 18
+// warps leave room for), the rest in shared memory -- and its units' cell state.  Every path through the (layer, step)
 // grid has steps-1 hops along time and layers-1 hops across layers, so the hop along time is the one
 // that has to be short: a CTA writes its units' new hidden state straight into the shared memory of
 // the eight CTAs of its cluster (distributed shared memory, st.async: the store itself counts as a
@@ -33,6 +34,7 @@ constexpr int kLstmBlock = kLstmThreads + 64;      // + the fetch warp and the p
 constexpr int kLstmParts = 8;                      // CTAs per layer = cluster size
 constexpr int kLstmMaxHidden = 256;
 constexpr int kLstmXBufs = 4;                      // input vectors the fetch warp may run ahead
+constexpr int kLstmRegChunks = 3;                  // of a thread's (up to 4) weight chunks per gate row, those kept in registers
 
 struct LstmParams {
   const __half* w_in;     // [4*L][H][H], row = output unit, col = input
@@ -48,7 +50,9 @@ struct LstmParams {
   unsigned long long timeout_ns;
 };
 
-__device__ __forceinline__ float sigmoid_f(float v) { return 1.0f / (1.0f + __expf(-v)); }
+// ex2-based forms: absolute error of a few 1e-7 on values in [-1, 1], far inside the 5e-3 bar on hidden states
+__device__ __forceinline__ float sigmoid_f(float v) { return __fdividef(1.0f, 1.0f + __expf(-v)); }
+__device__ __forceinline__ float tanh_f(float v) { return 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * v)); }
 
 __device__ __forceinline__ bool wait_count(const unsigned* ctr, unsigned target, const WaitCtl& c, int where) {
   uint32_t spins = 0;
@@ -84,12 +88,13 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
 // second halves after them, so that the sixteen threads of a unit read 16 contiguous bytes each.
 __host__ __device__ inline int lstm_vec_index(int e, int H) { return ((e >> 3) << 2) + (e & 3) + ((e & 4) ? H / 2 : 0); }
 
-// Shared memory of a CTA, in this order: weights [rows = 4*U][2H halves, 64-byte pad per row]; input vectors
+// Shared memory of a CTA, in this order: weights [rows = 4*U][2H halves, 64-byte pad per row] (only the chunks the
+// cell threads do not keep in registers are read from it); input vectors
 // [kLstmXBufs][H] fp32; hidden vectors [2][H] fp32 (written by the whole cluster); gate pre-activations
 // [2][rows] fp32; mbarriers xfull[kLstmXBufs], xempty[kLstmXBufs], hfull[2]; abort, verdict and produced words.
 __host__ __device__ inline size_t lstm_smem_bytes(int H) {
   const int rows = 4 * (H / kLstmParts);
-  return (size_t)rows * (2 * H * 2 + 64) + (size_t)(kLstmXBufs * H + 2 * H + 2 * rows) * 4 + (2 * kLstmXBufs + 2) * 8 + 16;
+  return (kLstmRegChunks < 4 ? (size_t)rows * (2 * H * 2 + 64) : 0) + (size_t)(kLstmXBufs * H + 2 * H + 2 * rows) * 4 + (2 * kLstmXBufs + 2) * 8 + 16;
 }
 
 __global__ void __launch_bounds__(kLstmBlock, 1) souffle_lstm_wavefront(const LstmParams p) {
@@ -99,7 +104,7 @@ __global__ void __launch_bounds__(kLstmBlock, 1) souffle_lstm_wavefront(const Ls
   const int rows = 4 * U;                       // gate rows, row = unit*4 + gate
   const int row_bytes = 2 * H * 2 + 64;
   __half* w_s = reinterpret_cast<__half*>(lsm);
-  float* x_s = reinterpret_cast<float*>(lsm + (size_t)rows * row_bytes);      // [kLstmXBufs][H]
+  float* x_s = reinterpret_cast<float*>(lsm + (kLstmRegChunks < 4 ? (size_t)rows * row_bytes : 0));   // [kLstmXBufs][H]
   float* h_s = x_s + kLstmXBufs * H;                                          // [2][H]
   float* g_s = h_s + 2 * H;                                                   // [2][rows]
   uint64_t* bars = reinterpret_cast<uint64_t*>(g_s + 2 * rows);
@@ -127,8 +132,8 @@ __global__ void __launch_bounds__(kLstmBlock, 1) souffle_lstm_wavefront(const Ls
   }
   if (blockIdx.x == 0 && tid < L) p.done_next[tid] = 0u;
   for (int i = tid; i < 2 * H; i += kLstmBlock) h_s[i] = 0.0f;               // h before the first step
-  // ---- weights -> shared memory (once) ----
-  {
+  // ---- weights -> shared memory (once), unless the cell threads keep all of them in registers ----
+  if (kLstmRegChunks < 4) {
     const int chunks_per_row = 2 * H / 8;       // 16-byte chunks: first H/8 from w_in, rest from w_state
     for (int i = tid; i < rows * chunks_per_row; i += kLstmBlock) {
       const int r = i / chunks_per_row, ch = i % chunks_per_row;
@@ -205,13 +210,23 @@ __global__ void __launch_bounds__(kLstmBlock, 1) souffle_lstm_wavefront(const Ls
       float c_state = 0.0f;                     // cell state of unit u (kept by q == 0)
       const int unit = part * U + u;
       const float bias_u = (p.bias && q == 0) ? p.bias[layer * H + unit] : 0.0f;
-      uint32_t peer_h[kLstmParts], peer_bar[kLstmParts];
-#pragma unroll
-      for (int r = 0; r < kLstmParts; ++r) {
-        peer_h[r] = map_shared_rank(smem_u32(h_s), (uint32_t)r);
-        peer_bar[r] = map_shared_rank(hfull0, (uint32_t)r);
-      }
+      const uint32_t h_s_a = smem_u32(h_s);
       const uint8_t* wu = reinterpret_cast<const uint8_t*>(w_s) + (size_t)(4 * u) * row_bytes;
+      // this thread's weights: chunk j * 16 + q of the four gate rows of unit u, straight from global memory
+      uint4 wreg[kLstmRegChunks > 0 ? kLstmRegChunks : 1][4];
+#pragma unroll
+      for (int j = 0; j < kLstmRegChunks; ++j) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          wreg[j][g] = make_uint4(0u, 0u, 0u, 0u);
+          if (j < nj) {
+            const int ch = j * 16 + q;
+            const bool st = ch >= H / 8;
+            const __half* src = (st ? p.w_state : p.w_in) + ((size_t)(layer * 4 + g) * H + unit) * H + (st ? ch - H / 8 : ch) * 8;
+            wreg[j][g] = __ldg(reinterpret_cast<const uint4*>(src));
+          }
+        }
+      }
       for (int t = 0; t < T; ++t) {
         const int xb = t % kLstmXBufs, hb = t & 1;          // h(t) goes to h_s[hb]; h(t-1) is in h_s[hb ^ 1]
         // ---- one thread waits for x(t) and h(t-1); its verdict is the CTA's ----
@@ -246,7 +261,16 @@ __global__ void __launch_bounds__(kLstmBlock, 1) souffle_lstm_wavefront(const Ls
             const float4 b = *reinterpret_cast<const float4*>(vec + H / 2 + cl * 4);
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
-              const uint4 w = *reinterpret_cast<const uint4*>(wu + (size_t)g * row_bytes + ch * 16);
+              uint4 w;
+              if (j < kLstmRegChunks) {
+                uint4& wr = wreg[j < kLstmRegChunks ? j : 0][g];
+                // opaque to the optimiser: otherwise the fp16 -> fp32 conversions are hoisted out of the step loop
+                // and the weights occupy twice the registers
+                asm volatile("" : "+r"(wr.x), "+r"(wr.y), "+r"(wr.z), "+r"(wr.w));
+                w = wr;
+              } else {
+                w = *reinterpret_cast<const uint4*>(wu + (size_t)g * row_bytes + ch * 16);
+              }
               const __half2* h2 = reinterpret_cast<const __half2*>(&w);
               const float2 w0 = __half22float2(h2[0]), w1 = __half22float2(h2[1]), w2 = __half22float2(h2[2]),
                            w3 = __half22float2(h2[3]);
@@ -269,11 +293,12 @@ __global__ void __launch_bounds__(kLstmBlock, 1) souffle_lstm_wavefront(const Ls
         // ---- cell update of unit u; h(t) -> the whole cluster and the next layer ----
         if (q == 0) {
           const float gi = gsum[0] + bias_u, gj = gsum[1] + bias_u, gf = gsum[2] + bias_u, go = gsum[3] + bias_u;
-          c_state = c_state * sigmoid_f(gf + 1.0f) + sigmoid_f(gi) * tanhf(gj);
-          const float h = tanhf(c_state) * sigmoid_f(go);
+          c_state = c_state * sigmoid_f(gf + 1.0f) + sigmoid_f(gi) * tanh_f(gj);
+          const float h = tanh_f(c_state) * sigmoid_f(go);
           const uint32_t off = (uint32_t)(hb * H + lstm_vec_index(unit, H)) * 4u;
 #pragma unroll
-          for (int r = 0; r < kLstmParts; ++r) st_async_b32(peer_h[r] + off, __float_as_uint(h), peer_bar[r] + 8u * (uint32_t)hb);
+          for (int r = 0; r < kLstmParts; ++r)
+            st_async_b32(map_shared_rank(h_s_a + off, (uint32_t)r), __float_as_uint(h), map_shared_rank(hfull0 + 8u * (uint32_t)hb, (uint32_t)r));
           __stcg(p.h_all + ((size_t)layer * T + t) * H + unit, h);
           if (layer == L - 1) p.y[(size_t)t * H + unit] = h;
           red_add_release_cta_shared_u32(produced_a, 1u);     // the publish warp takes it from here
