@@ -197,6 +197,18 @@ def latency_cold_us(bert, so, iters: int = 30) -> float:
     return ts[len(ts) // 2] * 1000.0
 
 
+_RESULT_FD = None
+
+
+def emit(line: str) -> None:
+    """The one result line goes to the process's original stdout."""
+    if _RESULT_FD is None:
+        print(line, flush=True)
+    else:
+        sys.stdout.flush()
+        os.write(_RESULT_FD, (line + "\n").encode())
+
+
 def run_ours(args, rank: int, world: int, local_rank: int):
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
@@ -326,7 +338,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     }
     if cpu:
         out["cpu_baseline"] = cpu
-    print(json.dumps(out))
+    emit(json.dumps(out))
 
 
 def profile_case(batch: int, n_layers: int) -> None:
@@ -370,6 +382,11 @@ def main():
         return
     if world > 1:
         import torch.distributed as dist
+        # libraries print banners (the NCCL version) on the C-level stdout: send everything but the result line to stderr
+        global _RESULT_FD
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     try:
