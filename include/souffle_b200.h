@@ -177,7 +177,7 @@ int souffle_bert_plan_stage_info(SouffleBertPlan* plan, int index, int out[6]);
  * (cpp/lstm/lstm_reuse_shared_memory.cu:309-318).
  * ------------------------------------------------------------------------------------------ */
 typedef struct SouffleLstmDesc {
-  int32_t layers;          /* 1..18 (8 CTAs per layer must be co-resident) */
+  int32_t layers;          /* 1..18 (one thread-block cluster of 8 CTAs per layer; all clusters must be co-resident) */
   int32_t hidden;          /* 64, 128 or 256 (input width == hidden) */
   int32_t steps;           /* >= 1 */
   int32_t ref_input_delay; /* 1: feed x one step late like the reference kernel (step 0 sees zeros, the last
