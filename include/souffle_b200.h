@@ -193,6 +193,10 @@ int souffle_lstm_plan_destroy(SouffleLstmPlan* plan);
 /* y[steps][hidden] (fp32, top layer's h per step) from x[steps][hidden] (fp32); zero initial state. */
 int souffle_lstm_forward(SouffleLstmPlan* plan, const float* x, float* y, souffle_stream_t stream);
 int souffle_lstm_plan_status(SouffleLstmPlan* plan);
+/* 1 while the driver has accepted every LSTM launch as a cooperative launch of thread-block clusters (all clusters
+ * guaranteed resident together); 0 once it has refused that combination and launches carry the cluster dimension
+ * alone (residency then rests on the occupancy check made at plan creation and on an otherwise idle GPU). */
+int souffle_lstm_launch_mode(void);
 
 /* Has no counterpart in the reference.  The same stacked-LSTM forward for callers that must not allocate
  * device memory (a server whose memory pool owns the whole GPU, a plugin inside someone else's process, a

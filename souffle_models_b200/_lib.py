@@ -71,6 +71,7 @@ SIGNATURES = {
     "souffle_lstm_plan_destroy": (C.c_int, [C.c_void_p]),
     "souffle_lstm_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "souffle_lstm_plan_status": (C.c_int, [C.c_void_p]),
+    "souffle_lstm_launch_mode": (C.c_int, []),
     "souffle_lstm_forward_static": (C.c_int, [C.POINTER(LstmDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                               C.c_void_p, C.c_void_p, C.c_void_p]),
     "souffle_gemm_workspace_bytes": (C.c_size_t, []),

@@ -1329,7 +1329,11 @@ int souffle_swin_block_plan_status(SouffleSwinPlan* sp) {
 // once, which the cross-layer waits assume); a driver that refuses the two attributes together gets the cluster
 // launch alone -- lstm_check_resident() has then already established that every cluster fits, and every wait in
 // the kernel is bounded.
-static int g_lstm_coop = 1;
+static int lstm_coop_default() {
+  const char* e = getenv("SOUFFLE_LSTM_COOPERATIVE");     // "0": never ask for the cooperative attribute
+  return (e && e[0] == '0') ? 0 : 1;
+}
+static int g_lstm_coop = lstm_coop_default();
 static void lstm_launch_config(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* at, int layers, size_t smem, cudaStream_t st, bool coop) {
   memset(cfg, 0, sizeof(*cfg));
   cfg->gridDim = dim3(layers * kLstmParts);
@@ -1450,6 +1454,8 @@ int souffle_lstm_forward(SouffleLstmPlan* plan, const float* x, float* y, souffl
   plan->launch_id++;
   return SOUFFLE_OK;
 }
+
+int souffle_lstm_launch_mode(void) { return g_lstm_coop; }
 
 int souffle_lstm_plan_status(SouffleLstmPlan* plan) {
   if (!plan) return fail(SOUFFLE_BAD_ARGUMENT, "null plan");
