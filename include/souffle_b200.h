@@ -193,9 +193,10 @@ int souffle_lstm_plan_destroy(SouffleLstmPlan* plan);
 /* y[steps][hidden] (fp32, top layer's h per step) from x[steps][hidden] (fp32); zero initial state. */
 int souffle_lstm_forward(SouffleLstmPlan* plan, const float* x, float* y, souffle_stream_t stream);
 int souffle_lstm_plan_status(SouffleLstmPlan* plan);
-/* 1 while the driver has accepted every LSTM launch as a cooperative launch of thread-block clusters (all clusters
- * guaranteed resident together); 0 once it has refused that combination and launches carry the cluster dimension
- * alone (residency then rests on the occupancy check made at plan creation and on an otherwise idle GPU). */
+/* 0: LSTM launches carry the cluster dimension alone (the default: residency of all clusters rests on the occupancy
+ * check made at plan creation, every device-side wait is bounded, and Nsight Compute can capture the launch);
+ * 1: SOUFFLE_LSTM_COOPERATIVE=1 was set when the library was loaded and the driver has so far accepted the
+ * cooperative attribute on top of the cluster dimension. */
 int souffle_lstm_launch_mode(void);
 
 /* Has no counterpart in the reference.  The same stacked-LSTM forward for callers that must not allocate

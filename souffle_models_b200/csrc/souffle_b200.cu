@@ -1325,13 +1325,14 @@ int souffle_swin_block_plan_status(SouffleSwinPlan* sp) {
 // ======================================================================================
 // LSTM plan
 // ======================================================================================
-// One cluster of kLstmParts CTAs per layer.  The launch is also asked to be cooperative (all clusters resident at
-// once, which the cross-layer waits assume); a driver that refuses the two attributes together gets the cluster
-// launch alone -- lstm_check_resident() has then already established that every cluster fits, and every wait in
-// the kernel is bounded.
+// One cluster of kLstmParts CTAs per layer.  lstm_check_resident() establishes at plan creation that all clusters fit
+// the GPU at once, which the cross-layer waits assume, and every wait in the kernel is bounded.  The cooperative
+// launch attribute would add the driver's own guarantee, but Nsight Compute cannot capture a launch that carries both
+// attributes (it answers LaunchFailed), so it is asked for only when SOUFFLE_LSTM_COOPERATIVE=1 is set; a driver that
+// refuses the combination gets the cluster launch alone from then on.
 static int lstm_coop_default() {
-  const char* e = getenv("SOUFFLE_LSTM_COOPERATIVE");     // "0": never ask for the cooperative attribute
-  return (e && e[0] == '0') ? 0 : 1;
+  const char* e = getenv("SOUFFLE_LSTM_COOPERATIVE");
+  return (e && e[0] == '1') ? 1 : 0;
 }
 static int g_lstm_coop = lstm_coop_default();
 static void lstm_launch_config(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* at, int layers, size_t smem, cudaStream_t st, bool coop) {
