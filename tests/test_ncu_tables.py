@@ -44,3 +44,14 @@ def test_missing_header(tmp_path):
     p.write_text("nothing,here\n")
     with pytest.raises(ValueError):
         ncu_tables.read_launches(str(p))
+
+
+def test_profile_cases_lists_every_model_and_refuses_unknown_names():
+    import pytest
+    from souffle_models_b200 import profile_cases
+    for name in ("bert_layer", "bert_base", "bert_layer_s384", "bert_layer_s384_plan", "lstm", "swin_mlp", "swin_pair", "swin_stage",
+                 "se_module"):
+        assert name in profile_cases.__doc__
+    assert len(profile_cases.SE_SHAPES) == 10
+    with pytest.raises(SystemExit):
+        profile_cases.make_case("no_such_case")

@@ -193,3 +193,11 @@ def test_lstm_and_swin_mlp_match_reference_cuda_outputs(golden_dir):
     hidden, out = swin.swin_fused_feed_mlp(src.cuda(), w1.cuda(), w2.cuda())
     assert (hidden[:32].float().cpu() - torch.from_numpy(g["swin_hidden_head"]).float()).abs().max() < 1e-2
     assert (out.float().cpu() - torch.from_numpy(g["swin_out"]).float()).abs().max() < 1.5e-2
+
+
+def test_lstm_launch_mode_and_profile_case():
+    """The default launch form carries the cluster dimension alone (mode 0); the small fixed workload used for ncu
+    captures runs and reports a time."""
+    from souffle_models_b200 import _lib, profile_cases
+    assert profile_cases.run("lstm", warmup=1, iters=2) > 0
+    assert _lib.load().souffle_lstm_launch_mode() in (0, 1)
