@@ -207,9 +207,9 @@ __global__ void __launch_bounds__(kLstmBlock, 1) souffle_lstm_wavefront(const Ls
     if (tid < n_act) {
       const int u = tid >> 4, q = tid & 15;
       const int nj = H / 64;                    // chunks per thread: 1, 2 or 4
-      float c_state = 0.0f;                     // cell state of unit u (kept by q == 0)
+      float c_state = 0.0f;                     // cell state of unit u (the same value in all sixteen lanes)
       const int unit = part * U + u;
-      const float bias_u = (p.bias && q == 0) ? p.bias[layer * H + unit] : 0.0f;
+      const float bias_u = p.bias ? p.bias[layer * H + unit] : 0.0f;
       const uint32_t h_s_a = smem_u32(h_s);
       const uint8_t* wu = reinterpret_cast<const uint8_t*>(w_s) + (size_t)(4 * u) * row_bytes;
       // this thread's weights: chunk j * 16 + q of the four gate rows of unit u, straight from global memory
@@ -291,17 +291,26 @@ __global__ void __launch_bounds__(kLstmBlock, 1) souffle_lstm_wavefront(const Ls
           gsum[g] = v;
         }
         // ---- cell update of unit u; h(t) -> the whole cluster and the next layer ----
-        if (q == 0) {
-          const float gi = gsum[0] + bias_u, gj = gsum[1] + bias_u, gf = gsum[2] + bias_u, go = gsum[3] + bias_u;
-          c_state = c_state * sigmoid_f(gf + 1.0f) + sigmoid_f(gi) * tanh_f(gj);
-          const float h = tanh_f(c_state) * sigmoid_f(go);
+        // All sixteen lanes hold the four sums.  Lanes 0..3 of the group take one gate's nonlinearity each (f, i, j, o),
+        // the four results come back by shuffle, and every lane then carries the same cell state and h: the sends to
+        // the eight CTAs of the cluster are issued by eight lanes at once.
+        {
+          const int q4 = q & 3;
+          const float pre = (q4 == 0 ? gsum[2] + 1.0f : q4 == 1 ? gsum[0] : q4 == 2 ? gsum[1] : gsum[3]) + bias_u;
+          const float act = q4 == 2 ? tanh_f(pre) : sigmoid_f(pre);
+          const int base = tid & 16;                        // lane of q == 0 within the warp
+          const float sf = __shfl_sync(0xffffffffu, act, base), si = __shfl_sync(0xffffffffu, act, base + 1);
+          const float tj = __shfl_sync(0xffffffffu, act, base + 2), so = __shfl_sync(0xffffffffu, act, base + 3);
+          c_state = c_state * sf + si * tj;
+          const float h = tanh_f(c_state) * so;
           const uint32_t off = (uint32_t)(hb * H + lstm_vec_index(unit, H)) * 4u;
-#pragma unroll
-          for (int r = 0; r < kLstmParts; ++r)
-            st_async_b32(map_shared_rank(h_s_a + off, (uint32_t)r), __float_as_uint(h), map_shared_rank(hfull0 + 8u * (uint32_t)hb, (uint32_t)r));
-          __stcg(p.h_all + ((size_t)layer * T + t) * H + unit, h);
-          if (layer == L - 1) p.y[(size_t)t * H + unit] = h;
-          red_add_release_cta_shared_u32(produced_a, 1u);     // the publish warp takes it from here
+          if (q < kLstmParts)
+            st_async_b32(map_shared_rank(h_s_a + off, (uint32_t)q), __float_as_uint(h), map_shared_rank(hfull0 + 8u * (uint32_t)hb, (uint32_t)q));
+          if (q == 0) {
+            __stcg(p.h_all + ((size_t)layer * T + t) * H + unit, h);
+            if (layer == L - 1) p.y[(size_t)t * H + unit] = h;
+            red_add_release_cta_shared_u32(produced_a, 1u);   // the publish warp takes it from here
+          }
         }
       }
     }
