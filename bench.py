@@ -11,7 +11,9 @@ all-gather of the outputs.  Metric: sequences per second over all GPUs.
 Prints one JSON line.  `value` is timed with inputs resident in HBM; `e2e` is the same step through
 the host-buffer entry point (pinned host input -> device -> encoder -> host output).  The batch-1
 latencies of one layer and of the 12-layer stack are reported under `latency_us`.
-`--impl reference` times the CPU restatement of the reference model (oracle/) on the host cores.
+`stages` carries the per-stage time of one layer at batch 1 and at batch 64 from the kernel's own stage clocks.
+`--impl reference` times the CPU restatement of the reference model (oracle/) on the host cores: the whole batch
+of 64 sequences per step, for exactly the steps and warm-ups asked for.
 """
 from __future__ import annotations
 
@@ -30,8 +32,12 @@ sys.path.insert(0, ROOT)
 
 BATCH, SEQ, HEADS, HEAD_DIM, FFN, LAYERS = 64, 128, 12, 64, 3072, 12
 HIDDEN = HEADS * HEAD_DIM
-DRAM_BYTES_PER_LAUNCH_B64 = 459_977_728 + 2_045_136_384      # read + write, measured with ncu (see profiles/)
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the timed kernel, from a one-pass
+# `ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum --clock-control none` capture of this command
+# (64 sequences per GPU) and of its 8-GPU shard size (8 sequences per GPU): {sequences per GPU: bytes}
+DRAM_BYTES_PER_LAUNCH = {64: 459_977_728 + 2_045_136_384, 8: 171_800_000 + 5_400_000}
 METRIC = "bert_base_12layer_seq128_batch64_sequences_per_second"
+WORKLOAD = "BERT-base 12-layer encoder, batch 64 (sharded by sequence), seq 128, lengths U[32,128]"
 SEED = 1239
 
 
@@ -122,16 +128,18 @@ def cpu_sample(n_seq: int, steps: int, warmup: int):
 
 
 def run_reference(args, rank: int, world: int):
+    """The reference arm: the CPU restatement of the reference model on all host threads, the whole batch of 64
+    sequences per step, exactly `--warmup` untimed and `--steps` timed passes."""
     if rank != 0:
         return
-    n_seq = 8
-    value, dt, cores = cpu_sample(n_seq, max(1, min(args.steps, 5)), max(1, min(args.warmup, 2)))
-    sample = f"{n_seq} of the {BATCH} sequences per step (12 layers, fp32 torch-CPU restatement of python/models/bert/bert_torch.py)"
+    steps, warmup = max(1, args.steps), max(0, args.warmup)
+    value, dt, cores = cpu_sample(BATCH, steps, warmup)
+    sample = f"all {BATCH} sequences per step (12 layers, fp32 torch-CPU restatement of python/models/bert/bert_torch.py)"
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": "sequences/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1000.0 * BATCH / n_seq,
+        "steps": steps, "warmup": warmup, "ms_per_step": dt * 1000.0,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "BERT-base 12-layer encoder, batch 64, seq 128, lengths U[32,128]", "sample": sample},
+        "config": {"workload": WORKLOAD, "sample": sample},
         "cpu_baseline": {"value": value, "unit": "sequences/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "sequences/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0}))
@@ -209,6 +217,34 @@ def emit(line: str) -> None:
         os.write(_RESULT_FD, (line + "\n").encode())
 
 
+STAGE_NAMES = ("qkv", "attention", "proj", "ln1", "fc1", "fc2", "ln2")
+
+
+def stage_profile(bert, so, batch: int, mhz: float):
+    """Per-stage time of ONE encoder layer at `batch` sequences from the kernel's own stage clocks (desc.profile):
+    median over the CTAs of work (stage start -> the CTA reaches the grid barrier) and barrier wait, in SM cycles and
+    in microseconds at `mhz`."""
+    cfg = so.BertConfig(batch, SEQ, HEADS, HEAD_DIM, FFN, "std")
+    layers = [{k: v.cuda() for k, v in w.items()} for w in so.make_bert_weights(cfg, SEED + 2, 1)]
+    enc = bert.BertEncoder(batch, SEQ, HEADS, HEAD_DIM, FFN, layers, tuning={"profile": 1})
+    x, lens = so.make_bert_input(cfg, SEED + 2, ragged=batch > 1)
+    xs, ls = x.cuda(), (lens.cuda() if lens is not None else None)
+    y = torch.empty_like(xs)
+    for _ in range(5):
+        enc.forward(xs, ls, y)
+    enc.status()
+    pr = enc.read_profile().double()
+    out = {}
+    for si, name in enumerate(STAGE_NAMES):
+        work = (pr[si, :, 1] - pr[si, :, 0]).median().item()
+        bar = (pr[si, :, 2] - pr[si, :, 1]).median().item() if si + 1 < len(STAGE_NAMES) else 0.0
+        out[name] = {"work_cycles": work, "barrier_cycles": bar, "us": (work + bar) / mhz}
+    k = pr[-1]
+    out["kernel_us"] = (k[:, 4].max() - k[:, 3].min()).item() / 1000.0      # first CTA in -> last CTA out, wall clock
+    enc.close()
+    return out
+
+
 def run_ours(args, rank: int, world: int, local_rank: int):
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
@@ -233,47 +269,20 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         if world > 1:
             sharding.gather_outputs(y_d, full)
 
+    # end to end: pinned host shard in, this rank's slice of the (gathered) result back to pinned host memory, every
+    # step; one GPU goes through the library's own host-buffer entry point, several through the package's pipeline
     x_h, y_h, l_h = xs.pin_memory(), torch.empty_like(xs).pin_memory(), ls.pin_memory()
-    # every rank reads back its own slice of the gathered result: the whole result reaches host memory once per step,
-    # spread over the rank processes like the inputs
-    full_h = torch.empty(per, SEQ, HIDDEN, dtype=torch.float16).pin_memory() if world > 1 else None
-    # multi-GPU end-to-end step: shard host -> device, encoder, gather over NVLink, gathered result -> host, as a
-    # three-stream pipeline over two sets of device buffers (the single-GPU entry point does the same inside the library)
-    pipe = None
-    if world > 1:
-        pipe = {"s_in": torch.cuda.Stream(), "s_out": torch.cuda.Stream(), "i": 0,
-                "x": [torch.empty_like(x_d) for _ in range(2)], "l": [torch.empty_like(l_d) for _ in range(2)],
-                "y": [torch.empty_like(y_d) for _ in range(2)], "full": [torch.empty_like(full) for _ in range(2)],
-                "ev_k": [None, None], "ev_out": [None, None]}
+    pipe = sharding.ShardedHostPipeline(enc.forward, x_d, l_d, rank, world) if world > 1 else None
 
     def step_e2e():
-        if world == 1:              # consecutive steps overlap copy-in, compute and copy-out (three streams)
+        if world == 1:
             enc.forward_host(x_h, l_h, y_h, wait=False)
-            return
-        cur, b = torch.cuda.current_stream(), pipe["i"] & 1
-        pipe["i"] += 1
-        with torch.cuda.stream(pipe["s_in"]):
-            if pipe["ev_k"][b] is not None:
-                pipe["s_in"].wait_event(pipe["ev_k"][b])        # the encoder of the step before last has read x[b]
-            pipe["x"][b].copy_(x_h, non_blocking=True)
-            pipe["l"][b].copy_(l_h, non_blocking=True)
-            ev_in = pipe["s_in"].record_event()
-        cur.wait_event(ev_in)
-        if pipe["ev_out"][b] is not None:
-            cur.wait_event(pipe["ev_out"][b])                    # full[b] has been copied out
-        enc.forward(pipe["x"][b], pipe["l"][b], pipe["y"][b])
-        sharding.gather_outputs(pipe["y"][b], pipe["full"][b])
-        pipe["ev_k"][b] = cur.record_event()
-        with torch.cuda.stream(pipe["s_out"]):
-            pipe["s_out"].wait_event(pipe["ev_k"][b])
-            full_h.copy_(pipe["full"][b][rank * per:(rank + 1) * per], non_blocking=True)
-            pipe["ev_out"][b] = pipe["s_out"].record_event()
+        else:
+            pipe.step(x_h, l_h, y_h)
 
     def drain_e2e():
         if pipe is not None:
-            for ev in pipe["ev_out"]:
-                if ev is not None:
-                    torch.cuda.current_stream().wait_event(ev)
+            pipe.drain()
 
     for _ in range(max(3, args.warmup)):
         step()
@@ -288,7 +297,19 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     ms_e2e = timed(step_e2e, args.steps, barrier, drain_e2e)
     enc.status()
     info = enc.info()
+    # outside the timed region: what every rank computed and gathered equals, bit for bit, what ONE GPU computes for
+    # the same sequences with the same plan (rank 0 runs every shard through its own encoder)
+    gathered_ok = None
     if world > 1:
+        step()
+        torch.cuda.synchronize()
+        if rank == 0:
+            gathered_ok = True
+            for r in range(world):
+                xr, lr = sharding.shard_batch(x, lens, r, world)
+                yr = enc.forward(xr.cuda(), lr.cuda())
+                enc.status()
+                gathered_ok = gathered_ok and bool(torch.equal(yr.reshape(per, SEQ, HIDDEN), full[r * per:(r + 1) * per]))
         t = torch.tensor([ms, ms_e2e], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, ms_e2e = t[0].item(), t[1].item()
@@ -297,8 +318,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     peaks = measured_peaks()
     flops_step_gpu = layer_flops(per) * LAYERS
     achieved = flops_step_gpu / (ms * 1e-3) / 1e12
-    lat = {}
-    cpu = None
+    lat, stages, cpu = {}, {}, None
     if world == 1:
         lat = {"bert_layer_b1_s128": latency_us(bert, so, 1), "bert_12layer_b1_s128": latency_us(bert, so, 12, 50)}
         hbm_floor_us = (layer_weight_bytes() + 2 * SEQ * HIDDEN * 2) / (peaks["hbm"] * 1e9) * 1e6
@@ -306,22 +326,25 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         lat["hbm_floor_layer_us"] = hbm_floor_us
         lat["hbm_frac_layer_cold_l2"] = hbm_floor_us / lat["bert_layer_b1_s128_cold_l2"]
         lat["hbm_frac_12layer"] = 12 * hbm_floor_us / lat["bert_12layer_b1_s128"]
-        n_seq = 4
-        v, dt, cores = cpu_sample(n_seq, 2, 1)
+        mhz = float(clocks.get("sm_max_mhz") or 1965.0)         # short launches run at the maximum clock
+        stages = {"clock_mhz": mhz, "layer_b1_s128": stage_profile(bert, so, 1, mhz),
+                  "layer_b64_s128": stage_profile(bert, so, BATCH, mhz)}
+        n_seq = BATCH
+        v, dt, cores = cpu_sample(n_seq, 3, 1)
         cpu = {"value": v, "unit": "sequences/s", "cores": cores, "kind": "port",
                "sample": f"{n_seq} of the {BATCH} sequences, 12 layers, fp32 torch-CPU oracle, {dt:.2f} s per pass"}
     out = {
         "metric": METRIC, "value": BATCH / (ms * 1e-3), "unit": "sequences/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f16 (fp32 accumulate)", "data": "synthetic",
-        "config": {"workload": "BERT-base 12-layer encoder, batch 64 (sharded by sequence), seq 128, lengths U[32,128]",
+        "config": {"workload": WORKLOAD,
                    "sequences_per_gpu": per, "parallelism": f"replicas x{world}, output all-gather" if world > 1 else "single GPU",
                    "l2": "no flush: 170 MB of weights per step exceed the 126 MB L2", "grid": info["grid"],
                    "stages_per_launch": info["stages"],
                    "tiles": "timed at plan creation (desc.autotune): " + ", ".join(
                        "%dx%d/%d" % (t["bm"], t["bn"], t["splitk"]) for t in (enc.stage_info(i) for i in (0, 2, 4, 5))),
-                   "e2e": ("pinned host in/out per step; steps pipelined over copy-in, compute and copy-out streams"
-                           if world == 1 else "pinned host shard in, all-gather on the device, every rank reads its slice of the gathered result back; steps pipelined over three streams")},
+                   "e2e": ("souffle_bert_forward_host_async: pinned host in/out per step; steps pipelined over copy-in, compute and copy-out streams"
+                           if world == 1 else "sharding.ShardedHostPipeline: pinned host shard in, all-gather on the device, every rank reads its slice of the gathered result back; steps pipelined over three streams")},
         "e2e": {"value": BATCH / (ms_e2e * 1e-3), "unit": "sequences/s",
                 "h2d_bytes_per_step": int((xs.numel() * 2 + ls.numel() * 4) * world),      # whole job: all ranks' shards
                 "d2h_bytes_per_step": int(BATCH * SEQ * HIDDEN * 2)},
@@ -329,37 +352,18 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
                      "frac": achieved / peaks["tflops"], "frac_of_sustained_peak": achieved / peaks["tflops_sustained"],
                      "peak_source": peaks["src"] + " (cuBLAS bf16 burst)",
-                     # dram__bytes_read.sum + dram__bytes_write.sum of one 64-sequence, 12-layer launch from a one-pass ncu
-                     # capture (profiles/megakernel_bert_b64_bench_launches.md); not captured for the smaller per-GPU shards
-                     "traffic": DRAM_BYTES_PER_LAUNCH_B64 if per == BATCH else None,
+                     "traffic": DRAM_BYTES_PER_LAUNCH.get(per),
                      "kernel": "souffle_megakernel", "flops_per_launch": flops_step_gpu},
         "clocks": clocks,
         "latency_us": lat,
     }
+    if stages:
+        out["stages"] = stages
+    if gathered_ok is not None:
+        out["gathered_equals_single_gpu"] = gathered_ok
     if cpu:
         out["cpu_baseline"] = cpu
     emit(json.dumps(out))
-
-
-def profile_case(batch: int, n_layers: int) -> None:
-    """Eight forward calls of one plan, nothing else: the target of `ncu -k regex:souffle_megakernel -s 4 -c 1`."""
-    from oracle import souffle_oracle as so
-    from souffle_models_b200 import bert
-    cfg = so.BertConfig(batch, SEQ, HEADS, HEAD_DIM, FFN, "std")
-    layers = [{k: v.cuda() for k, v in w.items()} for w in so.make_bert_weights(cfg, SEED, n_layers)]
-    x, lens = so.make_bert_input(cfg, SEED, ragged=batch > 1)
-    enc = bert.BertEncoder(batch, SEQ, HEADS, HEAD_DIM, FFN, layers)
-    xs, ls = x.cuda(), (lens.cuda() if lens is not None else None)
-    y = torch.empty_like(xs)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    for i in range(8):
-        if i == 3:
-            e0.record()
-        enc.forward(xs, ls, y)
-    e1.record()
-    e1.synchronize()
-    enc.status()
-    print(f"batch {batch}, {n_layers} layers: {e0.elapsed_time(e1) * 1000 / 5:.1f} us per call")
 
 
 def main():
@@ -368,12 +372,7 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--profile-case", nargs=2, type=int, metavar=("BATCH", "LAYERS"), default=None,
-                    help="build a plan for BATCH sequences x LAYERS layers and call forward 8 times (for ncu captures)")
     args = ap.parse_args()
-    if args.profile_case:
-        profile_case(*args.profile_case)
-        return
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

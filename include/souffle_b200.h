@@ -216,6 +216,11 @@ int souffle_lstm_launch_mode(void);
  * streams, or different host threads) would race on it -- serialise them. */
 int souffle_lstm_forward_static(const SouffleLstmDesc* desc, const void* w_in, const void* w_state, const float* bias,
                                 const float* x, float* y, int32_t* device_status, souffle_stream_t stream);
+/* Has no counterpart in the reference.  For callers of souffle_lstm_forward_static that passed no
+ * `device_status`: waits until `stream` is idle, then reads the status words the last such call on the current
+ * device left in the built-in array (one device-to-host copy, no allocation) and returns SOUFFLE_OK or
+ * SOUFFLE_DEVICE_TIMEOUT.  A call that did pass `device_status` reports there, not here. */
+int souffle_lstm_static_status(souffle_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
  * Plain fp16 GEMM with fp32 accumulation: c[M][N] = a[M][K] . w[K][N].
@@ -223,8 +228,10 @@ int souffle_lstm_forward_static(const SouffleLstmDesc* desc, const void* w_in, c
  * and swin_trans_fc2 (swin_trans_fc2_binding.cu:19-55) for any K % 64 == 0, N % 64 == 0.
  * `workspace` must hold souffle_gemm_workspace_bytes() bytes and is reusable across calls
  * that do not overlap.  The library clears it the first time it sees the address and keeps the barrier words
- * consistent from call to call; nobody else may write its first 128 bytes in between (a workspace that was
- * handed out again with other contents costs one call that ends in SOUFFLE_DEVICE_TIMEOUT).
+ * consistent from call to call; nobody else may write its first 128 bytes in between.  A caller that frees a
+ * workspace, or hands its memory to another use, tells the library with souffle_workspace_forget() before the
+ * address can come back with other contents: barrier words the library believes consistent but that were
+ * overwritten make the next call's result undefined (the barriers may pass at once), not merely a timeout.
  * ------------------------------------------------------------------------------------------ */
 size_t souffle_gemm_workspace_bytes(void);
 int souffle_gemm_f16(const void* a, const void* w_kn, void* c, int32_t M, int32_t N, int32_t K,
@@ -313,6 +320,9 @@ int souffle_se_module_forward(const float* input, const float* w_reduce, const f
 
 /* Blocks until `stream` is idle, then decodes the status words in `workspace`. */
 int souffle_workspace_status(void* workspace, souffle_stream_t stream);
+/* Drops what the library remembers about a caller-owned workspace address (to be called before the memory is
+ * freed or re-used for something else); the next call that is given the address clears it again. */
+int souffle_workspace_forget(void* workspace);
 
 #ifdef __cplusplus
 }

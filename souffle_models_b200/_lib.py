@@ -74,6 +74,8 @@ SIGNATURES = {
     "souffle_lstm_launch_mode": (C.c_int, []),
     "souffle_lstm_forward_static": (C.c_int, [C.POINTER(LstmDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                               C.c_void_p, C.c_void_p, C.c_void_p]),
+    "souffle_lstm_static_status": (C.c_int, [C.c_void_p]),
+    "souffle_workspace_forget": (C.c_int, [C.c_void_p]),
     "souffle_gemm_workspace_bytes": (C.c_size_t, []),
     "souffle_gemm_f16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
                                    C.c_void_p, C.c_size_t, C.c_void_p]),

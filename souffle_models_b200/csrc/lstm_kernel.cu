@@ -14,6 +14,8 @@
 // the eight CTAs of its cluster (distributed shared memory, st.async: the store itself counts as a
 // transfer on the receiver's mbarrier, no fence on either side) -- no trip through L2.  Only the hop to
 // the next layer goes through global memory: one slot per (layer, step) and per-layer arrival counters.
+// Every CTA of a layer publishes its own count of finished steps; the consumer checks all eight, so a CTA whose
+// publication lags cannot be covered by its peers running ahead.
 // Two more warps keep that hop off the cell arithmetic's path: a fetch warp brings the layer's input
 // vectors into shared memory up to four steps ahead, and a publish warp pays for the release fence
 // behind the hidden states the cell warps have stored.
@@ -35,6 +37,9 @@ constexpr int kLstmParts = 8;                      // CTAs per layer = cluster s
 constexpr int kLstmMaxHidden = 256;
 constexpr int kLstmXBufs = 4;                      // input vectors the fetch warp may run ahead
 constexpr int kLstmRegChunks = 3;                  // of a thread's (up to 4) weight chunks per gate row, those kept in registers
+constexpr int kLstmMaxLayers = 18;
+constexpr int kLstmDoneWords = 256;                // one set of published-step counters: kLstmMaxLayers * kLstmParts, rounded up
+static_assert(kLstmMaxLayers * kLstmParts <= kLstmDoneWords, "counter block too small");
 
 struct LstmParams {
   const __half* w_in;     // [4*L][H][H], row = output unit, col = input
@@ -43,8 +48,8 @@ struct LstmParams {
   const float* x;         // [T][H]
   float* y;               // [T][H]: top layer's h per step
   float* h_all;           // [L][T][H] scratch: every published hidden state
-  unsigned* done;         // [L] arrival counters of this launch
-  unsigned* done_next;    // [L] counters the next launch will use (cleared here)
+  unsigned* done;         // [L][kLstmParts] published-step counters of this launch, one per (layer, CTA of its cluster)
+  unsigned* done_next;    // the counters the next launch will use (cleared here)
   int* status;
   int layers, hidden, steps, ref_input_delay;
   unsigned long long timeout_ns;
@@ -53,20 +58,6 @@ struct LstmParams {
 // ex2-based forms: absolute error of a few 1e-7 on values in [-1, 1], far inside the 5e-3 bar on hidden states
 __device__ __forceinline__ float sigmoid_f(float v) { return __fdividef(1.0f, 1.0f + __expf(-v)); }
 __device__ __forceinline__ float tanh_f(float v) { return 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * v)); }
-
-__device__ __forceinline__ bool wait_count(const unsigned* ctr, unsigned target, const WaitCtl& c, int where) {
-  uint32_t spins = 0;
-  while (ld_acquire_u32(ctr) < target) {
-    if (((++spins) & 0x3F) == 0) {
-      if (*c.abort_smem) return false;
-      if (globaltimer_ns() > c.deadline_ns) {
-        record_timeout(c, DEV_TIMEOUT_FLAG, where);
-        return false;
-      }
-    }
-  }
-  return true;
-}
 
 // Bounded wait on an mbarrier whose arrivals come from other CTAs of the cluster.
 __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, const WaitCtl& c, int where) {
@@ -91,10 +82,11 @@ __host__ __device__ inline int lstm_vec_index(int e, int H) { return ((e >> 3) <
 // Shared memory of a CTA, in this order: weights [rows = 4*U][2H halves, 64-byte pad per row] (only the chunks the
 // cell threads do not keep in registers are read from it); input vectors
 // [kLstmXBufs][H] fp32; hidden vectors [2][H] fp32 (written by the whole cluster); gate pre-activations
-// [2][rows] fp32; mbarriers xfull[kLstmXBufs], xempty[kLstmXBufs], hfull[2]; abort, verdict and produced words.
+// [2][rows] fp32; mbarriers xfull[kLstmXBufs], xempty[kLstmXBufs], hfull[2]; abort, verdict (two, by step parity)
+// and produced words.
 __host__ __device__ inline size_t lstm_smem_bytes(int H) {
   const int rows = 4 * (H / kLstmParts);
-  return (kLstmRegChunks < 4 ? (size_t)rows * (2 * H * 2 + 64) : 0) + (size_t)(kLstmXBufs * H + 2 * H + 2 * rows) * 4 + (2 * kLstmXBufs + 2) * 8 + 16;
+  return (kLstmRegChunks < 4 ? (size_t)rows * (2 * H * 2 + 64) : 0) + (size_t)(kLstmXBufs * H + 2 * H + 2 * rows) * 4 + (2 * kLstmXBufs + 2) * 8 + 32;
 }
 
 __global__ void __launch_bounds__(kLstmBlock, 1) souffle_lstm_wavefront(const LstmParams p) {
@@ -109,7 +101,9 @@ __global__ void __launch_bounds__(kLstmBlock, 1) souffle_lstm_wavefront(const Ls
   float* g_s = h_s + 2 * H;                                                   // [2][rows]
   uint64_t* bars = reinterpret_cast<uint64_t*>(g_s + 2 * rows);
   int* abort_s = reinterpret_cast<int*>(bars + 2 * kLstmXBufs + 2);
-  int* verdict_s = abort_s + 1;
+  // verdict of step t lives in slot t & 1: thread 0 can only write step t+2's after everyone has read step t's
+  // (it has to pass the barrier of step t+1 first), so all threads leave the loop at the same iteration
+  volatile int* verdict_s = abort_s + 4;
   const uint32_t produced_a = smem_u32(abort_s + 2);       // steps whose hidden states this CTA has stored to global memory
   const uint32_t xfull0 = smem_u32(bars), xempty0 = smem_u32(bars + kLstmXBufs), hfull0 = smem_u32(bars + 2 * kLstmXBufs);
   const int layer = blockIdx.x / kLstmParts;
@@ -118,7 +112,8 @@ __global__ void __launch_bounds__(kLstmBlock, 1) souffle_lstm_wavefront(const Ls
 
   if (tid == 0) {
     *abort_s = 0;
-    *verdict_s = 1;
+    verdict_s[0] = 1;
+    verdict_s[1] = 1;
     abort_s[2] = 0;
     for (int i = 0; i < kLstmXBufs; ++i) {
       mbar_init(xfull0 + 8 * i, 32);            // the 32 lanes of the fetch warp
@@ -130,7 +125,8 @@ __global__ void __launch_bounds__(kLstmBlock, 1) souffle_lstm_wavefront(const Ls
     }
     fence_mbar_init();
   }
-  if (blockIdx.x == 0 && tid < L) p.done_next[tid] = 0u;
+  if (blockIdx.x == 0)
+    for (int i = tid; i < L * kLstmParts; i += kLstmBlock) p.done_next[i] = 0u;
   for (int i = tid; i < 2 * H; i += kLstmBlock) h_s[i] = 0.0f;               // h before the first step
   // ---- weights -> shared memory (once), unless the cell threads keep all of them in registers ----
   if (kLstmRegChunks < 4) {
@@ -159,7 +155,7 @@ __global__ void __launch_bounds__(kLstmBlock, 1) souffle_lstm_wavefront(const Ls
       while (published < (uint32_t)T) {
         const uint32_t n = ld_acquire_cta_shared_u32(produced_a) / (uint32_t)U;     // whole steps only
         if (n > published) {
-          red_add_release_u32(p.done + layer, n - published);
+          st_release_u32(p.done + layer * kLstmParts + part, n);      // this CTA's units of steps < n are in h_all
           published = n;
         } else if (((++spins) & 0xFF) == 0) {
           if (*ctl.abort_smem) break;
@@ -177,13 +173,38 @@ __global__ void __launch_bounds__(kLstmBlock, 1) souffle_lstm_wavefront(const Ls
     for (int t = 0; t < T; ++t) {
       const int xb = t % kLstmXBufs, use = t / kLstmXBufs;
       int ok = 1;
-      if (lane == 0) {
-        if (use > 0) ok = mbar_wait(xempty0 + 8 * xb, (uint32_t)(use - 1) & 1u, ctl, 900) ? 1 : 0;
-        if (ok && layer > 0) ok = wait_count(p.done + layer - 1, (unsigned)kLstmParts * (t + 1), ctl, 700 + layer) ? 1 : 0;
-        if (!ok) *abort_s = 1;
-      }
+      if (lane == 0 && use > 0) ok = mbar_wait(xempty0 + 8 * xb, (uint32_t)(use - 1) & 1u, ctl, 900) ? 1 : 0;
       ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) break;
+      if (ok && layer > 0) {
+        // lane k < 8 waits until CTA k of the layer below has published step t; the warp-wide vote (which also orders
+        // the other lanes' loads behind these acquires) says when all eight have
+        const unsigned* ctr = p.done + (layer - 1) * kLstmParts + (lane & (kLstmParts - 1));
+        bool mine = lane >= kLstmParts;
+        uint32_t spins = 0;
+        for (;;) {
+          if (!mine) mine = ld_acquire_u32(ctr) >= (unsigned)(t + 1);
+          if (__all_sync(0xffffffffu, mine)) break;
+          if (((++spins) & 0x3F) == 0) {
+            int give_up = 0;
+            if (lane == 0) {
+              if (*ctl.abort_smem) {
+                give_up = 1;
+              } else if (globaltimer_ns() > ctl.deadline_ns) {
+                record_timeout(ctl, DEV_TIMEOUT_FLAG, 700 + layer);
+                give_up = 1;
+              }
+            }
+            if (__shfl_sync(0xffffffffu, give_up, 0)) {
+              ok = 0;
+              break;
+            }
+          }
+        }
+      }
+      if (!ok) {
+        if (lane == 0) *abort_s = 1;
+        break;
+      }
       const float* src = nullptr;
       if (layer == 0) {
         const int tx = p.ref_input_delay ? t - 1 : t;
@@ -237,13 +258,11 @@ __global__ void __launch_bounds__(kLstmBlock, 1) souffle_lstm_wavefront(const Ls
             // that barrier's next phase receives h(t+1); nobody sends it before having this CTA's h(t)
             if (ok && t + 1 < T) mbar_expect_tx(hfull0 + 8 * (hb ^ 1), (uint32_t)H * 4u);
           }
-          if (!ok) {
-            *abort_s = 1;
-            *verdict_s = 0;
-          }
+          if (!ok) *abort_s = 1;
+          verdict_s[t & 1] = ok ? 1 : 0;
         }
         named_barrier_sync(1, n_act);
-        if (*verdict_s == 0) break;
+        if (verdict_s[t & 1] == 0) break;
         // ---- gate pre-activations: fp16 weights x fp32 vector, fp32 accumulate ----
         const float* xv = x_s + xb * H;
         const float* hv = h_s + (hb ^ 1) * H;

@@ -55,7 +55,6 @@ struct MegaParams {
   unsigned* sync_next;  // the pair the next launch will use; cleared by this launch
   int* status;        // [0] code, [1] where, [2] cta
   unsigned long long timeout_ns;
-  int dbg_flags;      // experiment knob: 1 = epilogue does not store, 2 = epilogue does not read TMEM either
   int max_slots;      // experiment knob: cap on operand ring slots, 0 = as many as fit
   int skip_arrival;   // test hook: CTA (skip_arrival-1) leaves at barrier 0 without arriving; 0 = off
   long long* prof;    // optional [n_stages][grid][8]: clock64 at stage start, work done, barrier left, then GEMM
@@ -553,15 +552,14 @@ __device__ __forceinline__ void gemm_stage(const Stage& st, const CallArgs& ca, 
         }
         tc_fence_after_sync();
         const int row0 = mt * g.bm + h * 128 + q * 32;
-        const bool nostore = (p.dbg_flags & 1) != 0;
-        const uint32_t own = nostore ? kNoRow : epi_row_offset<kSwin>(st, e, row0 + lane, ks);
+        const uint32_t own = epi_row_offset<kSwin>(st, e, row0 + lane, ks);
         uint32_t so[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) so[i] = nostore ? kNoRow : epi_row_offset<kSwin>(st, e, row0 + 8 * i + (lane >> 2), ks);
+        for (int i = 0; i < 4; ++i) so[i] = epi_row_offset<kSwin>(st, e, row0 + 8 * i + (lane >> 2), ks);
         const uint32_t t0 = tmem + acc * kAccStride;
         const int colbase = nt * g.bn;
         // this warp takes chunks cpar, cpar+2, ... (its partner warp on the same lane quarter the others)
-        for (int c = (p.dbg_flags & 2) ? full_chunks : cpar; c < full_chunks; c += 2) {
+        for (int c = cpar; c < full_chunks; c += 2) {
           uint32_t r[32];
           const unsigned tl = prof ? (unsigned)clock64() : 0u;
           tmem_ld32(t0 + c * 32, r);

@@ -645,7 +645,7 @@ static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* la
   // one attention item per CTA at most, or a long sequence: the stage in which all softmax warps share an item
   p->family = (d.seq > 128 || d.batch * d.heads <= p->grid) ? kFamilyBertCoop : kFamilyBert;
   for (Stage& fs : p->stages)
-    if ((rc = finalize_stage(fs, p->desc.debug_max_slots & 0xFF, p->grid))) return rc;
+    if ((rc = finalize_stage(fs, p->desc.debug_max_slots, p->grid))) return rc;
   if ((rc = plan_alloc(p, (void**)&p->d_stages, p->stages.size() * sizeof(Stage)))) return rc;
   if ((rc = plan_alloc(p, (void**)&p->d_maps, p->maps.size() * sizeof(CUtensorMap)))) return rc;
   SF_CUDA(cudaMemcpy(p->d_stages, p->stages.data(), p->stages.size() * sizeof(Stage), cudaMemcpyHostToDevice));
@@ -738,8 +738,7 @@ int souffle_bert_forward(SouffleBertPlan* plan, const void* x, const int32_t* se
   mp.timeout_ns = (unsigned long long)(d.timeout_ms > 0 ? d.timeout_ms : 2000) * 1000000ull;
   mp.prof = plan->d_prof;
   mp.skip_arrival = d.debug_skip_arrival;
-  mp.max_slots = d.debug_max_slots & 0xFF;
-  mp.dbg_flags = d.debug_max_slots >> 8;
+  mp.max_slots = d.debug_max_slots;
   int rc = launch_mega(args, plan->grid, reinterpret_cast<cudaStream_t>(stream), plan->family);
   if (rc) return rc;
   plan->launch_id++;
@@ -1098,7 +1097,7 @@ static int finish_plan(SouffleBertPlan* p, int sms) {
   }
   p->grid = max_items < sms ? max_items : sms;
   for (Stage& fs : p->stages)
-    if ((rc = finalize_stage(fs, p->desc.debug_max_slots & 0xFF, p->grid))) return rc;
+    if ((rc = finalize_stage(fs, p->desc.debug_max_slots, p->grid))) return rc;
   if ((rc = plan_alloc(p, (void**)&p->d_stages, p->stages.size() * sizeof(Stage)))) return rc;
   if ((rc = plan_alloc(p, (void**)&p->d_maps, p->maps.size() * sizeof(CUtensorMap)))) return rc;
   SF_CUDA(cudaMemcpy(p->d_stages, p->stages.data(), p->stages.size() * sizeof(Stage), cudaMemcpyHostToDevice));
@@ -1380,7 +1379,7 @@ struct SouffleLstmPlan {
   SouffleLstmDesc desc;
   __half *w_in = nullptr, *w_state = nullptr;
   float *bias = nullptr, *h_all = nullptr;
-  unsigned* done = nullptr;   // two sets of [32] counters
+  unsigned* done = nullptr;   // two sets of kLstmDoneWords counters, used by alternate launches
   int* status = nullptr;
   unsigned launch_id = 0;
   size_t smem = 0;
@@ -1391,7 +1390,7 @@ int souffle_lstm_plan_create(const SouffleLstmDesc* desc, const void* w_in, cons
   if (!desc || !plan_out) return fail(SOUFFLE_BAD_ARGUMENT, "null argument");
   *plan_out = nullptr;
   const SouffleLstmDesc& d = *desc;
-  if (d.layers < 1 || d.layers > 18) return fail(SOUFFLE_BAD_SHAPE, "layers must be in 1..18 (got %d)", d.layers);
+  if (d.layers < 1 || d.layers > kLstmMaxLayers) return fail(SOUFFLE_BAD_SHAPE, "layers must be in 1..%d (got %d)", kLstmMaxLayers, d.layers);
   if (d.hidden != 64 && d.hidden != 128 && d.hidden != 256)
     return fail(SOUFFLE_BAD_SHAPE, "hidden must be 64, 128 or 256 (got %d)", d.hidden);
   if (d.steps < 1) return fail(SOUFFLE_BAD_SHAPE, "steps must be >= 1");
@@ -1414,13 +1413,13 @@ int souffle_lstm_plan_create(const SouffleLstmDesc* desc, const void* w_in, cons
   if (e == cudaSuccess) e = cudaMalloc((void**)&p->w_in, wbytes);
   if (e == cudaSuccess) e = cudaMalloc((void**)&p->w_state, wbytes);
   if (e == cudaSuccess) e = cudaMalloc((void**)&p->h_all, (size_t)d.layers * d.steps * H * 4);
-  if (e == cudaSuccess) e = cudaMalloc((void**)&p->done, 256);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&p->done, 2 * kLstmDoneWords * sizeof(unsigned));
   if (e == cudaSuccess) e = cudaMalloc((void**)&p->status, 64);
   if (e == cudaSuccess && bias) e = cudaMalloc((void**)&p->bias, (size_t)d.layers * H * 4);
   if (e == cudaSuccess) e = cudaMemcpy(p->w_in, w_in, wbytes, cudaMemcpyDeviceToDevice);
   if (e == cudaSuccess) e = cudaMemcpy(p->w_state, w_state, wbytes, cudaMemcpyDeviceToDevice);
   if (e == cudaSuccess && bias) e = cudaMemcpy(p->bias, bias, (size_t)d.layers * H * 4, cudaMemcpyDeviceToDevice);
-  if (e == cudaSuccess) e = cudaMemset(p->done, 0, 256);
+  if (e == cudaSuccess) e = cudaMemset(p->done, 0, 2 * kLstmDoneWords * sizeof(unsigned));
   if (e == cudaSuccess) e = cudaMemset(p->status, 0, 64);
   if (e != cudaSuccess) {
     souffle_lstm_plan_destroy(p);
@@ -1445,8 +1444,8 @@ int souffle_lstm_forward(SouffleLstmPlan* plan, const float* x, float* y, souffl
   LstmParams lp;
   lp.w_in = plan->w_in; lp.w_state = plan->w_state; lp.bias = plan->bias; lp.x = x; lp.y = y; lp.h_all = plan->h_all;
   const unsigned par = plan->launch_id & 1u;
-  lp.done = plan->done + 32 * par;
-  lp.done_next = plan->done + 32 * (par ^ 1u);
+  lp.done = plan->done + kLstmDoneWords * par;
+  lp.done_next = plan->done + kLstmDoneWords * (par ^ 1u);
   lp.status = plan->status;
   lp.layers = d.layers; lp.hidden = d.hidden; lp.steps = d.steps; lp.ref_input_delay = d.ref_input_delay;
   lp.timeout_ns = (unsigned long long)(d.timeout_ms > 0 ? d.timeout_ms : 2000) * 1000000ull;
@@ -1465,18 +1464,41 @@ int souffle_lstm_plan_status(SouffleLstmPlan* plan) {
   SF_CUDA(cudaMemcpy(h, plan->status, sizeof(h), cudaMemcpyDeviceToHost));
   if (h[0] != DEV_OK) {
     cudaMemset(plan->status, 0, 64);
-    cudaMemset(plan->done, 0, 256);
+    cudaMemset(plan->done, 0, 2 * kLstmDoneWords * sizeof(unsigned));
   }
   return decode_status(h, "souffle_lstm_forward");
 }
 
 // Allocation-free variant (see lstm_static.cu).  The first call on a device looks up the scratch
 // array's device address and sets the kernel attributes; make that call before any stream capture.
+static int static_lstm_device(int* dev_out, StaticLstmDevice** sd_out) {
+  int dev = 0;
+  SF_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 16) return fail(SOUFFLE_BAD_DEVICE, "device index %d out of range", dev);
+  StaticLstmDevice& sd = g_static_lstm[dev];
+  std::lock_guard<std::mutex> lock(sd.mutex);             // host threads may race for the first call on a device
+  if (!sd.ready) {
+    int cc = 0;
+    SF_CUDA(cudaDeviceGetAttribute(&cc, cudaDevAttrComputeCapabilityMajor, dev));
+    if (cc != 10) return fail(SOUFFLE_BAD_DEVICE, "device %d is not sm_100", dev);
+    SF_CUDA(cudaDeviceGetAttribute(&sd.sms, cudaDevAttrMultiProcessorCount, dev));
+    void* ptr = nullptr;
+    SF_CUDA(cudaGetSymbolAddress(&ptr, g_lstm_static_scratch));
+    // the largest shared-memory request any shape makes (plans ask for the same limit)
+    SF_CUDA(cudaFuncSetAttribute(souffle_lstm_wavefront, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lstm_smem_bytes(kLstmMaxHidden)));
+    sd.scratch = static_cast<unsigned char*>(ptr);
+    sd.ready = true;
+  }
+  *dev_out = dev;
+  *sd_out = &sd;
+  return SOUFFLE_OK;
+}
+
 int souffle_lstm_forward_static(const SouffleLstmDesc* desc, const void* w_in, const void* w_state, const float* bias,
                                 const float* x, float* y, int32_t* device_status, souffle_stream_t stream) {
   if (!desc) return fail(SOUFFLE_BAD_ARGUMENT, "null descriptor");
   const SouffleLstmDesc& d = *desc;
-  if (d.layers < 1 || d.layers > 18) return fail(SOUFFLE_BAD_SHAPE, "layers must be in 1..18 (got %d)", d.layers);
+  if (d.layers < 1 || d.layers > kLstmMaxLayers) return fail(SOUFFLE_BAD_SHAPE, "layers must be in 1..%d (got %d)", kLstmMaxLayers, d.layers);
   if (d.hidden != 64 && d.hidden != 128 && d.hidden != 256)
     return fail(SOUFFLE_BAD_SHAPE, "hidden must be 64, 128 or 256 (got %d)", d.hidden);
   if (d.steps < 1) return fail(SOUFFLE_BAD_SHAPE, "steps must be >= 1");
@@ -1486,25 +1508,20 @@ int souffle_lstm_forward_static(const SouffleLstmDesc* desc, const void* w_in, c
   if (!aligned16(w_in) || !aligned16(w_state) || !aligned16(x) || !aligned16(y))
     return fail(SOUFFLE_BAD_POINTER, "w_in, w_state, x and y must be non-null and 16-byte aligned");
   int dev = 0;
-  SF_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 16) return fail(SOUFFLE_BAD_DEVICE, "device index %d out of range", dev);
+  StaticLstmDevice* sdp = nullptr;
+  int rc = static_lstm_device(&dev, &sdp);
+  if (rc) return rc;
+  StaticLstmDevice& sd = *sdp;
   const size_t smem = lstm_smem_bytes(d.hidden);
-  StaticLstmDevice& sd = g_static_lstm[dev];
-  if (!sd.ready) {
-    int cc = 0;
-    SF_CUDA(cudaDeviceGetAttribute(&cc, cudaDevAttrComputeCapabilityMajor, dev));
-    if (cc != 10) return fail(SOUFFLE_BAD_DEVICE, "device %d is not sm_100", dev);
-    SF_CUDA(cudaDeviceGetAttribute(&sd.sms, cudaDevAttrMultiProcessorCount, dev));
-    void* ptr = nullptr;
-    SF_CUDA(cudaGetSymbolAddress(&ptr, g_lstm_static_scratch));
-    sd.scratch = static_cast<unsigned char*>(ptr);
-    sd.ready = true;
-  }
-  // allow the largest shared-memory request any shape makes (a plan may have lowered the limit since)
-  SF_CUDA(cudaFuncSetAttribute(souffle_lstm_wavefront, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lstm_smem_bytes(kLstmMaxHidden)));
   {
-    const int rc = lstm_check_resident(d.layers, smem);
-    if (rc) return rc;
+    // all clusters must be resident at once: asked of the driver once per (device, layers, hidden)
+    const int hi = d.hidden == 64 ? 0 : (d.hidden == 128 ? 1 : 2);
+    std::lock_guard<std::mutex> lock(sd.mutex);
+    if (!(sd.resident_ok[hi] & (1u << d.layers))) {
+      rc = lstm_check_resident(d.layers, smem);
+      if (rc) return rc;
+      sd.resident_ok[hi] |= 1u << d.layers;
+    }
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   unsigned char* ctl = sd.scratch + kStaticHiddenFloats * 4;
@@ -1517,11 +1534,24 @@ int souffle_lstm_forward_static(const SouffleLstmDesc* desc, const void* w_in, c
   lp.bias = bias; lp.x = x; lp.y = y;
   lp.h_all = reinterpret_cast<float*>(sd.scratch);
   lp.done = reinterpret_cast<unsigned*>(ctl);
-  lp.done_next = reinterpret_cast<unsigned*>(ctl + 128);
-  lp.status = device_status ? reinterpret_cast<int*>(device_status) : reinterpret_cast<int*>(ctl + 256);
+  lp.done_next = reinterpret_cast<unsigned*>(ctl) + kLstmDoneWords;
+  lp.status = device_status ? reinterpret_cast<int*>(device_status) : reinterpret_cast<int*>(ctl + kStaticStatusOffset);
   lp.layers = d.layers; lp.hidden = d.hidden; lp.steps = d.steps; lp.ref_input_delay = d.ref_input_delay;
   lp.timeout_ns = (unsigned long long)(d.timeout_ms > 0 ? d.timeout_ms : 2000) * 1000000ull;
   return lstm_launch(lp, smem, st);
+}
+
+// For callers that passed no device_status: waits for `stream`, then reads the status words the last
+// allocation-free call on the current device left in the built-in array (a plain device-to-host copy).
+int souffle_lstm_static_status(souffle_stream_t stream) {
+  int dev = 0;
+  StaticLstmDevice* sd = nullptr;
+  int rc = static_lstm_device(&dev, &sd);
+  if (rc) return rc;
+  SF_CUDA(cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(stream)));
+  int h[4] = {0, 0, 0, 0};
+  SF_CUDA(cudaMemcpy(h, sd->scratch + kStaticHiddenFloats * 4 + kStaticStatusOffset, sizeof(h), cudaMemcpyDeviceToHost));
+  return decode_status(h, "souffle_lstm_forward_static");
 }
 
 // ======================================================================================
@@ -1594,6 +1624,13 @@ int souffle_se_module_forward(const float* input, const float* w_reduce, const f
   p.timeout_ns = 2000ull * 1000000ull;
   void* kargs[] = {&p};
   SF_CUDA(cudaLaunchCooperativeKernel((const void*)souffle_se_module, dim3(grid), dim3(kSeThreads), kargs, smem, st));
+  return SOUFFLE_OK;
+}
+
+int souffle_workspace_forget(void* workspace) {
+  if (!workspace) return fail(SOUFFLE_BAD_ARGUMENT, "null workspace");
+  std::lock_guard<std::mutex> lock(g_ws_mutex);
+  g_ws_launches.erase(workspace);
   return SOUFFLE_OK;
 }
 

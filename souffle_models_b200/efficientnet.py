@@ -16,7 +16,11 @@ def _stream_ptr() -> int:
 def _workspace(nbytes: int) -> torch.Tensor:
     dev = torch.cuda.current_device()
     if dev not in _ws or _ws[dev].numel() < nbytes:
+        lib = _lib.load()
+        if dev in _ws:          # the old block goes back to the allocator: the library must not trust its address any more
+            lib.souffle_workspace_forget(_ws[dev].data_ptr())
         _ws[dev] = torch.zeros(int(nbytes), dtype=torch.uint8, device="cuda")
+        lib.souffle_workspace_forget(_ws[dev].data_ptr())      # fresh memory, whatever lived at this address before
     return _ws[dev]
 
 

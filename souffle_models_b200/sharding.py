@@ -41,3 +41,81 @@ def gather_outputs(local: torch.Tensor, out: Optional[torch.Tensor] = None,
         out = torch.empty((local.shape[0] * world,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
     dist.all_gather_into_tensor(out, local.contiguous(), group=group)
     return out
+
+
+class ShardedHostPipeline:
+    """One rank's end-to-end step of the sharded encoder with HOST buffers on both sides:
+
+        pinned shard -> device  |  encoder on the shard  |  all-gather over NVLink  |  this rank's slice of the
+        gathered batch -> host
+
+    Consecutive steps are pipelined over a copy-in stream, the caller's current stream (encoder + gather) and a
+    copy-out stream, with two sets of device buffers, so the copies of one step run under the kernel of its
+    neighbours -- what souffle_bert_forward_host_async does inside the library for the single-GPU case.  Every rank
+    reads back its own 1/world of the gathered result, so the whole batch reaches host memory once per step, spread
+    over the rank processes like the inputs.
+
+    `forward(x_dev, lens_dev, y_dev)` is the rank's encoder (BertEncoder.forward).  With CPU tensors (gloo tests) the
+    same steps run synchronously without streams.
+    """
+
+    def __init__(self, forward, x_like: torch.Tensor, lens_like: Optional[torch.Tensor], rank: int, world: int,
+                 group: Optional[dist.ProcessGroup] = None):
+        self.forward, self.rank, self.world, self.group = forward, rank, world, group
+        self.per = x_like.shape[0]
+        self.cuda = x_like.is_cuda
+        n = 2 if self.cuda else 1
+        self.x = [torch.empty_like(x_like) for _ in range(n)]
+        self.l = [torch.empty_like(lens_like) if lens_like is not None else None for _ in range(n)]
+        self.y = [torch.empty_like(x_like) for _ in range(n)]
+        full_shape = (self.per * world,) + tuple(x_like.shape[1:])
+        self.full = [torch.empty(full_shape, dtype=x_like.dtype, device=x_like.device) for _ in range(n)]
+        self.calls = 0
+        if self.cuda:
+            self.s_in, self.s_out = torch.cuda.Stream(), torch.cuda.Stream()
+            self.ev_k, self.ev_out = [None, None], [None, None]
+
+    def step(self, x_host: torch.Tensor, lens_host: Optional[torch.Tensor], out_host: torch.Tensor) -> torch.Tensor:
+        """Queues one step; `out_host` ([per, ...]) is complete after drain() (or once a later step that reuses the
+        same buffer set has been queued and the current stream has caught up).  Returns the device tensor that will
+        hold the gathered batch of this step."""
+        b = self.calls & 1 if self.cuda else 0
+        self.calls += 1
+        lo, hi = self.rank * self.per, (self.rank + 1) * self.per
+        if not self.cuda:
+            self.x[b].copy_(x_host)
+            if lens_host is not None:
+                self.l[b].copy_(lens_host)
+            self.forward(self.x[b], self.l[b], self.y[b])
+            gather_outputs(self.y[b], self.full[b], self.group) if self.world > 1 else self.full[b].copy_(self.y[b])
+            out_host.copy_(self.full[b][lo:hi])
+            return self.full[b]
+        cur = torch.cuda.current_stream()
+        with torch.cuda.stream(self.s_in):
+            if self.ev_k[b] is not None:
+                self.s_in.wait_event(self.ev_k[b])             # the encoder of the step before last has read x[b]
+            self.x[b].copy_(x_host, non_blocking=True)
+            if lens_host is not None:
+                self.l[b].copy_(lens_host, non_blocking=True)
+            ev_in = self.s_in.record_event()
+        cur.wait_event(ev_in)
+        if self.ev_out[b] is not None:
+            cur.wait_event(self.ev_out[b])                     # full[b] has been copied out
+        self.forward(self.x[b], self.l[b], self.y[b])
+        if self.world > 1:
+            gather_outputs(self.y[b], self.full[b], self.group)
+        else:
+            self.full[b].copy_(self.y[b])
+        self.ev_k[b] = cur.record_event()
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_event(self.ev_k[b])
+            out_host.copy_(self.full[b][lo:hi], non_blocking=True)
+            self.ev_out[b] = self.s_out.record_event()
+        return self.full[b]
+
+    def drain(self) -> None:
+        """Makes the current stream wait for every copy-out queued so far."""
+        if self.cuda:
+            for ev in self.ev_out:
+                if ev is not None:
+                    torch.cuda.current_stream().wait_event(ev)

@@ -10,12 +10,24 @@ from oracle import souffle_oracle as so
 
 pytestmark = pytest.mark.gpu
 
-# fp16 outputs after LayerNorm vs the fp32 golden: max-abs 1e-2 for one layer (the stated bar);
-# twelve chained layers compound the fp16 rounding of the activations handed from layer to layer
-# (1 ulp at |y| ~ 4 is 4e-3), so the stack is held to the reference test's own final-output
-# tolerance of 2e-2 (cpp/bert/test_souffle_bert_layer.py:214) plus an rms bound of 2e-3.
+# fp16 outputs after LayerNorm: max-abs 1e-2 against the fp32 golden for one layer, and for a chain of layers
+# against the oracle that rounds what the CUDA path stores in fp16 (emulate_fp16) -- the stated bar.  Against the
+# un-rounded fp32 golden a chain also carries the fp16 rounding of every activation handed from layer to layer
+# (1 ulp at |y| ~ 4 is 4e-3): that comparison is held to the reference test's own final-output tolerance of 2e-2
+# (cpp/bert/test_souffle_bert_layer.py:214) plus an rms bound of 2e-3, and the measured maxima are reported.
 TOL_LAYER = 1e-2
+TOL_STACK_EMULATED = 1e-2
 TOL_STACK_FP32 = 2e-2
+
+
+def _report(name, value):
+    """Measured parity figures: printed (pytest -s) and appended to $SOUFFLE_PARITY_LOG when that is set."""
+    line = f"{name} = {value:.3e}"
+    print(line)
+    path = os.environ.get("SOUFFLE_PARITY_LOG")
+    if path:
+        with open(path, "a") as f:
+            f.write(line + "\n")
 
 
 def _encoder(cfg, layers, **kw):
@@ -75,9 +87,12 @@ def test_twelve_layer_stack_b1():
     cfg = so.BertConfig(1, 128, 12, 64, 3072, "std")
     enc, layers, x, lens, y = _run(cfg, 1236, n_layers=12)
     want = so.bert_stack(cfg, x, layers, lens)
-    assert _err(y, want) < TOL_STACK_FP32
+    e32, e16 = _err(y, want), _err(y, so.bert_stack(cfg, x, layers, lens, emulate_fp16=True))
+    _report("12 layers, batch 1: max-abs vs fp32 golden", e32)
+    _report("12 layers, batch 1: max-abs vs fp16-storage oracle", e16)
+    assert e16 < TOL_STACK_EMULATED
+    assert e32 < TOL_STACK_FP32
     assert (y - want).pow(2).mean().sqrt() < 2e-3                      # rms error
-    assert _err(y, so.bert_stack(cfg, x, layers, lens, emulate_fp16=True)) < TOL_STACK_FP32
     assert enc.info()["launches"] == 1
 
 
@@ -95,9 +110,9 @@ def test_batched_ragged_stack_and_batch_independence():
         assert (y1 - y.reshape(8, 128, -1)[b]).abs().max() < 4e-3
 
 
-def test_full_size_batch64_properties():
-    """Benchmark config 5 (B=64, 12 layers): finite, unit-variance rows, deterministic, and a
-    sampled sequence agrees with the oracle."""
+def test_full_size_batch64_all_sequences():
+    """Benchmark config 5 (B=64, 12 layers, ragged lengths): every one of the 64 sequences against the oracle
+    (fp32 golden and fp16-storage form), plus finite, unit-variance rows and bit-identical reruns."""
     cfg = so.BertConfig(64, 128, 12, 64, 3072, "std")
     layers = so.make_bert_weights(cfg, 1239, 12)
     x, lens = so.make_bert_input(cfg, 1239, ragged=True)
@@ -110,10 +125,16 @@ def test_full_size_batch64_properties():
     yf = y_a.float().reshape(64 * 128, 768)
     assert torch.isfinite(yf).all()
     assert (yf.mean(-1).abs().max() < 5e-3) and ((yf.var(-1, unbiased=False) - 1).abs().max() < 2e-2)
-    b = 17
-    cfg1 = so.BertConfig(1, 128, 12, 64, 3072, "std")
-    want = so.bert_stack(cfg1, x[b:b + 1], layers, lens[b:b + 1])
-    assert (yf.cpu().reshape(64, 128, 768)[b] - want).abs().max() < TOL_STACK_FP32
+    got = yf.cpu()
+    want = so.bert_stack(cfg, x, layers, lens)
+    per_seq = (got - want).abs().reshape(64, -1).max(dim=1).values
+    e16 = _err(got, so.bert_stack(cfg, x, layers, lens, emulate_fp16=True))
+    _report("12 layers, batch 64: max-abs vs fp32 golden (worst sequence)", per_seq.max().item())
+    _report("12 layers, batch 64: max-abs vs fp32 golden (median sequence)", per_seq.median().item())
+    _report("12 layers, batch 64: max-abs vs fp16-storage oracle", e16)
+    assert e16 < TOL_STACK_EMULATED
+    assert per_seq.max() < TOL_STACK_FP32
+    assert (got - want).pow(2).mean().sqrt() < 2e-3
 
 
 def test_tile_overrides_agree():

@@ -152,6 +152,27 @@ def test_se_module_hand_computed():
     assert torch.allclose(out[0, 0], x[0, 0] + g0, atol=1e-6) and torch.allclose(out[0, 1], x[0, 1] + g1, atol=1e-6)
 
 
+def test_se_module_matches_reference_cuda_kernel(golden_dir):
+    """Oracle vs outputs of the reference's own fused squeeze-and-excite kernel run on a B200
+    (tests/golden/make_ref_se_golden.py; efficientnet_se_module_v2_short_cut_fused, fp32 throughout): the four
+    shapes of its dispatch table that run one channel per block."""
+    import importlib.util
+    import os
+    spec = importlib.util.spec_from_file_location("make_ref_se_golden", os.path.join(golden_dir, "make_ref_se_golden.py"))
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    g = np.load(f"{golden_dir}/ref_cuda_se.npz")
+    for h, c, r in gen.SHAPES:
+        x, wr, we = gen.se_case(h, c, r)
+        pooled, out = so.se_module(x, wr, we)
+        key = f"se_{h}_{c}_{r}"
+        assert (pooled[0] - _t(g[key + "_pooled"])).abs().max() < 1e-5, key
+        head = torch.stack([out[0, 0], out[0, 1], out[0, c - 1]])
+        assert (head - _t(g[key + "_out_head"])).abs().max() < 2e-5, key
+        s, sa = g[key + "_out_sum"]
+        assert abs(sa - out.double().abs().sum().item()) / sa < 1e-5, key
+
+
 def test_patch_merging_gathers_the_four_neighbours():
     """Channel block q of merged token (h, w) is input token (2h + q % 2, 2w + q // 2)
     (python/models/swin_transformer/swin_patch_merge.py:39-44); with an identity-like reduction and no affine the

@@ -29,7 +29,15 @@ def _worker(rank, world, port, ret):
         assert xs.shape[0] == 8 // world and torch.equal(ls, lens[rank * 4:(rank + 1) * 4])
         y_local = xs * 2 + 1                      # stands in for the per-rank encoder
         full = sharding.gather_outputs(y_local)
-        ret[rank] = bool(torch.equal(full, x * 2 + 1))
+        ok = bool(torch.equal(full, x * 2 + 1))
+        # the host-buffer pipeline (synchronous on CPU): shard in, "encoder", gather, this rank's slice back out
+        pipe = sharding.ShardedHostPipeline(lambda xd, ld, yd: yd.copy_(xd * 2 + 1), xs, ls, rank, world)
+        out = torch.empty_like(xs)
+        for _ in range(3):
+            gathered = pipe.step(xs, ls, out)
+        pipe.drain()
+        ok = ok and bool(torch.equal(gathered, x * 2 + 1)) and bool(torch.equal(out, xs * 2 + 1))
+        ret[rank] = ok
     finally:
         dist.destroy_process_group()
 
