@@ -83,10 +83,11 @@ struct __align__(8) SmemCtl {
   uint64_t qk_full, qk_empty, v_full, v_empty, s_full, p_full, o_full;   // attention, pipeline 0
   uint64_t attn1[7];                                                     // attention, pipeline 1 (same order)
   uint64_t ln_full[4], ln_empty[4];
+  uint64_t rec_full;                // the next stage's record has landed (bulk copy issued inside the grid barrier)
   uint32_t tmem_base;
   int abort;
   unsigned long long deadline_ns;   // read from the global timer once per CTA
-  Stage stage;        // current stage, copied once per stage
+  alignas(16) Stage stage;   // current stage; plan-owned programs fetch the next record while the CTA waits at the barrier
 };
 static_assert(sizeof(SmemCtl) <= kCtlBytes, "control block too large");
 
@@ -101,6 +102,15 @@ struct RoleState {
   uint32_t ln_bits = 0;    // phase bit per LayerNorm batch buffer
 };
 
+// SM clock for the stage-level stamps of the in-kernel profile.  The memory clobber keeps the read where it is
+// written: a plain clock64() may be scheduled above a preceding barrier, which charges a stage's work to the wait
+// that follows it.
+__device__ __forceinline__ long long clock_now() {
+  long long t;
+  asm volatile("mov.u64 %0, %%clock64;" : "=l"(t) :: "memory");
+  return t;
+}
+
 __device__ __forceinline__ const void* sel_ptr(int sel, const void* plan, const MegaParams& p) {
   return sel == PTR_CALL_X ? p.x : (sel == PTR_CALL_Y ? (const void*)p.y : plan);
 }
@@ -108,19 +118,26 @@ __device__ __forceinline__ const void* sel_ptr(int sel, const void* plan, const 
 // ------------------------------------------------------------------------------------
 // grid barrier: one monotonic arrival counter per launch, bounded spin
 // ------------------------------------------------------------------------------------
-__device__ bool grid_barrier(const MegaParams& p, const WaitCtl& ctl, int where) {
+__device__ bool grid_barrier(const MegaParams& p, const WaitCtl& ctl, int where, SmemCtl& cs) {
   // The CTA barrier orders every thread's global writes before thread 0, whose gpu-scope release is
   // cumulative and publishes them to the other CTAs.  On the way out thread 0's acquire, the second CTA
   // barrier and a proxy fence order the other CTAs' writes before this CTA's TMA and bulk-copy reads.
   __syncthreads();
   if (threadIdx.x == 0) {
-    if (p.prof) p.prof[((size_t)where * gridDim.x + blockIdx.x) * kProfSlots + 1] = clock64();
+    if (p.prof) p.prof[((size_t)where * gridDim.x + blockIdx.x) * kProfSlots + 1] = clock_now();
     // The counter only grows during a launch: barrier number `where` is passed once every CTA
     // has added 1 for it.  (The launch that runs next clears the other counter, see the prologue.)
     unsigned* count = p.sync;
     const unsigned target = (unsigned)(where + 1) * gridDim.x;
     const bool skip = p.skip_arrival > 0 && where == 0 && (int)blockIdx.x == p.skip_arrival - 1;
     if (skip) *ctl.abort_smem = 1; else red_add_release_u32(count, 1u);
+    // Nobody reads the current stage record any more (the CTA barrier above): the next one is fetched by a bulk
+    // copy while this thread waits for the other CTAs, so its round trip to L2 costs the stage nothing.
+    const bool fetch = p.stages != nullptr;
+    if (fetch) {
+      mbar_expect_tx(smem_u32(&cs.rec_full), (uint32_t)sizeof(Stage));
+      bulk_load(smem_u32(&cs.stage), p.stages + where + 1, (uint32_t)sizeof(Stage), smem_u32(&cs.rec_full));
+    }
     uint32_t spins = 0;
     while (!skip && ld_acquire_u32(count) < target) {
       if (((++spins) & 0x3F) == 0) {
@@ -131,6 +148,7 @@ __device__ bool grid_barrier(const MegaParams& p, const WaitCtl& ctl, int where)
         }
       }
     }
+    if (fetch) mbar_wait(smem_u32(&cs.rec_full), (uint32_t)where & 1u, ctl, 50);
   }
   __syncthreads();
   fence_proxy_async();
@@ -1471,9 +1489,98 @@ __device__ __noinline__ void ln_row_wide(const __half* row, const __half* gamma,
   }
 }
 
+// One row of the direct form: the lanes of a warp read the row straight from L2.  Every round trip costs ~800 cycles,
+// so the loads are issued in as few dependent rounds as the registers allow: bias, residual and the first planes
+// together, further planes kG at a time, gamma and beta just before the statistics (they land while the shuffles run).
+// With the loads strung one behind the other a row of six planes took 6.2 k cycles.
+template <int NJ>
+__device__ __forceinline__ void ln_row_direct(const float* pl, int n_partial, int plane_stride, const __half* res,
+                                              const __half* bias, const __half* gamma, const __half* beta, float eps,
+                                              __half* out, int lane) {
+  constexpr int kG = NJ <= 4 ? 4 : (NJ <= 6 ? 3 : 2);      // planes in flight at once
+  float z[NJ][4];
+  {
+    uint2 ub[NJ], ur[NJ];
+    float4 v[kG][NJ];
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+      ub[j] = bias ? __ldg(reinterpret_cast<const uint2*>(bias + (lane + 32 * j) * 4)) : make_uint2(0u, 0u);
+      ur[j] = res ? __ldcg(reinterpret_cast<const uint2*>(res + (lane + 32 * j) * 4)) : make_uint2(0u, 0u);
+    }
+#pragma unroll
+    for (int g = 0; g < kG; ++g)
+#pragma unroll
+      for (int j = 0; j < NJ; ++j)
+        v[g][j] = g < n_partial ? __ldcg(reinterpret_cast<const float4*>(pl + (size_t)g * plane_stride + (lane + 32 * j) * 4))
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+      const float2 b0 = __half22float2(*reinterpret_cast<const __half2*>(&ub[j].x)), b1 = __half22float2(*reinterpret_cast<const __half2*>(&ub[j].y));
+      const float2 r0 = __half22float2(*reinterpret_cast<const __half2*>(&ur[j].x)), r1 = __half22float2(*reinterpret_cast<const __half2*>(&ur[j].y));
+      z[j][0] = b0.x + r0.x; z[j][1] = b0.y + r0.y; z[j][2] = b1.x + r1.x; z[j][3] = b1.y + r1.y;
+#pragma unroll
+      for (int g = 0; g < kG; ++g) { z[j][0] += v[g][j].x; z[j][1] += v[g][j].y; z[j][2] += v[g][j].z; z[j][3] += v[g][j].w; }
+    }
+    for (int p0 = kG; p0 < n_partial; p0 += kG) {
+#pragma unroll
+      for (int g = 0; g < kG; ++g)
+#pragma unroll
+        for (int j = 0; j < NJ; ++j)
+          v[g][j] = p0 + g < n_partial ? __ldcg(reinterpret_cast<const float4*>(pl + (size_t)(p0 + g) * plane_stride + (lane + 32 * j) * 4))
+                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int j = 0; j < NJ; ++j)
+#pragma unroll
+        for (int g = 0; g < kG; ++g) { z[j][0] += v[g][j].x; z[j][1] += v[g][j].y; z[j][2] += v[g][j].z; z[j][3] += v[g][j].w; }
+    }
+  }
+  if (eps < 0.0f) {                     // sum only
+#pragma unroll
+    for (int j = 0; j < NJ; ++j)
+      *reinterpret_cast<uint2*>(out + (lane + 32 * j) * 4) = make_uint2(pack_h2(z[j][0], z[j][1]), pack_h2(z[j][2], z[j][3]));
+    return;
+  }
+  uint2 ug[NJ], ubt[NJ];
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) {
+    ug[j] = gamma ? __ldg(reinterpret_cast<const uint2*>(gamma + (lane + 32 * j) * 4)) : make_uint2(0u, 0u);
+    ubt[j] = gamma ? __ldg(reinterpret_cast<const uint2*>(beta + (lane + 32 * j) * 4)) : make_uint2(0u, 0u);
+  }
+  const float inv_n = 1.0f / (float)(NJ * 128);
+  float sa = 0.0f;
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) sa += (z[j][0] + z[j][1]) + (z[j][2] + z[j][3]);
+  sa = warp_sum(sa);
+  const float mean = sa * inv_n;
+  float va = 0.0f;
+#pragma unroll
+  for (int j = 0; j < NJ; ++j)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float d0 = z[j][i] - mean;
+      va = fmaf(d0, d0, va);
+    }
+  va = warp_sum(va);
+  const float rstd = rsqrtf(va * inv_n + eps), nm = -mean * rstd;
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) {
+    uint32_t w0 = pack_h2(fmaf(z[j][0], rstd, nm), fmaf(z[j][1], rstd, nm));
+    uint32_t w1 = pack_h2(fmaf(z[j][2], rstd, nm), fmaf(z[j][3], rstd, nm));
+    if (gamma) {
+      const __half2 y0 = __hfma2(*reinterpret_cast<const __half2*>(&w0), *reinterpret_cast<const __half2*>(&ug[j].x),
+                                 *reinterpret_cast<const __half2*>(&ubt[j].x));
+      const __half2 y1 = __hfma2(*reinterpret_cast<const __half2*>(&w1), *reinterpret_cast<const __half2*>(&ug[j].y),
+                                 *reinterpret_cast<const __half2*>(&ubt[j].y));
+      w0 = *reinterpret_cast<const uint32_t*>(&y0);
+      w1 = *reinterpret_cast<const uint32_t*>(&y1);
+    }
+    *reinterpret_cast<uint2*>(out + (lane + 32 * j) * 4) = make_uint2(w0, w1);
+  }
+}
+
 // Direct form of the LayerNorm stage (the host picks it when a CTA has at most one row per normalising warp): every
-// warp reads its row from global memory itself -- one round trip to L2 instead of copy issue, copy latency and a
-// barrier wait.  Out of line: its registers are not charged to the stage interpreter.
+// warp reads its row from global memory itself -- no copy issue, copy latency and barrier wait of the staging ring.
+// Out of line: its registers are not charged to the stage interpreter.
 __device__ __noinline__ void ln_stage_direct(const Stage& st, const MegaParams& p, int warp, int lane) {
   const int N = st.N, M = st.M, P = st.n_partial, rb = st.bm, n_batches = st.items;
   if (warp == 0 || warp - 1 >= rb) return;
@@ -1489,11 +1596,11 @@ __device__ __noinline__ void ln_stage_direct(const Stage& st, const MegaParams& 
     const __half* ra = resid ? resid + (size_t)row * N : nullptr;
     __half* o0 = out + (size_t)row * N;
     switch (N >> 7) {
-      case 1: ln_rows2<1, true>(pl0, nullptr, P, M * N, ra, nullptr, bias, gamma, beta, st.eps, o0, nullptr, lane); break;
-      case 2: ln_rows2<2, true>(pl0, nullptr, P, M * N, ra, nullptr, bias, gamma, beta, st.eps, o0, nullptr, lane); break;
-      case 4: ln_rows2<4, true>(pl0, nullptr, P, M * N, ra, nullptr, bias, gamma, beta, st.eps, o0, nullptr, lane); break;
-      case 6: ln_rows2<6, true>(pl0, nullptr, P, M * N, ra, nullptr, bias, gamma, beta, st.eps, o0, nullptr, lane); break;
-      default: ln_rows2<8, true>(pl0, nullptr, P, M * N, ra, nullptr, bias, gamma, beta, st.eps, o0, nullptr, lane); break;
+      case 1: ln_row_direct<1>(pl0, P, M * N, ra, bias, gamma, beta, st.eps, o0, lane); break;
+      case 2: ln_row_direct<2>(pl0, P, M * N, ra, bias, gamma, beta, st.eps, o0, lane); break;
+      case 4: ln_row_direct<4>(pl0, P, M * N, ra, bias, gamma, beta, st.eps, o0, lane); break;
+      case 6: ln_row_direct<6>(pl0, P, M * N, ra, bias, gamma, beta, st.eps, o0, lane); break;
+      default: ln_row_direct<8>(pl0, P, M * N, ra, bias, gamma, beta, st.eps, o0, lane); break;
     }
   }
 }
@@ -1686,6 +1793,7 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
       mbar_init(smem_u32(&cs.tmem_full[i]), 1);
       mbar_init(smem_u32(&cs.tmem_empty[i]), kThreads - 64);
     }
+    mbar_init(smem_u32(&cs.rec_full), 1);
     mbar_init(smem_u32(&cs.qk_full), 1);
     mbar_init(smem_u32(&cs.qk_empty), 1);
     mbar_init(smem_u32(&cs.v_full), 1);
@@ -1725,15 +1833,16 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
 
   RoleState rs;
   for (int si = 0; si < p.n_stages; ++si) {
-    // stage record -> shared memory (uniform, read-only afterwards)
-    {
+    // stage record -> shared memory (uniform, read-only afterwards).  Records of a plan-owned program arrive during
+    // the barrier before the stage (grid_barrier), except the first; the stages of the plan-less entry points travel
+    // in the launch parameters and are copied here.
+    if (si == 0 || !p.stages) {
       const uint32_t* src = reinterpret_cast<const uint32_t*>(p.stages ? p.stages + si : &ca.inline_stages[si]);
       uint32_t* dst = reinterpret_cast<uint32_t*>(&cs.stage);
       for (int i = threadIdx.x; i < (int)(sizeof(Stage) / 4); i += kThreads) dst[i] = src[i];
     }
-    if (threadIdx.x == 0) cs.stage.prof_index = si;
     __syncthreads();
-    if (p.prof && threadIdx.x == 0) p.prof[((size_t)si * gridDim.x + blockIdx.x) * kProfSlots + 0] = clock64();
+    if (p.prof && threadIdx.x == 0) p.prof[((size_t)si * gridDim.x + blockIdx.x) * kProfSlots + 0] = clock_now();
     const Stage& st = cs.stage;
     if constexpr (kFamily == kFamilySwin) {
       if (st.type == STAGE_GEMM) gemm_stage_ool(st, ca, cs, ring, vec_s, stage_s, rs, ctl, warp, lane);
@@ -1750,12 +1859,12 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
       }
     }
     if (si + 1 < p.n_stages) {
-      if (!grid_barrier(p, ctl, si)) break;
+      if (!grid_barrier(p, ctl, si, cs)) break;
     } else {
       __syncthreads();
-      if (p.prof && threadIdx.x == 0) p.prof[((size_t)si * gridDim.x + blockIdx.x) * kProfSlots + 1] = clock64();
+      if (p.prof && threadIdx.x == 0) p.prof[((size_t)si * gridDim.x + blockIdx.x) * kProfSlots + 1] = clock_now();
     }
-    if (p.prof && threadIdx.x == 0) p.prof[((size_t)si * gridDim.x + blockIdx.x) * kProfSlots + 2] = clock64();
+    if (p.prof && threadIdx.x == 0) p.prof[((size_t)si * gridDim.x + blockIdx.x) * kProfSlots + 2] = clock_now();
     if (cs.abort) break;
   }
 

@@ -222,8 +222,10 @@ static int device_info(DeviceInfo** out) {
 }
 
 // `family` selects the build of the kernel (see souffle_megakernel).
-static int launch_mega(const CallArgs& args, int grid, cudaStream_t stream, int family = kFamilyBert) {
-  void* kargs[] = {const_cast<CallArgs*>(&args)};
+static int launch_mega(const CallArgs& args_in, int grid, cudaStream_t stream, int family = kFamilyBert) {
+  CallArgs args = args_in;
+  for (int i = 0; i < 3; ++i) args.inline_stages[i].prof_index = i;      // stages that travel in the launch parameters
+  void* kargs[] = {&args};
   const void* fn = family == kFamilySwin ? (const void*)souffle_megakernel<kFamilySwin>
                    : family == kFamilyBertCoop ? (const void*)souffle_megakernel<kFamilyBertCoop>
                                                : (const void*)souffle_megakernel<kFamilyBert>;
@@ -334,6 +336,20 @@ struct SouffleBertPlan {
 };
 
 namespace souffle {
+
+static int plan_alloc(SouffleBertPlan* p, void** ptr, size_t bytes);
+
+// Numbers the stages and copies the program and its tensor maps to the device.
+static int upload_program(SouffleBertPlan* p) {
+  int rc;
+  for (size_t i = 0; i < p->stages.size(); ++i) p->stages[i].prof_index = (int)i;
+  if ((rc = plan_alloc(p, (void**)&p->d_stages, p->stages.size() * sizeof(Stage)))) return rc;
+  if ((rc = plan_alloc(p, (void**)&p->d_maps, p->maps.size() * sizeof(CUtensorMap)))) return rc;
+  SF_CUDA(cudaMemcpy(p->d_stages, p->stages.data(), p->stages.size() * sizeof(Stage), cudaMemcpyHostToDevice));
+  SF_CUDA(cudaMemcpy(p->d_maps, p->maps.data(), p->maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice));
+  SF_CUDA(cudaDeviceSynchronize());
+  return SOUFFLE_OK;
+}
 
 static int plan_alloc(SouffleBertPlan* p, void** ptr, size_t bytes) {
   SF_CUDA(cudaMalloc(ptr, bytes));
@@ -646,12 +662,7 @@ static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* la
   p->family = (d.seq > 128 || d.batch * d.heads <= p->grid) ? kFamilyBertCoop : kFamilyBert;
   for (Stage& fs : p->stages)
     if ((rc = finalize_stage(fs, p->desc.debug_max_slots, p->grid))) return rc;
-  if ((rc = plan_alloc(p, (void**)&p->d_stages, p->stages.size() * sizeof(Stage)))) return rc;
-  if ((rc = plan_alloc(p, (void**)&p->d_maps, p->maps.size() * sizeof(CUtensorMap)))) return rc;
-  SF_CUDA(cudaMemcpy(p->d_stages, p->stages.data(), p->stages.size() * sizeof(Stage), cudaMemcpyHostToDevice));
-  SF_CUDA(cudaMemcpy(p->d_maps, p->maps.data(), p->maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice));
-  SF_CUDA(cudaDeviceSynchronize());
-  return SOUFFLE_OK;
+  return upload_program(p);
 }
 
 }  // namespace souffle
@@ -1098,12 +1109,7 @@ static int finish_plan(SouffleBertPlan* p, int sms) {
   p->grid = max_items < sms ? max_items : sms;
   for (Stage& fs : p->stages)
     if ((rc = finalize_stage(fs, p->desc.debug_max_slots, p->grid))) return rc;
-  if ((rc = plan_alloc(p, (void**)&p->d_stages, p->stages.size() * sizeof(Stage)))) return rc;
-  if ((rc = plan_alloc(p, (void**)&p->d_maps, p->maps.size() * sizeof(CUtensorMap)))) return rc;
-  SF_CUDA(cudaMemcpy(p->d_stages, p->stages.data(), p->stages.size() * sizeof(Stage), cudaMemcpyHostToDevice));
-  SF_CUDA(cudaMemcpy(p->d_maps, p->maps.data(), p->maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice));
-  SF_CUDA(cudaDeviceSynchronize());
-  return SOUFFLE_OK;
+  return upload_program(p);
 }
 
 static int build_swin_plan(SouffleSwinPlan* sp, const SouffleSwinWeights* blocks) {

@@ -30,7 +30,7 @@ enum Activation : int { ACT_NONE = 0, ACT_RELU = 1, ACT_GELU = 2 };
 // Pointer selectors: a stage either carries a plan-owned pointer or names a per-call argument.
 enum PtrSel : int { PTR_PLAN = 0, PTR_CALL_X = 1, PTR_CALL_Y = 2 };
 
-struct Stage {
+struct alignas(16) Stage {      // 16-byte multiples: records are fetched with bulk copies
   int type;
   // ---- GEMM ----
   int tm_a;          // tensor-map index of the A operand ([M][K], box 64 x bm); negative = per-call map
@@ -63,7 +63,7 @@ struct Stage {
   const void* beta;  // fp16 [N] or null
   float eps;
   int n_partial;     // number of fp32 partial planes to sum
-  int prof_index;    // filled in by the kernel: position of this stage in the program
+  int prof_index;    // position of this stage in the program (set by the host when the program is built)
   // ---- derived on the host by finalize_stage(): the kernel's lone producer / MMA lanes would otherwise
   //      spend a few thousand cycles per stage in integer divisions ----
   int tiles_n, kchunks, items, slot_bytes, nslots;
