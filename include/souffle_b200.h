@@ -79,6 +79,12 @@ typedef struct SouffleBertDesc {
                          launches each on the plan's own buffers, tens of milliseconds in all) and keeps the
                          fastest; stages with an explicit bm_ / bn_ / split_ setting are left alone.  0: tiles come
                          from the cycle model alone.  Two plans of one shape may then differ in summation order. */
+  int32_t pair_mma;   /* 1: run on CTA pairs where the shape qualifies (seq <= 128, an even number of heads, more
+                         (sequence, head) items than CTAs, at least 2048 rows): clusters of two CTAs share every
+                         tensor-core instruction (cta_group::2), each CTA loads half of every weight tile and the
+                         attention stage takes two heads per pair.  0 (default): single-CTA MMAs, which measure
+                         3 % faster at batch 64 because the epilogues, not the operand traffic, bound the GEMM stages
+                         once the main loops speed up.  souffle_bert_plan_uses_pairs reports what a plan uses. */
 } SouffleBertDesc;
 
 /* Device pointers to one layer's parameters, fp16.  Matrices use the reference's [K][N]
@@ -166,6 +172,8 @@ int souffle_bert_plan_status(SouffleBertPlan* plan);
 int souffle_bert_plan_read_profile(SouffleBertPlan* plan, int64_t* out, size_t capacity_elems);
 /* Number of kernels launched by the last forward call and the persistent grid size. */
 int souffle_bert_plan_info(SouffleBertPlan* plan, int* launches_out, int* grid_out, int* n_stages_out);
+/* 1 if the plan's launch runs on CTA pairs (see SouffleBertDesc.pair_mma), else 0. */
+int souffle_bert_plan_uses_pairs(SouffleBertPlan* plan);
 /* The tiling chosen for stage `index` of the program: out[0..5] = {stage type (0 GEMM, 1 attention, 2 LayerNorm),
  * tile rows, tile columns, split-K factor, work items, ring slots}.  The reference fixes these at compile time
  * (cpp/bert/kernels/bert.h:18-52); here they depend on the shape and on the SM count. */

@@ -24,7 +24,7 @@ class BertDesc(C.Structure):
                                          "keep_probs")] + [("eps", C.c_float)] + \
                [(n, C.c_int32) for n in ("bn_qkv", "bn_fc1", "bn_proj", "split_proj", "bn_fc2", "split_fc2",
                                          "max_ctas", "timeout_ms", "profile", "bm_qkv", "bm_fc1", "bm_proj",
-                                         "bm_fc2", "debug_max_slots", "debug_skip_arrival", "autotune")]
+                                         "bm_fc2", "debug_max_slots", "debug_skip_arrival", "autotune", "pair_mma")]
 
 
 class BertLayerWeights(C.Structure):
@@ -64,6 +64,7 @@ SIGNATURES = {
     "souffle_bert_plan_status": (C.c_int, [C.c_void_p]),
     "souffle_bert_plan_read_profile": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),
     "souffle_bert_plan_info": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "souffle_bert_plan_uses_pairs": (C.c_int, [C.c_void_p]),
     "souffle_bert_packed_weights": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.POINTER(BertLayerWeights),
                                               C.POINTER(C.c_void_p), C.POINTER(C.c_size_t)]),
     "souffle_bert_plan_stage_info": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_int)]),

@@ -106,7 +106,7 @@ class BertEncoder:
     def info(self) -> Dict[str, int]:
         a, b, c = C.c_int(), C.c_int(), C.c_int()
         _lib.check(self._lib.souffle_bert_plan_info(self._h, C.byref(a), C.byref(b), C.byref(c)))
-        return dict(launches=a.value, grid=b.value, stages=c.value)
+        return dict(launches=a.value, grid=b.value, stages=c.value, pairs=int(self._lib.souffle_bert_plan_uses_pairs(self._h)))
 
     def stage_info(self, index: int) -> Dict[str, int]:
         """Tiling of stage `index`: type (0 GEMM, 1 attention, 2 LayerNorm), tile rows/columns, split-K, items, ring slots."""

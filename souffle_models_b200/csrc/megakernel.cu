@@ -30,10 +30,10 @@ namespace souffle {
 constexpr int kThreads = 320;               // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
 constexpr int kRingBytes = 196608;          // 192 KiB operand ring (4 x 48 KiB, 3 x 64 KiB or 6 x 32 KiB slots)
 constexpr int kCtlBytes = 1024;             // barriers + control words
-constexpr int kVecBytes = 8192;              // per-stage bias vector staged in shared memory
-constexpr int kStageRow = 80;                // bytes per staged row: 64 B of payload + 16 B against bank conflicts
+constexpr int kVecBytes = 16384;             // per-stage vectors staged in shared memory (a GEMM's bias as fp32: N <= 4096)
+constexpr int kStageRow = 64;                // bytes per staged row; the 16-byte pieces of a row are XOR-swizzled (see below)
 constexpr int kStageWarp = 32 * kStageRow;   // one epilogue warp's transpose buffer
-constexpr int kStageBytes = 8 * kStageWarp;  // 20 KiB
+constexpr int kStageBytes = 8 * kStageWarp;  // 16 KiB
 // Layout after the control block: ring | bias vector | store staging.  The attention stage with three
 // key blocks needs 208 KiB and simply runs over all three regions (it uses neither of the other two).
 constexpr int kSmemBytes = kCtlBytes + kRingBytes + kVecBytes + kStageBytes + 1024;  // + alignment slack
@@ -82,6 +82,7 @@ struct __align__(8) SmemCtl {
   uint64_t tmem_empty[2];
   uint64_t qk_full, qk_empty, v_full, v_empty, s_full, p_full, o_full;   // attention, pipeline 0
   uint64_t attn1[7];                                                     // attention, pipeline 1 (same order)
+  uint64_t o_empty[2];                                                   // pair attention: output accumulator read out
   uint64_t ln_full[4], ln_empty[4];
   uint64_t rec_full;                // the next stage's record has landed (bulk copy issued inside the grid barrier)
   uint32_t tmem_base;
@@ -100,6 +101,7 @@ struct RoleState {
   uint32_t attn_bit = 0;   // phase bit of the attention barriers, pipeline 0
   uint32_t attn_bit1 = 0;  // phase bit of the attention barriers, pipeline 1
   uint32_t ln_bits = 0;    // phase bit per LayerNorm batch buffer
+  uint32_t o_bits = 0;     // pair attention: phase bit of the o_empty barrier of each pipeline (MMA lane)
 };
 
 // SM clock for the stage-level stamps of the in-kernel profile.  The memory clobber keeps the read where it is
@@ -135,6 +137,14 @@ __device__ bool grid_barrier(const MegaParams& p, const WaitCtl& ctl, int where,
     // copy while this thread waits for the other CTAs, so its round trip to L2 costs the stage nothing.
     const bool fetch = p.stages != nullptr;
     if (fetch) {
+      // first this CTA's slice of the weights of the GEMM stage after next -> L2 (they come from HBM when the program's
+      // weights exceed L2; without this every GEMM stage starts with all CTAs waiting on the same DRAM rows)
+      const uint32_t pf_bytes = cs.stage.pf_bytes;
+      if (pf_bytes) {
+        const uint32_t per = ((pf_bytes + gridDim.x - 1) / gridDim.x + 15u) & ~15u, off = blockIdx.x * per;
+        if (off < pf_bytes)
+          bulk_prefetch_l2(reinterpret_cast<const char*>(cs.stage.pf_ptr) + off, off + per <= pf_bytes ? per : pf_bytes - off);
+      }
       mbar_expect_tx(smem_u32(&cs.rec_full), (uint32_t)sizeof(Stage));
       bulk_load(smem_u32(&cs.stage), p.stages + where + 1, (uint32_t)sizeof(Stage), smem_u32(&cs.rec_full));
     }
@@ -191,7 +201,7 @@ __device__ __forceinline__ void gemm_item(const Stage& st, int item, int& mt, in
 // shared memory and would otherwise be re-read around every asm statement).
 struct EpiCtx {
   int epi, act, M, N, ldo;
-  const __half* bias_s;    // bias staged in shared memory, or null
+  const float* bias_s;     // bias staged in shared memory as fp32 (converted once per stage), or null
   const __half* resid;
   __half* out;
   float* partial;
@@ -205,15 +215,23 @@ constexpr uint32_t kNoRow = 0xFFFFFFFFu;      // "this row is outside the matrix
 // +24), so every store instruction writes eight rows with 64 contiguous bytes each.
 // `rowptr[i]` is the global byte address of row (8*i + lane/4) at this chunk's first column, or null.
 __device__ __forceinline__ void staged_store_64B(uint8_t* sbuf, const uint32_t (&w)[16], uint8_t* const (&rowptr)[4], int lane) {
-  uint4* mine = reinterpret_cast<uint4*>(sbuf + lane * kStageRow);
+  // Piece i (16 bytes) of row r sits at r * 64 + ((i ^ (r >> 1)) & 3) * 16: the eight lanes of a quarter warp then hit
+  // distinct banks both when every lane writes piece i of its own row and when four lanes read one row each of two
+  // neighbouring rows (padded rows avoided the conflicts of the writes only: two thirds of the reads were replays).
+  const int sw_w = (lane >> 1) & 3;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) mine[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+  for (int i = 0; i < 4; ++i)
+    *reinterpret_cast<uint4*>(sbuf + lane * kStageRow + ((i ^ sw_w) << 4)) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
   __syncwarp();
+  uint4 v[4];                    // all four loads are issued before the first store waits for its data
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const uint4 v = *reinterpret_cast<const uint4*>(sbuf + (8 * i + (lane >> 2)) * kStageRow + (lane & 3) * 16);
-    if (rowptr[i]) *reinterpret_cast<uint4*>(rowptr[i] + (lane & 3) * 16) = v;
+    const int r = 8 * i + (lane >> 2);
+    v[i] = *reinterpret_cast<const uint4*>(sbuf + r * kStageRow + ((((lane & 3) ^ (r >> 1)) & 3) << 4));
   }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    if (rowptr[i]) *reinterpret_cast<uint4*>(rowptr[i] + (lane & 3) * 16) = v[i];
   __syncwarp();
 }
 
@@ -305,21 +323,18 @@ __device__ __forceinline__ void epilogue_chunk32(const Stage& st, const EpiCtx& 
     }
     return;
   }
+  // The arithmetic below is written phase by phase over the whole chunk -- every loop is 16 or 32 independent
+  // operations -- instead of element by element: an epilogue warp has at most one other warp on its scheduler, so
+  // a dependent chain per element (conversion, add, pack, seven GELU steps) runs at one instruction per ALU latency.
   float v[32];
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-  if (e.bias_s) {
-    const uint4* b4 = reinterpret_cast<const uint4*>(e.bias_s + col);
+  if (e.bias_s) {               // fp32 in shared memory: no conversions here (they run on the narrow XU pipe)
+    const float4* b4 = reinterpret_cast<const float4*>(e.bias_s + col);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint4 u = b4[i];
-      const __half2* h = reinterpret_cast<const __half2*>(&u);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = __half22float2(h[j]);
-        v[8 * i + 2 * j] += f.x;
-        v[8 * i + 2 * j + 1] += f.y;
-      }
+    for (int i = 0; i < 8; ++i) {
+      const float4 b = b4[i];
+      v[4 * i] += b.x; v[4 * i + 1] += b.y; v[4 * i + 2] += b.z; v[4 * i + 3] += b.w;
     }
   }
   const bool gelu_packed = e.act == ACT_GELU && e.resid == nullptr;   // GELU on fp16 pairs after packing (below)
@@ -332,16 +347,18 @@ __device__ __forceinline__ void epilogue_chunk32(const Stage& st, const EpiCtx& 
   }
   if (e.resid && own != kNoRow) {
     const uint4* r4 = reinterpret_cast<const uint4*>(e.resid + own + col);
+    float2 fr[16];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const uint4 u = r4[i];
       const __half2* h = reinterpret_cast<const __half2*>(&u);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = __half22float2(h[j]);
-        v[8 * i + 2 * j] += f.x;
-        v[8 * i + 2 * j + 1] += f.y;
-      }
+      for (int j = 0; j < 4; ++j) fr[4 * i + j] = __half22float2(h[j]);
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      v[2 * i] += fr[i].x;
+      v[2 * i + 1] += fr[i].y;
     }
   }
   const uint32_t coff = epi_col_offset<kSwin>(st, e, col);
@@ -351,10 +368,7 @@ __device__ __forceinline__ void epilogue_chunk32(const Stage& st, const EpiCtx& 
   uint32_t w[16];
 #pragma unroll
   for (int i = 0; i < 16; ++i) w[i] = pack_h2(v[2 * i], v[2 * i + 1]);
-  if (gelu_packed) {
-#pragma unroll
-    for (int i = 0; i < 16; ++i) w[i] = gelu_tanh_h2(w[i]);
-  }
+  if (gelu_packed) gelu_tanh_h2x16(w);
   if (e.prof) t_mid = (unsigned)clock64();
   staged_store_64B(sbuf, w, rowptr, lane);
 }
@@ -376,11 +390,7 @@ __device__ __forceinline__ void epilogue_chunk16(const Stage& st, const EpiCtx& 
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
   if (e.bias_s) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(e.bias_s + col + 2 * i));
-      v[2 * i] += f.x;
-      v[2 * i + 1] += f.y;
-    }
+    for (int i = 0; i < 16; ++i) v[i] += e.bias_s[col + i];
   }
   if (e.act == ACT_RELU) {
 #pragma unroll
@@ -411,22 +421,38 @@ __device__ __forceinline__ void epilogue_chunk16(const Stage& st, const EpiCtx& 
 // Tiles are bm x bn with bm = 128 (two accumulators used alternately, so the epilogue of one tile
 // overlaps the main loop of the next) or bm = 256 (two 128-row halves share every B tile, which
 // halves the B traffic per FLOP; each half has its own accumulator and hand-shake).
-template <bool kSwin>
+// kPair: the two CTAs of a cluster work on one 256 x bn tile with pair MMAs (see sm100_ptx.cuh).  CTA r loads rows
+// 128 r .. 128 r + 127 of the A tile and rows bn/2 * r .. of the B tile (the weights' output columns) into its own
+// shared memory -- half the B traffic per FLOP of the single-CTA form -- with every copy's completion counted on the
+// leader's full barrier; the leader's MMA lane issues for both and its commits arrive on the barriers of both CTAs;
+// each CTA's epilogue warps drain their own 128 rows and report to the leader's accumulator-free barrier.
+template <bool kSwin, bool kPair = false>
 __device__ __forceinline__ void gemm_stage(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, uint32_t ring, __half* vec_s,
                            uint8_t* stage_s, RoleState& rs, const WaitCtl& ctl, int warp, int lane) {
   const MegaParams& p = ca.p;
-  const GemmGeom g = gemm_geom(st);
+  GemmGeom g = gemm_geom(st);
+  if constexpr (kPair) g.nh = 1;                                       // per CTA: one 128-row half of the pair's tile
   if (rs.slot >= (uint32_t)g.nslots) rs.slot = 0;
   const uint32_t full0 = smem_u32(&ctl_s.full[0]), empty0 = smem_u32(&ctl_s.empty[0]);
   const uint32_t tfull0 = smem_u32(&ctl_s.tmem_full[0]), tempty0 = smem_u32(&ctl_s.tmem_empty[0]);
   const uint32_t a_bytes = (uint32_t)(g.nh * kATileBytes);
+  const uint32_t rank = kPair ? cluster_cta_rank() : 0u;               // 0 = the pair's leader
+  const int first_item = kPair ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int item_step = kPair ? (int)(gridDim.x >> 1) : (int)gridDim.x;
   // the stage's bias vector -> shared memory (one global read per CTA instead of one per tile chunk)
   // (done by the epilogue warps alone; the producer and MMA warps start the main loop meanwhile)
-  const __half* bias_s = nullptr;
-  if (warp >= 2 && st.bias && st.epi != EPI_PARTIAL && st.N * 2 <= kVecBytes) {
+  const float* bias_s = nullptr;
+  if (warp >= 2 && st.bias && st.epi != EPI_PARTIAL && st.N * 4 <= kVecBytes) {
     const uint4* src = reinterpret_cast<const uint4*>(st.bias);
-    for (int i = threadIdx.x - 64; i < st.N / 8; i += kThreads - 64) reinterpret_cast<uint4*>(vec_s)[i] = __ldg(src + i);
-    bias_s = vec_s;
+    float4* dst = reinterpret_cast<float4*>(vec_s);
+    for (int i = threadIdx.x - 64; i < st.N / 8; i += kThreads - 64) {
+      const uint4 u = __ldg(src + i);
+      const __half2* h = reinterpret_cast<const __half2*>(&u);
+      const float2 f0 = __half22float2(h[0]), f1 = __half22float2(h[1]), f2 = __half22float2(h[2]), f3 = __half22float2(h[3]);
+      dst[2 * i] = make_float4(f0.x, f0.y, f1.x, f1.y);
+      dst[2 * i + 1] = make_float4(f2.x, f2.y, f3.x, f3.y);
+    }
+    bias_s = reinterpret_cast<const float*>(vec_s);
     named_barrier_sync(1, kThreads - 64);
   }
 
@@ -439,27 +465,35 @@ __device__ __forceinline__ void gemm_stage(const Stage& st, const CallArgs& ca, 
       long long t_wait = 0, t_first = 0;
       const bool prof = p.prof != nullptr;
       uint32_t s = rs.slot, bits = rs.slot_bits;
-      for (int item = blockIdx.x; ok && item < g.items; item += gridDim.x) {
+      for (int item = first_item; ok && item < g.items; item += item_step) {
         int mt, nt, ks;
         gemm_item(st, item, mt, nt, ks);
-        const int m0 = mt * g.bm, n0 = nt * g.bn, kbase = ks * g.kchunks;
+        const int m0 = mt * g.bm + (int)rank * 128, n0 = nt * g.bn + (int)rank * (g.bn >> 1), kbase = ks * g.kchunks;
         // CTAs start at different K chunks so they do not all pull the same A tile at once
-        const uint32_t rot = blockIdx.x + (uint32_t)item;
+        const uint32_t rot = (uint32_t)first_item + (uint32_t)item;
         int kk = (int)(rot - fast_div(rot, (uint32_t)g.kchunks, st.mg_kchunks) * (uint32_t)g.kchunks);
         for (int kc = 0; kc < g.kchunks; ++kc) {
           const long long tw = prof ? clock64() : 0;
           if (!mbar_wait(empty0 + 8 * s, ((bits >> s) & 1u) ^ 1u, ctl, 100 + (int)s)) { ok = false; break; }
           if (prof) t_wait += clock64() - tw;
           const uint32_t fb = full0 + 8 * s;
-          mbar_expect_tx(fb, (uint32_t)g.slot_bytes);
           const uint32_t a_dst = ring + s * g.slot_bytes, b_dst = a_dst + a_bytes;
           const int k0 = (kbase + kk) * 64;
           if (prof && !t_first) t_first = clock64();
-          tma_load_2d(a_dst, tmA, fb, k0, m0);                  // box rows = bm: both halves in one copy
-          if (!st.b_mn_major) {
-            tma_load_2d(b_dst, tmB, fb, k0, n0);
+          if constexpr (kPair) {
+            // both CTAs' bytes are counted on the leader's barrier, which only the leader arms
+            if (rank == 0) mbar_expect_tx(fb, 2u * (uint32_t)g.slot_bytes);
+            const uint32_t fbl = map_shared_rank(fb, 0);
+            tma_load_2d_pair(a_dst, tmA, fbl, k0, m0);          // box rows = 128: this CTA's half of the rows
+            tma_load_2d_pair(b_dst, tmB, fbl, k0, n0);          // box rows = bn / 2: this CTA's half of the columns
           } else {
-            for (int j = 0; j < g.bn / 64; ++j) tma_load_2d(b_dst + j * 8192, tmB, fb, n0 + j * 64, k0);
+            mbar_expect_tx(fb, (uint32_t)g.slot_bytes);
+            tma_load_2d(a_dst, tmA, fb, k0, m0);                // box rows = bm: both halves in one copy
+            if (!st.b_mn_major) {
+              tma_load_2d(b_dst, tmB, fb, k0, n0);
+            } else {
+              for (int j = 0; j < g.bn / 64; ++j) tma_load_2d(b_dst + j * 8192, tmB, fb, n0 + j * 64, k0);
+            }
           }
           bits ^= 1u << s;
           s = (s + 1 == (uint32_t)g.nslots) ? 0 : s + 1;
@@ -476,9 +510,10 @@ __device__ __forceinline__ void gemm_stage(const Stage& st, const CallArgs& ca, 
     }
     __syncwarp();
   } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      const uint32_t idesc = umma_idesc_f16((uint32_t)g.bn, (uint32_t)st.b_mn_major);
+    // ---------------- MMA issuer (of a pair: the leader's) ----------------
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = kPair ? umma_idesc_f16_pair((uint32_t)g.bn, (uint32_t)st.b_mn_major)
+                                   : umma_idesc_f16((uint32_t)g.bn, (uint32_t)st.b_mn_major);
       const uint32_t tmem = ctl_s.tmem_base;
       // descriptor low words of slot 0; a slot further on adds slot_bytes/16 to both
       const uint32_t a_lo0 = umma_desc_lo(ring, 16);
@@ -488,7 +523,7 @@ __device__ __forceinline__ void gemm_stage(const Stage& st, const CallArgs& ca, 
       const bool prof = p.prof != nullptr;
       bool ok = true;
       long long t_full = 0, t_acc = 0, t_first = 0, t_last = 0;
-      for (int item = blockIdx.x; ok && item < g.items; item += gridDim.x) {
+      for (int item = first_item; ok && item < g.items; item += item_step) {
         const uint32_t acc0 = g.nh == 2 ? 0u : rs.acc;       // accumulator of half 0; half 1 uses buffer 1
         const uint32_t d0 = tmem + acc0 * kAccStride, d1 = d0 + kAccStride;
         {                                                      // the epilogue must have drained the buffers
@@ -511,16 +546,22 @@ __device__ __forceinline__ void gemm_stage(const Stage& st, const CallArgs& ca, 
           }
           tc_fence_after_sync();
           const uint32_t a_lo = a_lo0 + s * slot16, b_lo = b_lo0 + s * slot16;
-          if (g.nh == 2) umma_f16_k64_x2(d0, d1, a_lo, b_lo, bstep, idesc, (uint32_t)(kc != 0));
-          else umma_f16_k64(d0, a_lo, b_lo, bstep, idesc, (uint32_t)(kc != 0));
-          umma_commit(empty0 + 8 * s);
+          if constexpr (kPair) {
+            umma_f16_k64_pair(d0, a_lo, b_lo, bstep, idesc, (uint32_t)(kc != 0));
+            umma_commit_pair(empty0 + 8 * s);
+          } else {
+            if (g.nh == 2) umma_f16_k64_x2(d0, d1, a_lo, b_lo, bstep, idesc, (uint32_t)(kc != 0));
+            else umma_f16_k64(d0, a_lo, b_lo, bstep, idesc, (uint32_t)(kc != 0));
+            umma_commit(empty0 + 8 * s);
+          }
           rs.slot_bits ^= 1u << s;
           rs.slot = (s + 1 == (uint32_t)g.nslots) ? 0 : s + 1;
         }
         if (!ok) break;
         for (int h = 0; h < g.nh; ++h) {
           const uint32_t acc = acc0 + (uint32_t)h;
-          umma_commit(tfull0 + 8 * acc);
+          if constexpr (kPair) umma_commit_pair(tfull0 + 8 * acc);
+          else umma_commit(tfull0 + 8 * acc);
           rs.acc_bits ^= 1u << acc;
         }
         if (prof) t_last = clock64();
@@ -551,7 +592,7 @@ __device__ __forceinline__ void gemm_stage(const Stage& st, const CallArgs& ca, 
     uint8_t* sbuf = stage_s + (warp - 2) * kStageWarp;
     unsigned t_wait = 0, t_busy = 0, t_tmem = 0, t_math = 0, t_store = 0;   // cycle totals (32 bits are plenty)
     long long t_first = 0;
-    for (int item = blockIdx.x; item < g.items; item += gridDim.x) {
+    for (int item = first_item; item < g.items; item += item_step) {
       int mt, nt, ks;
       gemm_item(st, item, mt, nt, ks);
       const uint32_t acc0 = g.nh == 2 ? 0u : rs.acc;
@@ -569,7 +610,7 @@ __device__ __forceinline__ void gemm_stage(const Stage& st, const CallArgs& ca, 
           if (!t_first) t_first = now;
         }
         tc_fence_after_sync();
-        const int row0 = mt * g.bm + h * 128 + q * 32;
+        const int row0 = mt * g.bm + (kPair ? (int)rank : h) * 128 + q * 32;
         const uint32_t own = epi_row_offset<kSwin>(st, e, row0 + lane, ks);
         uint32_t so[4];
 #pragma unroll
@@ -600,7 +641,12 @@ __device__ __forceinline__ void gemm_stage(const Stage& st, const CallArgs& ca, 
           epilogue_chunk16<kSwin>(st, e, r, own, colbase + full_chunks * 32);
         }
         tc_fence_before_sync();
-        mbar_arrive(tempty0 + 8 * acc);
+        if constexpr (kPair) {                      // one arrival per warp on the leader's barrier (16 in all)
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster_relaxed(map_shared_rank(tempty0 + 8 * acc, 0));
+        } else {
+          mbar_arrive(tempty0 + 8 * acc);
+        }
         rs.acc_bits ^= 1u << acc;
         if (prof) t_busy += (unsigned)clock64() - tb;
       }
@@ -901,31 +947,54 @@ enum AttnBar : int { AB_QK_FULL = 0, AB_QK_EMPTY, AB_V_FULL, AB_V_EMPTY, AB_S_FU
 constexpr int kPipeBytes = 5 * kATileBytes;      // Q 16 KiB, K 16, V 16, P 32
 constexpr int kPipeOCol = 256;                   // TMEM: scores at 0 / 128, outputs at 256 / 320
 
+template <bool kPair>
 __device__ __forceinline__ void attn_stage_pp(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, uint32_t ring, uint8_t* ring_ptr,
                               uint8_t* stage_s, RoleState& rs, const WaitCtl& ctl, int warp, int lane) {
   const MegaParams& p = ca.p;
   const int S = st.seq, B = st.batch, H = st.heads;
-  const int items = B * H;
-  const int my_items = items > (int)blockIdx.x ? (items - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  // kPair: the two CTAs of a pair take the two heads 2c, 2c + 1 of one sequence (same valid length) and the leader
+  // issues ONE pair MMA for both: A = [Q_0; Q_1] (M = 256), B = [K_0; K_1] (N = 256), so CTA r finds Q_r K_r^T in
+  // columns 128 r .. of its accumulator (the off-diagonal blocks are waste the tensor core has time for); then
+  // A = [P_0; P_1], B = [V_0 | V_1] (N = 128) leaves O_r in columns 64 r ...  Every CTA loads exactly its own Q, K, V.
+  // The output accumulator re-uses the columns of the scores (512 columns hold two pipelines of 256), so the scores
+  // of a pipeline's next item wait until its output has been read (o_empty).
+  const uint32_t rank = kPair ? cluster_cta_rank() : 0u;
+  const int units = kPair ? (B * H) >> 1 : B * H;                      // couples of heads, or single (sequence, head) items
+  const int first = kPair ? (int)(blockIdx.x >> 1) : (int)blockIdx.x, step = kPair ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  const int my_items = units > first ? (units - 1 - first) / step + 1 : 0;
+  auto item_of = [&](int k) -> int { const int u = first + k * step; return kPair ? 2 * u + (int)rank : u; };
   const uint32_t bar0 = smem_u32(&ctl_s.qk_full), bar1 = smem_u32(&ctl_s.attn1[0]);
   auto bar = [&](int g, int which) -> uint32_t { return (g ? bar1 : bar0) + 8u * (uint32_t)which; };
+  const uint32_t oempty0 = smem_u32(&ctl_s.o_empty[0]);
   const CUtensorMap* tm = map_ptr(ca, st.tm_qkv);
 
   if (warp == 0) {
     if (lane == 0) {
       uint32_t bits = rs.attn_bit | (rs.attn_bit1 << 1);
       for (int k = 0; k < my_items; ++k) {
-        const int item = blockIdx.x + k * gridDim.x, g = k & 1;
+        const int item = item_of(k), g = k & 1;
         const int h = item % H, b = item / H;
         const int rq = ((0 * B + b) * H + h) * S, rk = ((1 * B + b) * H + h) * S, rv = ((2 * B + b) * H + h) * S;
         const uint32_t base = ring + g * kPipeBytes, bit = (bits >> g) & 1u;
         if (!mbar_wait(bar(g, AB_QK_EMPTY), bit ^ 1u, ctl, 500 + g)) break;
-        mbar_expect_tx(bar(g, AB_QK_FULL), 2u * kATileBytes);
-        tma_load_2d(base, tm, bar(g, AB_QK_FULL), 0, rq);
-        tma_load_2d(base + kATileBytes, tm, bar(g, AB_QK_FULL), 0, rk);
+        if constexpr (kPair) {            // both CTAs' tiles are counted on the leader's barriers
+          if (rank == 0) mbar_expect_tx(bar(g, AB_QK_FULL), 4u * kATileBytes);
+          const uint32_t fl = map_shared_rank(bar(g, AB_QK_FULL), 0);
+          tma_load_2d_pair(base, tm, fl, 0, rq);
+          tma_load_2d_pair(base + kATileBytes, tm, fl, 0, rk);
+        } else {
+          mbar_expect_tx(bar(g, AB_QK_FULL), 2u * kATileBytes);
+          tma_load_2d(base, tm, bar(g, AB_QK_FULL), 0, rq);
+          tma_load_2d(base + kATileBytes, tm, bar(g, AB_QK_FULL), 0, rk);
+        }
         if (!mbar_wait(bar(g, AB_V_EMPTY), bit ^ 1u, ctl, 502 + g)) break;
-        mbar_expect_tx(bar(g, AB_V_FULL), (uint32_t)kATileBytes);
-        tma_load_2d(base + 2 * kATileBytes, tm, bar(g, AB_V_FULL), 0, rv);
+        if constexpr (kPair) {
+          if (rank == 0) mbar_expect_tx(bar(g, AB_V_FULL), 2u * kATileBytes);
+          tma_load_2d_pair(base + 2 * kATileBytes, tm, map_shared_rank(bar(g, AB_V_FULL), 0), 0, rv);
+        } else {
+          mbar_expect_tx(bar(g, AB_V_FULL), (uint32_t)kATileBytes);
+          tma_load_2d(base + 2 * kATileBytes, tm, bar(g, AB_V_FULL), 0, rv);
+        }
         bits ^= 1u << g;
       }
       rs.attn_bit = bits & 1u;
@@ -933,19 +1002,27 @@ __device__ __forceinline__ void attn_stage_pp(const Stage& st, const CallArgs& c
     }
     __syncwarp();
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc_s = umma_idesc_f16(128u, 0u), idesc_o = umma_idesc_f16(64u, 1u);
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc_s = kPair ? umma_idesc_f16_pair(256u, 0u) : umma_idesc_f16(128u, 0u);
+      const uint32_t idesc_o = kPair ? umma_idesc_f16_pair(128u, 1u) : umma_idesc_f16(64u, 1u);
       const uint32_t tmem = ctl_s.tmem_base;
       uint32_t bits = rs.attn_bit | (rs.attn_bit1 << 1);
+      uint32_t obits = rs.o_bits;                              // pair form: phase bit of the o_empty barrier of each pipeline
       bool ok = true;
       auto issue_s = [&](int k) {                              // scores of item k: S = Q K^T
         const int g = k & 1;
         const uint32_t base = ring + g * kPipeBytes;
         if (!mbar_wait(bar(g, AB_QK_FULL), (bits >> g) & 1u, ctl, 510 + g)) { ok = false; return; }
         tc_fence_after_sync();
-        umma_f16_k64(tmem + g * 128, umma_desc_lo(base, 16), umma_desc_lo(base + kATileBytes, 16), 2u, idesc_s, 0u);
-        umma_commit(bar(g, AB_S_FULL));
-        umma_commit(bar(g, AB_QK_EMPTY));
+        if constexpr (kPair) {
+          umma_f16_k64_pair(tmem + g * 256, umma_desc_lo(base, 16), umma_desc_lo(base + kATileBytes, 16), 2u, idesc_s, 0u);
+          umma_commit_pair(bar(g, AB_S_FULL));
+          umma_commit_pair(bar(g, AB_QK_EMPTY));
+        } else {
+          umma_f16_k64(tmem + g * 128, umma_desc_lo(base, 16), umma_desc_lo(base + kATileBytes, 16), 2u, idesc_s, 0u);
+          umma_commit(bar(g, AB_S_FULL));
+          umma_commit(bar(g, AB_QK_EMPTY));
+        }
       };
       if (my_items > 0) issue_s(0);
       if (ok && my_items > 1) issue_s(1);
@@ -956,17 +1033,34 @@ __device__ __forceinline__ void attn_stage_pp(const Stage& st, const CallArgs& c
         if (!mbar_wait(bar(g, AB_V_FULL), bit, ctl, 514 + g)) break;
         tc_fence_after_sync();
         // O = P V: K = 128 keys = two chunks of 64; V is an MN-major B operand (16 keys = 2048 B per step)
-        const uint32_t d = tmem + kPipeOCol + g * 64;
-        umma_f16_k64(d, umma_desc_lo(base + 3 * kATileBytes, 16), umma_desc_lo(base + 2 * kATileBytes, 8192), 128u, idesc_o, 0u);
-        umma_f16_k64(d, umma_desc_lo(base + 4 * kATileBytes, 16), umma_desc_lo(base + 2 * kATileBytes + 8192, 8192), 128u,
-                     idesc_o, 1u);
-        umma_commit(bar(g, AB_O_FULL));
-        umma_commit(bar(g, AB_V_EMPTY));
+        if constexpr (kPair) {
+          const uint32_t d = tmem + g * 256;                   // over the scores, which the softmax has consumed
+          umma_f16_k64_pair(d, umma_desc_lo(base + 3 * kATileBytes, 16), umma_desc_lo(base + 2 * kATileBytes, 8192), 128u, idesc_o, 0u);
+          umma_f16_k64_pair(d, umma_desc_lo(base + 4 * kATileBytes, 16), umma_desc_lo(base + 2 * kATileBytes + 8192, 8192), 128u,
+                            idesc_o, 1u);
+          umma_commit_pair(bar(g, AB_O_FULL));
+          umma_commit_pair(bar(g, AB_V_EMPTY));
+        } else {
+          const uint32_t d = tmem + kPipeOCol + g * 64;
+          umma_f16_k64(d, umma_desc_lo(base + 3 * kATileBytes, 16), umma_desc_lo(base + 2 * kATileBytes, 8192), 128u, idesc_o, 0u);
+          umma_f16_k64(d, umma_desc_lo(base + 4 * kATileBytes, 16), umma_desc_lo(base + 2 * kATileBytes + 8192, 8192), 128u,
+                       idesc_o, 1u);
+          umma_commit(bar(g, AB_O_FULL));
+          umma_commit(bar(g, AB_V_EMPTY));
+        }
         bits ^= 1u << g;
-        if (k + 2 < my_items) issue_s(k + 2);
+        if (k + 2 < my_items) {
+          if constexpr (kPair) {          // the next scores of this pipeline overwrite the output just issued: wait for its readers
+            if (!mbar_wait(oempty0 + 8 * g, (obits >> g) & 1u, ctl, 516 + g)) break;
+            tc_fence_after_sync();
+          }
+          issue_s(k + 2);
+        }
+        obits ^= 1u << g;                 // one phase of o_empty per item, waited for or not
       }
       rs.attn_bit = bits & 1u;
       rs.attn_bit1 = (bits >> 1) & 1u;
+      rs.o_bits = obits;
     }
     __syncwarp();
   } else {
@@ -985,14 +1079,14 @@ __device__ __forceinline__ void attn_stage_pp(const Stage& st, const CallArgs& c
     const bool prof = p.prof != nullptr;
     long long t_ws = 0, t_sm = 0, t_wo = 0, t_ep = 0, t_p1 = 0;
     for (int k = g; k < my_items; k += 2) {
-      const int item = blockIdx.x + k * gridDim.x;
+      const int item = item_of(k);
       const int h = item % H, b = item / H;
       const int kv_len = lens ? lens[b] : S;
       const long long c0 = prof ? clock64() : 0;
       if (!mbar_wait_warp(bar(g, AB_S_FULL), bit, ctl, 520 + g, lane)) break;
       const long long c1 = prof ? clock64() : 0;
       tc_fence_after_sync();
-      const uint32_t ts = tmem + g * 128;
+      const uint32_t ts = kPair ? tmem + g * 256 + rank * 128 : tmem + g * 128;
       // Masked keys (>= kv_len) get -10000 added, which underflows to probability 0 in fp32 and never wins
       // the maximum, so both passes only visit the 16-column blocks that hold valid keys.  TMEM loads are
       // double-buffered 16 columns at a time: the next block is in flight while this one is processed.
@@ -1080,7 +1174,12 @@ __device__ __forceinline__ void attn_stage_pp(const Stage& st, const CallArgs& c
       }
       fence_proxy_async_smem();
       tc_fence_before_sync();
-      mbar_arrive(bar(g, AB_P_FULL));
+      if constexpr (kPair) {                                  // one arrival per warp on the leader's barrier (8 in all)
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(map_shared_rank(bar(g, AB_P_FULL), 0));
+      } else {
+        mbar_arrive(bar(g, AB_P_FULL));
+      }
       const long long c2 = prof ? clock64() : 0;
       if (!mbar_wait_warp(bar(g, AB_O_FULL), bit, ctl, 522 + g, lane)) break;
       const long long c3 = prof ? clock64() : 0;
@@ -1092,7 +1191,7 @@ __device__ __forceinline__ void attn_stage_pp(const Stage& st, const CallArgs& c
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           uint32_t r[32];
-          tmem_ld32(tmem + kPipeOCol + g * 64 + half * 32, r);
+          tmem_ld32((kPair ? tmem + g * 256 + rank * 64 : tmem + kPipeOCol + g * 64) + half * 32, r);
           tmem_ld_wait(r);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -1106,6 +1205,10 @@ __device__ __forceinline__ void attn_stage_pp(const Stage& st, const CallArgs& c
         }
       }
       tc_fence_before_sync();
+      if constexpr (kPair) {                                  // this warp has read its rows of the output accumulator
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster_relaxed(map_shared_rank(oempty0 + 8 * g, 0));
+      }
       bit ^= 1u;
       if (prof) { const long long c4 = clock64(); t_ws += c1 - c0; t_sm += c2 - c1; t_wo += c3 - c2; t_ep += c4 - c3; t_p1 += c1a - c1; }
     }
@@ -1755,7 +1858,10 @@ __device__ __forceinline__ void ln_stage(const Stage& st, const MegaParams& p, S
 //                    384, and short sequences at small batch, where a CTA has at most one item anyway.
 //   kFamilySwin      adds the Swin row-permuting epilogues and the window-attention stage; its stages stay out
 //                    of line (inlined as well, the allocation would no longer fit).
-constexpr int kFamilyBert = 0, kFamilyBertCoop = 1, kFamilySwin = 2;
+//   kFamilyBertPair  kFamilyBert on CTA pairs: a cluster of two CTAs shares every MMA (cta_group::2), which halves the
+//                    weight-tile traffic per FLOP of the GEMM stages; the attention stage takes two heads per pair.
+//                    Launched with a cluster dimension of two.
+constexpr int kFamilyBert = 0, kFamilyBertCoop = 1, kFamilySwin = 2, kFamilyBertPair = 3;
 __device__ __noinline__ void gemm_stage_ool(const Stage& st, const CallArgs& ca, SmemCtl& ctl_s, uint32_t ring, __half* vec_s,
                                             uint8_t* stage_s, RoleState& rs, const WaitCtl& ctl, int warp, int lane) {
   gemm_stage<true>(st, ca, ctl_s, ring, vec_s, stage_s, rs, ctl, warp, lane);
@@ -1789,9 +1895,12 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
       mbar_init(smem_u32(&cs.full[i]), 1);
       mbar_init(smem_u32(&cs.empty[i]), 1);
     }
+    constexpr bool kPairK = kFamily == kFamilyBertPair;
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&cs.tmem_full[i]), 1);
-      mbar_init(smem_u32(&cs.tmem_empty[i]), kThreads - 64);
+      // arrivals of the epilogue: every thread, or (pairs) one per epilogue warp of both CTAs on the leader's barrier
+      mbar_init(smem_u32(&cs.tmem_empty[i]), kPairK ? 2 * (kThreads / 32 - 2) : kThreads - 64);
+      mbar_init(smem_u32(&cs.o_empty[i]), 8);
     }
     mbar_init(smem_u32(&cs.rec_full), 1);
     mbar_init(smem_u32(&cs.qk_full), 1);
@@ -1799,9 +1908,9 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
     mbar_init(smem_u32(&cs.v_full), 1);
     mbar_init(smem_u32(&cs.v_empty), 1);
     mbar_init(smem_u32(&cs.s_full), 1);
-    mbar_init(smem_u32(&cs.p_full), 128);
+    mbar_init(smem_u32(&cs.p_full), kPairK ? 8 : 128);         // softmax threads, or (pairs) the softmax warps of both CTAs
     mbar_init(smem_u32(&cs.o_full), 1);
-    for (int i = 0; i < 7; ++i) mbar_init(smem_u32(&cs.attn1[i]), i == 5 ? 128 : 1);
+    for (int i = 0; i < 7; ++i) mbar_init(smem_u32(&cs.attn1[i]), i == 5 ? (kPairK ? 8 : 128) : 1);
     for (int i = 0; i < 4; ++i) {
       mbar_init(smem_u32(&cs.ln_full[i]), 1);
       mbar_init(smem_u32(&cs.ln_empty[i]), kThreads / 32 - 1);
@@ -1814,12 +1923,17 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
       p.sync_next[1] = 0u;
     }
   }
-  if (warp == 1) tmem_alloc(smem_u32(&cs.tmem_base), kTmemCols);
+  if constexpr (kFamily == kFamilyBertPair) {
+    if (warp == 1) tmem_alloc_pair(smem_u32(&cs.tmem_base), kTmemCols);
+  } else {
+    if (warp == 1) tmem_alloc(smem_u32(&cs.tmem_base), kTmemCols);
+  }
   if (warp >= 2 && p.maps) {               // warm the descriptor cache while the CTA sets up
     for (int i = (int)threadIdx.x - 64; i < p.n_maps; i += kThreads - 64) tma_prefetch_desc(p.maps + i);
   }
   tc_fence_before_sync();
   __syncthreads();
+  if constexpr (kFamily == kFamilyBertPair) cluster_sync_all();     // the peer's barriers exist before anything arrives on them
   tc_fence_after_sync();
 
   WaitCtl ctl;
@@ -1850,9 +1964,10 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
       else if (st.type == STAGE_LN) ln_stage_ool(st, p, cs, ring, ring_ptr, vec_s, rs, ctl, warp, lane);
     } else {
       if (st.type == STAGE_GEMM) {
-        gemm_stage<false>(st, ca, cs, ring, vec_s, stage_s, rs, ctl, warp, lane);
+        gemm_stage<false, kFamily == kFamilyBertPair>(st, ca, cs, ring, vec_s, stage_s, rs, ctl, warp, lane);
       } else if (st.type == STAGE_ATTN) {
-        if constexpr (kFamily == kFamilyBert) attn_stage_pp(st, ca, cs, ring, ring_ptr, stage_s, rs, ctl, warp, lane);
+        if constexpr (kFamily == kFamilyBert) attn_stage_pp<false>(st, ca, cs, ring, ring_ptr, stage_s, rs, ctl, warp, lane);
+        else if constexpr (kFamily == kFamilyBertPair) attn_stage_pp<true>(st, ca, cs, ring, ring_ptr, stage_s, rs, ctl, warp, lane);
         else attn_stage(st, ca, cs, ring, ring_ptr, stage_s, rs, ctl, warp, lane);
       } else if (st.type == STAGE_LN) {
         ln_stage<false>(st, p, cs, ring, ring_ptr, vec_s, rs, ctl, warp, lane);
@@ -1882,7 +1997,12 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(cs.tmem_base, kTmemCols);
+  if constexpr (kFamily == kFamilyBertPair) {
+    cluster_sync_all();                    // both CTAs are done with the pair's tensor memory and with each other's barriers
+    if (warp == 1) tmem_dealloc_pair(cs.tmem_base, kTmemCols);
+  } else {
+    if (warp == 1) tmem_dealloc(cs.tmem_base, kTmemCols);
+  }
 }
 
 }  // namespace souffle

@@ -127,6 +127,10 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
                ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
                : "memory");
 }
+// Pulls `bytes` (a multiple of 16, 16-byte aligned) of global memory into L2; nothing is written anywhere else.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
@@ -224,6 +228,70 @@ __device__ __forceinline__ void umma_f16_k64_x2(uint32_t d0, uint32_t d1, uint32
 // Arrives on the mbarrier once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// ------------------------------------------------------------------------------------
+// CTA pairs (cta_group::2): two CTAs of a cluster of two share every MMA.  An MMA of M = 256 takes 128 rows of A and
+// N / 2 columns of B from the shared memory of each CTA (same offsets in both) and leaves rows 128 r .. 128 r + 127 of
+// the 256 x N result in the tensor memory of CTA r, so each CTA stores only half of every B tile.  One thread of
+// the leader CTA (cluster rank 0) issues for both.  All tcgen05 instructions of a kernel use one CTA group.
+// ------------------------------------------------------------------------------------
+// one warp of EACH CTA of the pair, the same shared-memory offset for the result in both
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {  // one warp of each CTA
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// Instruction descriptor of a pair MMA: M = 256 over the two CTAs, N over both halves of B.
+__device__ __forceinline__ uint32_t umma_idesc_f16_pair(uint32_t n, uint32_t b_mn_major) {
+  return (1u << 4) | (b_mn_major << 16) | ((n >> 3) << 17) | ((256u >> 4) << 24);
+}
+// One K chunk of 64 as four pair MMAs (see umma_f16_k64).
+__device__ __forceinline__ void umma_f16_k64_pair(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t bstep,
+                                                  uint32_t idesc, uint32_t acc0) {
+  asm volatile(
+      "{\n\t.reg .pred p, pt;\n\t.reg .b64 da, db;\n\t.reg .b32 al, bl;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
+      "mov.b64 da, {%1, %6};\n\tmov.b64 db, {%2, %6};\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p;\n\t"
+      "add.u32 al, %1, 2;\n\tadd.u32 bl, %2, %3;\n\tmov.b64 da, {al, %6};\n\tmov.b64 db, {bl, %6};\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, pt;\n\t"
+      "add.u32 al, al, 2;\n\tadd.u32 bl, bl, %3;\n\tmov.b64 da, {al, %6};\n\tmov.b64 db, {bl, %6};\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, pt;\n\t"
+      "add.u32 al, al, 2;\n\tadd.u32 bl, bl, %3;\n\tmov.b64 da, {al, %6};\n\tmov.b64 db, {bl, %6};\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, pt;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(bstep), "r"(idesc), "r"(acc0), "r"(kDescHiSw128)
+      : "memory");
+}
+// Arrives, once every pair MMA issued so far by this thread has completed, on the mbarrier at this shared-memory
+// offset in BOTH CTAs of the pair (the commit is multicast over the cluster; it carries no data).
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .b16 m;\n\tmov.b16 m, 3;\n\t"
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], m;\n\t}"
+      ::"r"(bar) : "memory");
+}
+// Tiled 2-D load into this CTA's shared memory whose completion is counted on an mbarrier of the pair's leader
+// (`bar` is a shared::cluster address, see map_shared_rank).  A plain load: nothing is multicast.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(tmap), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+// Arrival on an mbarrier of another CTA of the cluster (`bar` is a shared::cluster address).  The release form makes
+// the thread's earlier writes visible to whoever sees the phase complete -- and so waits for ALL of them, global
+// stores still in flight included (measured: ~1.7 k cycles after an epilogue's stores).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// The same arrival with the default (CTA-scope) release: for hand-shakes that only protect tensor memory, whose
+// reads tcgen05.fence::before_thread_sync has already ordered before the arrival; it does not wait for global stores.
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
 // 32 lanes x 32 columns of fp32: thread i of the warp receives lane (base+i), columns [col, col+32).
@@ -369,6 +437,33 @@ __device__ __forceinline__ uint32_t gelu_tanh_h2(uint32_t xw) {
   const __half2 hx = __hmul2(x, __float2half2_rn(0.5f));
   const __half2 y = __hfma2(hx, t, hx);
   return *reinterpret_cast<const uint32_t*>(&y);
+}
+// Sixteen pairs at once, step by step: each loop is sixteen independent operations (see epilogue_chunk32).
+__device__ __forceinline__ void gelu_tanh_h2x16(uint32_t (&w)[16]) {
+  const __half2 c0 = __float2half2_rn(0.7978845608028654f), c1 = __float2half2_rn(0.7978845608028654f * 0.044715f);
+  const __half2 half = __float2half2_rn(0.5f);
+  __half2 x[16], t[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) x[i] = *reinterpret_cast<const __half2*>(&w[i]);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) t[i] = __hmul2(x[i], x[i]);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) t[i] = __hfma2(t[i], c1, c0);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) t[i] = __hmul2(x[i], t[i]);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    uint32_t uw = *reinterpret_cast<const uint32_t*>(&t[i]), tw;
+    asm("tanh.approx.f16x2 %0, %1;" : "=r"(tw) : "r"(uw));
+    t[i] = *reinterpret_cast<const __half2*>(&tw);
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) x[i] = __hmul2(x[i], half);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const __half2 y = __hfma2(x[i], t[i], x[i]);
+    w[i] = *reinterpret_cast<const uint32_t*>(&y);
+  }
 }
 __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
   __half2 h = __floats2half2_rn(a, b);

@@ -185,11 +185,49 @@ static TileChoice choose_tiles(int M, int N, int K, int sms, bool allow_split, b
   return bt;
 }
 
+// The same for a plan on CTA pairs: a pair owns a 256 x bn tile, each CTA loads 128 rows of A and bn/2 rows of B per
+// K chunk and runs MMAs of bn/2 cycles; both accumulator buffers of a CTA alternate, so the epilogue overlaps.
+static TileChoice choose_tiles_pair(int M, int N, int K, int npairs, bool allow_split, std::vector<RankedTile>* ranked = nullptr) {
+  const int kch = K / 64;
+  double best = 1e300;
+  TileChoice bt;
+  bt.bm = 256;
+  const int cands[6] = {256, 192, 128, 96, 64, 32};
+  for (int ci = 0; ci < 6; ++ci) {
+    const int bn = cands[ci];
+    if (N % bn) continue;
+    for (int split = 1; split <= (allow_split ? 16 : 1); ++split) {
+      if (kch % split) continue;
+      const long items = (long)((M + 255) / 256) * (N / bn) * split;
+      const long waves = (items + npairs - 1) / npairs;
+      const double load = (16384.0 + 64.0 * bn) / 55.0, mma = 2.0 * bn;
+      const double chunk = 1.05 * (load > mma ? load : mma);
+      const double epilogue = 128.0 * bn * (allow_split ? 0.2 : 0.35);
+      const double tile = (kch / split) * chunk + 0.45 * epilogue + 1500.0;
+      double cost = waves * tile;
+      if (allow_split) cost += (double)split * M * N * 8.0 / (2.0 * npairs) / 12.0;
+      if (ranked) {
+        RankedTile r;
+        r.cost = cost; r.t.bm = 256; r.t.bn = bn; r.t.split = split;
+        ranked->push_back(r);
+      }
+      if (cost < best - 1e-9) {
+        best = cost;
+        bt.bn = bn; bt.split = split;
+      }
+    }
+  }
+  if (ranked) std::stable_sort(ranked->begin(), ranked->end(), [](const RankedTile& a, const RankedTile& b) { return a.cost < b.cost; });
+  return bt;
+}
+
 // ------------------------------------------------------------------------------------
 // launch helper shared by every entry point
 // ------------------------------------------------------------------------------------
 struct DeviceInfo {
   int device = -1, sms = 0, cc_major = 0, max_ctas = 0;
+  int max_pairs = 0;             // clusters of two CTAs of the pair build that can be resident at once
+  int pair_coop = 1;             // the pair launch still carries the cooperative attribute on top of the cluster dimension
   bool attr_set = false;
 };
 static DeviceInfo g_dev[16];
@@ -215,6 +253,28 @@ static int device_info(DeviceInfo** out) {
     }
     d.max_ctas = per_sm * d.sms;
     if (d.max_ctas < 1) return fail(SOUFFLE_NOT_CORESIDENT, "megakernel does not fit on an SM of device %d", dev);
+    {   // the build that runs on CTA pairs: how many clusters of two fit the device at once
+      const void* pf = (const void*)souffle_megakernel<kFamilyBertPair>;
+      SF_CUDA(cudaFuncSetAttribute(pf, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+      cudaLaunchConfig_t cfg;
+      cudaLaunchAttribute at[1];
+      memset(&cfg, 0, sizeof(cfg));
+      cfg.gridDim = dim3(2 * d.sms);
+      cfg.blockDim = dim3(kThreads);
+      cfg.dynamicSmemBytes = kSmemBytes;
+      at[0].id = cudaLaunchAttributeClusterDimension;
+      at[0].val.clusterDim.x = 2;
+      at[0].val.clusterDim.y = 1;
+      at[0].val.clusterDim.z = 1;
+      cfg.attrs = at;
+      cfg.numAttrs = 1;
+      int clusters = 0;
+      if (cudaOccupancyMaxActiveClusters(&clusters, pf, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        clusters = 0;
+      }
+      d.max_pairs = clusters;
+    }
     d.device = dev;
   }
   *out = &d;
@@ -226,6 +286,40 @@ static int launch_mega(const CallArgs& args_in, int grid, cudaStream_t stream, i
   CallArgs args = args_in;
   for (int i = 0; i < 3; ++i) args.inline_stages[i].prof_index = i;      // stages that travel in the launch parameters
   void* kargs[] = {&args};
+  if (family == kFamilyBertPair) {
+    // Clusters of two CTAs.  All CTAs must be resident at once (the grid barrier): the grid never exceeds what
+    // cudaOccupancyMaxActiveClusters reported, every device-side wait is bounded, and the cooperative attribute
+    // adds the driver's own check where it accepts the combination (SOUFFLE_PAIR_COOPERATIVE=0 leaves it out:
+    // Nsight Compute cannot capture a launch that carries both attributes).
+    DeviceInfo* di = nullptr;
+    int rc = device_info(&di);
+    if (rc) return rc;
+    static const bool env_coop = []() { const char* e = getenv("SOUFFLE_PAIR_COOPERATIVE"); return !(e && e[0] == '0'); }();
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute at[2];
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = kSmemBytes;
+    cfg.stream = stream;
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    at[1].id = cudaLaunchAttributeCooperative;
+    at[1].val.cooperative = 1;
+    cfg.attrs = at;
+    const void* fn = (const void*)souffle_megakernel<kFamilyBertPair>;
+    if (env_coop && di->pair_coop) {
+      cfg.numAttrs = 2;
+      if (cudaLaunchKernelExC(&cfg, fn, kargs) == cudaSuccess) return SOUFFLE_OK;
+      cudaGetLastError();          // a refused launch configuration is not sticky
+      di->pair_coop = 0;
+    }
+    cfg.numAttrs = 1;
+    SF_CUDA(cudaLaunchKernelExC(&cfg, fn, kargs));
+    return SOUFFLE_OK;
+  }
   const void* fn = family == kFamilySwin ? (const void*)souffle_megakernel<kFamilySwin>
                    : family == kFamilyBertCoop ? (const void*)souffle_megakernel<kFamilyBertCoop>
                                                : (const void*)souffle_megakernel<kFamilyBert>;
@@ -233,8 +327,10 @@ static int launch_mega(const CallArgs& args_in, int grid, cudaStream_t stream, i
   return SOUFFLE_OK;
 }
 
-static int stage_items(const Stage& s) {
+// Work items of a stage; for a plan on CTA pairs GEMM tiles and attention couples are per PAIR (bm = 256).
+static int stage_items(const Stage& s, bool pair = false) {
   if (s.type == STAGE_GEMM) return ((s.M + s.bm - 1) / s.bm) * (s.N / s.bn) * s.splitk;
+  if (s.type == STAGE_ATTN && pair) return s.batch * s.heads / 2;
   if (s.type == STAGE_ATTN) return s.batch * s.heads * ((s.seq + 127) / 128);
   if (s.type == STAGE_ATTN_SWIN) return s.batch * (s.seq / s.win) * (s.seq / s.win) * s.heads;
   return (s.M + kThreads / 32 - 2) / (kThreads / 32 - 1);       // one row per normalising warp (all warps but the first)
@@ -242,7 +338,7 @@ static int stage_items(const Stage& s) {
 
 // Fills the derived fields of a GEMM stage (tile counts, ring geometry, magic divisors) and checks that its
 // output fits the kernel's 32-bit element offsets.
-static int finalize_stage(Stage& s, int max_slots, int grid) {
+static int finalize_stage(Stage& s, int max_slots, int grid, bool pair = false) {
   if (s.type == STAGE_LN) {
     // Rows per batch: up to 96 KB (two batches in flight), at most two rows per normalising warp, and few
     // enough that every CTA gets work.  The per-column vectors are staged in shared memory when a CTA
@@ -259,7 +355,7 @@ static int finalize_stage(Stage& s, int max_slots, int grid) {
     s.slot_bytes = rb * row_bytes;
     s.nslots = 196608 / s.slot_bytes > 4 ? 4 : 196608 / s.slot_bytes;
     s.items = (s.M + rb - 1) / rb;
-    s.kchunks = (3 * s.N * 2 <= 8192) ? 1 : 0;
+    s.kchunks = (3 * s.N * 2 <= kVecBytes) ? 1 : 0;
     // At most one row per normalising warp and CTA: the warps read their rows themselves (no staging ring).
     if (per_cta <= comp && s.seq == 0 && s.N <= 1024) {
       s.bm = per_cta;
@@ -272,10 +368,13 @@ static int finalize_stage(Stage& s, int max_slots, int grid) {
     return SOUFFLE_OK;
   }
   if (s.type != STAGE_GEMM) return SOUFFLE_OK;
+  if (s.bias && s.epi != EPI_PARTIAL && s.N * 4 > kVecBytes)
+    return fail(SOUFFLE_BAD_SHAPE, "a GEMM stage with a bias vector is limited to %d output columns (got %d)", kVecBytes / 4, s.N);
   s.tiles_n = s.N / s.bn;
   s.kchunks = s.K / 64 / s.splitk;
   s.items = stage_items(s);
-  s.slot_bytes = (s.bm / 128) * 16384 + s.bn * 128;
+  // per CTA and K chunk: the A rows (all of the tile's, or one 128-row half of a pair's) and the B rows (all, or half)
+  s.slot_bytes = pair ? 16384 + s.bn * 64 : (s.bm / 128) * 16384 + s.bn * 128;
   int n = 196608 / s.slot_bytes;
   if (n > 8) n = 8;
   if (max_slots > 0 && n > max_slots) n = max_slots;
@@ -308,9 +407,11 @@ using namespace souffle;
 struct SouffleBertPlan {
   SouffleBertDesc desc;
   int device = 0, grid = 0, launches = 0;
-  int family = 0;                // which build of the kernel runs this plan (kFamilyBert / kFamilyBertCoop)
+  int family = 0;                // which build of the kernel runs this plan (kFamilyBert / kFamilyBertCoop / kFamilyBertPair)
+  bool pair = false;             // the plan runs on CTA pairs: 256-row tiles, half a B tile per CTA
   unsigned launch_id = 0;
   std::vector<Stage> stages;
+  std::vector<const void*> stage_weights;   // per stage: the repacked [N][K] weight matrix of a GEMM stage, else null
   std::vector<CUtensorMap> maps;
   std::vector<void*> allocs;
   Stage* d_stages = nullptr;
@@ -342,7 +443,18 @@ static int plan_alloc(SouffleBertPlan* p, void** ptr, size_t bytes);
 // Numbers the stages and copies the program and its tensor maps to the device.
 static int upload_program(SouffleBertPlan* p) {
   int rc;
-  for (size_t i = 0; i < p->stages.size(); ++i) p->stages[i].prof_index = (int)i;
+  for (size_t i = 0; i < p->stages.size(); ++i) {
+    Stage& s = p->stages[i];
+    s.prof_index = (int)i;
+    // the weights of the GEMM stage after next are prefetched into L2 at the barrier that ends this stage
+    s.pf_ptr = nullptr;
+    s.pf_bytes = 0;
+    if (i + 2 < p->stages.size() && p->stages[i + 2].type == STAGE_GEMM && p->stage_weights.size() > i + 2 && p->stage_weights[i + 2]) {
+      const Stage& g = p->stages[i + 2];
+      s.pf_ptr = p->stage_weights[i + 2];
+      s.pf_bytes = (uint32_t)((size_t)g.N * g.K * 2) & ~15u;
+    }
+  }
   if ((rc = plan_alloc(p, (void**)&p->d_stages, p->stages.size() * sizeof(Stage)))) return rc;
   if ((rc = plan_alloc(p, (void**)&p->d_maps, p->maps.size() * sizeof(CUtensorMap)))) return rc;
   SF_CUDA(cudaMemcpy(p->d_stages, p->stages.data(), p->stages.size() * sizeof(Stage), cudaMemcpyHostToDevice));
@@ -367,6 +479,12 @@ static int add_map(SouffleBertPlan* p, const void* ptr, uint64_t rows, uint64_t 
   return SOUFFLE_OK;
 }
 
+// Remembers the weight matrix of the stage just appended (for the L2 prefetch, see upload_program).
+static void note_weights(SouffleBertPlan* p, const void* w) {
+  p->stage_weights.resize(p->stages.size(), nullptr);
+  p->stage_weights.back() = w;
+}
+
 static Stage blank_stage(int type) {
   Stage s;
   memset(&s, 0, sizeof(s));
@@ -383,9 +501,10 @@ static Stage blank_stage(int type) {
 // that writes split-K planes is timed together with the LayerNorm stage that sums them (`ln_proto`), since more
 // planes make that one slower.  Failures of any kind leave `*choice` as the cycle model set it.
 static void autotune_gemm(const Stage& proto, const Stage* ln_proto, const void* a, const void* w, int sms, bool allow_split,
-                          int head_split, int max_split, void* tune_ws, TileChoice* choice) {
+                          int head_split, int max_split, void* tune_ws, TileChoice* choice, bool pair = false) {
   std::vector<RankedTile> ranked;
-  choose_tiles(proto.M, proto.N, proto.K, sms, allow_split, false, head_split, &ranked);
+  if (pair) choose_tiles_pair(proto.M, proto.N, proto.K, sms / 2, allow_split, &ranked);
+  else choose_tiles(proto.M, proto.N, proto.K, sms, allow_split, false, head_split, &ranked);
   cudaEvent_t e0 = nullptr, e1 = nullptr;
   if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) return;
   float best_ms = 1e30f;
@@ -398,10 +517,10 @@ static void autotune_gemm(const Stage& proto, const Stage* ln_proto, const void*
     Stage& g = args.inline_stages[0];
     g = proto;
     g.tm_a = -1; g.tm_b = -2; g.bm = t.bm; g.bn = t.bn; g.splitk = t.split;
-    if (finalize_stage(g, 0, 1)) continue;
-    if (make_map_uncached(&args.call_maps[0], a, (uint64_t)proto.M, (uint64_t)proto.K, (uint32_t)t.bm)) continue;
-    if (make_map_uncached(&args.call_maps[1], w, (uint64_t)proto.N, (uint64_t)proto.K, (uint32_t)t.bn)) continue;
-    int items = stage_items(g);
+    if (finalize_stage(g, 0, 1, pair)) continue;
+    if (make_map_uncached(&args.call_maps[0], a, (uint64_t)proto.M, (uint64_t)proto.K, (uint32_t)(pair ? 128 : t.bm))) continue;
+    if (make_map_uncached(&args.call_maps[1], w, (uint64_t)proto.N, (uint64_t)proto.K, (uint32_t)(pair ? t.bn / 2 : t.bn))) continue;
+    int items = stage_items(g) * (pair ? 2 : 1);                // CTAs that have work
     args.p.n_stages = 1;
     if (ln_proto) {
       Stage& ln = args.inline_stages[1];
@@ -411,7 +530,7 @@ static void autotune_gemm(const Stage& proto, const Stage* ln_proto, const void*
       if (li > items) items = li;
       args.p.n_stages = 2;
     }
-    const int grid = items < sms ? items : sms;
+    const int grid = items < sms ? items : sms;                 // even for pairs: items and sms both are
     if (ln_proto && finalize_stage(args.inline_stages[1], 0, grid)) continue;
     args.p.sync = reinterpret_cast<unsigned*>(tune_ws);
     args.p.sync_next = args.p.sync + 2;
@@ -421,7 +540,7 @@ static void autotune_gemm(const Stage& proto, const Stage* ln_proto, const void*
     for (int it = 0; it < 26 && ok; ++it) {                // two warm-up launches, twenty-four timed ones
       ok = cudaMemsetAsync(tune_ws, 0, 128, nullptr) == cudaSuccess;
       if (it == 2) ok = ok && cudaEventRecord(e0, nullptr) == cudaSuccess;
-      ok = ok && launch_mega(args, grid, nullptr, kFamilyBert) == SOUFFLE_OK;
+      ok = ok && launch_mega(args, grid, nullptr, pair ? kFamilyBertPair : kFamilyBert) == SOUFFLE_OK;
     }
     float ms = 0.0f;
     int h[4] = {0, 0, 0, 0};
@@ -454,6 +573,13 @@ static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* la
   int sms = di->sms;
   if (d.max_ctas > 0 && d.max_ctas < sms) sms = d.max_ctas;
   if (sms > di->max_ctas) sms = di->max_ctas;
+  // CTA pairs (opt-in): for shapes whose GEMM stages have many tiles per CTA and whose attention stage has more
+  // (sequence, head) items than CTAs (its two-pipeline form, which the pair build has; the one-item form exists for
+  // single CTAs only)
+  int npairs = sms / 2 < di->max_pairs ? sms / 2 : di->max_pairs;
+  const bool pair = d.pair_mma == 1 && npairs >= 1 && S <= 128 && Hh % 2 == 0 && B * Hh > sms && M >= 2048;
+  p->pair = pair;
+  if (pair) sms = 2 * npairs;
 
   // ---- buffers ----
   if ((rc = plan_alloc(p, (void**)&p->qkv, (size_t)3 * M * H * 2))) return rc;
@@ -475,6 +601,12 @@ static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* la
   // ---- tiling ----
   TileChoice t_qkv = choose_tiles(M, 3 * H, H, sms, false, false, 1), t_fc1 = choose_tiles(M, F, H, sms, false, false),
              t_proj = choose_tiles(M, H, H, sms, true, false), t_fc2 = choose_tiles(M, H, F, sms, true, false);
+  if (pair) {
+    t_qkv = choose_tiles_pair(M, 3 * H, H, npairs, false);
+    t_fc1 = choose_tiles_pair(M, F, H, npairs, false);
+    t_proj = choose_tiles_pair(M, H, H, npairs, true);
+    t_fc2 = choose_tiles_pair(M, H, F, npairs, true);
+  }
   if (d.bm_qkv) t_qkv.bm = d.bm_qkv;
   if (d.bn_qkv) t_qkv.bn = d.bn_qkv;
   if (d.bm_fc1) t_fc1.bm = d.bm_fc1;
@@ -502,22 +634,22 @@ static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* la
       if (!d.bm_qkv && !d.bn_qkv) {
         Stage q = g;
         q.N = 3 * H; q.K = H; q.epi = EPI_QKV; q.out = p->qkv; q.ldo = H;
-        autotune_gemm(q, nullptr, p->ln1, w_tmp, sms, false, 1, 1, tune_ws, &t_qkv);
+        autotune_gemm(q, nullptr, p->ln1, w_tmp, sms, false, 1, 1, tune_ws, &t_qkv, pair);
       }
       if (!d.bm_fc1 && !d.bn_fc1) {
         Stage f = g;
         f.N = F; f.K = H; f.epi = EPI_F16; f.act = std_variant ? ACT_GELU : ACT_RELU; f.out = p->fc1; f.ldo = F;
-        autotune_gemm(f, nullptr, p->ln1, w_tmp, sms, false, 0, 1, tune_ws, &t_fc1);
+        autotune_gemm(f, nullptr, p->ln1, w_tmp, sms, false, 0, 1, tune_ws, &t_fc1, pair);
       }
       if (!d.bm_proj && !d.bn_proj && !d.split_proj) {
         Stage f = g;
         f.N = H; f.K = H; f.epi = EPI_PARTIAL; f.partial = reinterpret_cast<float*>(planes); f.ldo = H;
-        autotune_gemm(f, &ln, p->ctx, w_tmp, sms, true, 0, max_split, tune_ws, &t_proj);
+        autotune_gemm(f, &ln, p->ctx, w_tmp, sms, true, 0, max_split, tune_ws, &t_proj, pair);
       }
       if (!d.bm_fc2 && !d.bn_fc2 && !d.split_fc2) {
         Stage f = g;
         f.N = H; f.K = F; f.epi = EPI_PARTIAL; f.partial = reinterpret_cast<float*>(planes); f.ldo = H;
-        autotune_gemm(f, &ln, p->fc1, w_tmp, sms, true, 0, max_split, tune_ws, &t_fc2);
+        autotune_gemm(f, &ln, p->fc1, w_tmp, sms, true, 0, max_split, tune_ws, &t_fc2, pair);
       }
     }
     cudaDeviceSynchronize();
@@ -526,7 +658,9 @@ static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* la
     if (planes) cudaFree(planes);
     if (tune_ws) cudaFree(tune_ws);
   }
-  auto bad_tile = [](const TileChoice& t, int N) {
+  if (pair) t_qkv.bm = t_fc1.bm = t_proj.bm = t_fc2.bm = 256;      // a pair's tile is 256 rows: 128 per CTA
+  auto bad_tile = [pair](const TileChoice& t, int N) {
+    if (pair) return t.bn < 32 || t.bn > 256 || t.bn % 32 || N % t.bn;     // each CTA holds bn / 2 rows of the B tile
     return (t.bm != 128 && t.bm != 256) || t.bn < 16 || t.bn > 256 || t.bn % 16 || N % t.bn ||
            196608 / ((t.bm + t.bn) * 128) < 2;
   };
@@ -541,15 +675,19 @@ static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* la
             sp_fc2 = t_fc2.split;
   const int max_split = sp_proj > sp_fc2 ? sp_proj : sp_fc2;
   if ((rc = plan_alloc(p, (void**)&p->partial, (size_t)max_split * M * H * 4))) return rc;
-  p->x_box_rows = t_qkv.bm;
+  // rows of an A box: the tile's height, or one CTA's 128-row half of a pair's tile; rows of a B box: the tile's
+  // width, or one CTA's half of it
+  auto a_rows = [pair](const TileChoice& t) { return (uint32_t)(pair ? 128 : t.bm); };
+  auto b_rows = [pair](int bn) { return (uint32_t)(pair ? bn / 2 : bn); };
+  p->x_box_rows = (int)a_rows(t_qkv);
 
   // ---- activation maps (A operands, box 64 x 128) ----
   int m_ctx, m_ln1, m_fc1, m_act[2] = {-1, -1}, m_qkv;
-  if ((rc = add_map(p, p->ctx, M, H, t_proj.bm, &m_ctx))) return rc;
-  if ((rc = add_map(p, p->ln1, M, H, t_fc1.bm, &m_ln1))) return rc;
-  if ((rc = add_map(p, p->fc1, M, F, t_fc2.bm, &m_fc1))) return rc;
+  if ((rc = add_map(p, p->ctx, M, H, a_rows(t_proj), &m_ctx))) return rc;
+  if ((rc = add_map(p, p->ln1, M, H, a_rows(t_fc1), &m_ln1))) return rc;
+  if ((rc = add_map(p, p->fc1, M, F, a_rows(t_fc2), &m_fc1))) return rc;
   for (int i = 0; i < 2; ++i)
-    if (p->act[i] && (rc = add_map(p, p->act[i], M, H, t_qkv.bm, &m_act[i]))) return rc;
+    if (p->act[i] && (rc = add_map(p, p->act[i], M, H, a_rows(t_qkv), &m_act[i]))) return rc;
   if ((rc = add_map(p, p->qkv, (uint64_t)3 * B * Hh * S, hd, 128, &m_qkv))) return rc;
 
   // ---- per layer: repack weights, maps, stages ----
@@ -595,10 +733,10 @@ static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* la
       return fail(SOUFFLE_BAD_ARGUMENT, "layer %d: gamma and beta must be given together", l);
 
     int m_wqkv, m_wo, m_w1, m_w2;
-    if ((rc = add_map(p, wqkv_t, 3 * H, H, bn_qkv, &m_wqkv))) return rc;
-    if ((rc = add_map(p, wo_t, H, H, bn_proj, &m_wo))) return rc;
-    if ((rc = add_map(p, w1_t, F, H, bn_fc1, &m_w1))) return rc;
-    if ((rc = add_map(p, w2_t, H, F, bn_fc2, &m_w2))) return rc;
+    if ((rc = add_map(p, wqkv_t, 3 * H, H, b_rows(bn_qkv), &m_wqkv))) return rc;
+    if ((rc = add_map(p, wo_t, H, H, b_rows(bn_proj), &m_wo))) return rc;
+    if ((rc = add_map(p, w1_t, F, H, b_rows(bn_fc1), &m_w1))) return rc;
+    if ((rc = add_map(p, w2_t, H, F, b_rows(bn_fc2), &m_w2))) return rc;
 
     // layer input / output routing
     const bool first = l == 0, last = l == L - 1;
@@ -612,6 +750,7 @@ static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* la
     s.tm_a = in_map; s.tm_b = m_wqkv; s.M = M; s.N = 3 * H; s.K = H; s.bm = t_qkv.bm; s.bn = bn_qkv;
     s.epi = EPI_QKV; s.bias = qkv_b; s.out = p->qkv; s.batch = B; s.heads = Hh; s.seq = S; s.head_dim = hd;
     p->stages.push_back(s);
+    note_weights(p, wqkv_t);
 
     s = blank_stage(STAGE_ATTN);                       // softmax(QK^T) V
     s.tm_qkv = m_qkv; s.batch = B; s.heads = Hh; s.seq = S; s.head_dim = hd; s.scale = scale;
@@ -622,6 +761,7 @@ static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* la
     s.tm_a = m_ctx; s.tm_b = m_wo; s.M = M; s.N = H; s.K = H; s.bm = t_proj.bm; s.bn = bn_proj; s.splitk = sp_proj;
     s.epi = EPI_PARTIAL; s.partial = p->partial;
     p->stages.push_back(s);
+    note_weights(p, wo_t);
 
     s = blank_stage(STAGE_LN);                         // + bias + residual, LayerNorm 1
     s.M = M; s.N = H; s.ldo = H; s.partial = p->partial; s.n_partial = sp_proj; s.bias = proj_b;
@@ -632,11 +772,13 @@ static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* la
     s.tm_a = m_ln1; s.tm_b = m_w1; s.M = M; s.N = F; s.K = H; s.bm = t_fc1.bm; s.bn = bn_fc1;
     s.epi = EPI_F16; s.act = std_variant ? ACT_GELU : ACT_RELU; s.bias = fc1_b; s.out = p->fc1; s.ldo = F;
     p->stages.push_back(s);
+    note_weights(p, w1_t);
 
     s = blank_stage(STAGE_GEMM);                       // FC2 -> fp32 partials
     s.tm_a = m_fc1; s.tm_b = m_w2; s.M = M; s.N = H; s.K = F; s.bm = t_fc2.bm; s.bn = bn_fc2; s.splitk = sp_fc2;
     s.epi = EPI_PARTIAL; s.partial = p->partial;
     p->stages.push_back(s);
+    note_weights(p, w2_t);
 
     s = blank_stage(STAGE_LN);                         // + bias + residual, LayerNorm 2
     s.M = M; s.N = H; s.ldo = H; s.partial = p->partial; s.n_partial = sp_fc2; s.bias = fc2_b;
@@ -648,10 +790,11 @@ static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* la
 
   int max_items = 1;
   for (const Stage& s : p->stages) {
-    const int it = stage_items(s);
+    const int it = stage_items(s, pair) * ((pair && s.type != STAGE_LN) ? 2 : 1);      // CTAs that have work
     if (it > max_items) max_items = it;
   }
   p->grid = max_items < sms ? max_items : sms;
+  if (pair) p->grid &= ~1;
 
   if (d.profile) {
     const size_t pb = (p->stages.size() + 1) * (size_t)p->grid * kProfSlots * sizeof(long long);
@@ -659,9 +802,9 @@ static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* la
     SF_CUDA(cudaMemset(p->d_prof, 0, pb));
   }
   // one attention item per CTA at most, or a long sequence: the stage in which all softmax warps share an item
-  p->family = (d.seq > 128 || d.batch * d.heads <= p->grid) ? kFamilyBertCoop : kFamilyBert;
+  p->family = pair ? kFamilyBertPair : (d.seq > 128 || d.batch * d.heads <= p->grid) ? kFamilyBertCoop : kFamilyBert;
   for (Stage& fs : p->stages)
-    if ((rc = finalize_stage(fs, p->desc.debug_max_slots, p->grid))) return rc;
+    if ((rc = finalize_stage(fs, p->desc.debug_max_slots, p->grid, pair))) return rc;
   return upload_program(p);
 }
 
@@ -871,6 +1014,8 @@ int souffle_bert_plan_info(SouffleBertPlan* plan, int* launches_out, int* grid_o
   return SOUFFLE_OK;
 }
 
+int souffle_bert_plan_uses_pairs(SouffleBertPlan* plan) { return plan && plan->pair ? 1 : 0; }
+
 int souffle_bert_packed_weights(const void* blob, int32_t batch, int32_t seq, int32_t hidden, int32_t ffn,
                                 SouffleBertLayerWeights* out, const void** mask_out, size_t* blob_bytes) {
   if (batch < 1 || seq < 1 || hidden < 8 || hidden % 8 || ffn < 8 || ffn % 8)
@@ -904,9 +1049,8 @@ int souffle_bert_plan_stage_info(SouffleBertPlan* plan, int index, int out[6]) {
   if (!plan || !out) return fail(SOUFFLE_BAD_ARGUMENT, "null argument");
   if (index < 0 || index >= (int)plan->stages.size()) return fail(SOUFFLE_BAD_ARGUMENT, "stage index %d out of range", index);
   const Stage& s = plan->stages[index];
-  out[0] = s.type; out[1] = s.bm; out[2] = s.bn; out[3] = s.splitk; out[4] = stage_items(s);
-  const int slot = (s.bm == 256 ? 2 : 1) * 16384 + s.bn * 128;
-  out[5] = s.type == STAGE_GEMM ? (196608 / slot > 8 ? 8 : 196608 / slot) : 0;
+  out[0] = s.type; out[1] = s.bm; out[2] = s.bn; out[3] = s.splitk; out[4] = stage_items(s, plan->pair);
+  out[5] = s.type == STAGE_GEMM ? s.nslots : 0;
   return SOUFFLE_OK;
 }
 
@@ -1206,6 +1350,7 @@ static int build_swin_plan(SouffleSwinPlan* sp, const SouffleSwinWeights* blocks
     s.tm_a = m_y1; s.tm_b = m_wqkv; s.M = T; s.N = 3 * C; s.K = C; s.bm = t_qkv.bm; s.bn = t_qkv.bn; s.epi = EPI_SWIN_QKV;
     s.bias = qkv_b; s.out = qkvw; s.ldo = C; s.batch = d.batch; s.heads = Hh; s.head_dim = 32; s.seq = R; s.win = ws; s.shift = shift;
     p->stages.push_back(s);
+    note_weights(p, wqkv_t);
     s = blank_stage(STAGE_ATTN_SWIN);                      // window attention
     s.tm_qkv = m_qkv; s.batch = d.batch; s.heads = Hh; s.head_dim = 32; s.seq = R; s.win = ws; s.shift = shift; s.ldo = C;
     s.scale = 1.0f / sqrtf(32.0f); s.rel_bias = relb; s.out = ctxw;
@@ -1215,6 +1360,7 @@ static int build_swin_plan(SouffleSwinPlan* sp, const SouffleSwinWeights* blocks
     s.bias = proj_b; s.resid_sel = in_sel; s.resid = xin; s.out = x1; s.ldo = C; s.batch = d.batch; s.heads = Hh; s.head_dim = 32;
     s.seq = R; s.win = ws; s.shift = shift;
     p->stages.push_back(s);
+    note_weights(p, wo_t);
     s = blank_stage(STAGE_LN);                             // LN2(x1)
     s.M = T; s.N = C; s.ldo = C; s.n_partial = 0; s.resid = x1; s.out = y2; s.gamma = ln2_g; s.beta = ln2_b; s.eps = d.eps;
     p->stages.push_back(s);
@@ -1222,10 +1368,12 @@ static int build_swin_plan(SouffleSwinPlan* sp, const SouffleSwinWeights* blocks
     s.tm_a = m_y2; s.tm_b = m_w1; s.M = T; s.N = F; s.K = C; s.bm = t_fc1.bm; s.bn = t_fc1.bn; s.epi = EPI_F16; s.act = ACT_GELU;
     s.bias = fc1_b; s.out = hid; s.ldo = F;
     p->stages.push_back(s);
+    note_weights(p, w1_t);
     s = blank_stage(STAGE_GEMM);                           // FC2 -> fp32 planes
     s.tm_a = m_hid; s.tm_b = m_w2; s.M = T; s.N = C; s.K = F; s.bm = t_fc2.bm; s.bn = t_fc2.bn; s.splitk = t_fc2.split;
     s.epi = EPI_PARTIAL; s.partial = planes; s.ldo = C;
     p->stages.push_back(s);
+    note_weights(p, w2_t);
     s = blank_stage(STAGE_LN);                             // planes + bias + x1 -> block output (no normalisation)
     s.M = T; s.N = C; s.ldo = C; s.partial = planes; s.n_partial = t_fc2.split; s.bias = fc2_b; s.resid = x1; s.eps = -1.0f;
     if (last && !sp->has_merge) s.out_sel = PTR_CALL_Y; else s.out = last ? xlast : xbuf[bi & 1];
@@ -1257,6 +1405,7 @@ static int build_swin_plan(SouffleSwinPlan* sp, const SouffleSwinWeights* blocks
     s.tm_a = m_merged; s.tm_b = m_wr; s.M = Tm; s.N = C2; s.K = C4; s.bm = t_red.bm; s.bn = t_red.bn; s.splitk = t_red.split;
     s.epi = EPI_PARTIAL; s.partial = planes2; s.ldo = C2;
     p->stages.push_back(s);
+    note_weights(p, wr_t);
     s = blank_stage(STAGE_LN);                               // sum of the planes -> y
     s.M = Tm; s.N = C2; s.ldo = C2; s.partial = planes2; s.n_partial = t_red.split; s.eps = -1.0f; s.out_sel = PTR_CALL_Y;
     p->stages.push_back(s);

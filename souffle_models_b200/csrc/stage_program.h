@@ -64,6 +64,10 @@ struct alignas(16) Stage {      // 16-byte multiples: records are fetched with b
   float eps;
   int n_partial;     // number of fp32 partial planes to sum
   int prof_index;    // position of this stage in the program (set by the host when the program is built)
+  // ---- weight prefetch: the B matrix of the GEMM stage two stages further on, pulled into L2 by all CTAs while
+  //      they wait at the barrier that ends this stage (weights never depend on an earlier stage) ----
+  uint32_t pf_bytes;
+  const void* pf_ptr;
   // ---- derived on the host by finalize_stage(): the kernel's lone producer / MMA lanes would otherwise
   //      spend a few thousand cycles per stage in integer divisions ----
   int tiles_n, kchunks, items, slot_bytes, nslots;

@@ -36,7 +36,7 @@ def test_every_declared_symbol_is_exported_and_bound():
 
 
 def test_struct_layout_matches_header():
-    assert C.sizeof(_lib.BertDesc) == 4 * 25
+    assert C.sizeof(_lib.BertDesc) == 4 * 26
     assert C.sizeof(_lib.BertLayerWeights) == 8 * 12
     assert C.sizeof(_lib.LstmDesc) == 4 * 5
     assert C.sizeof(_lib.SwinDesc) == 4 * 11 and C.sizeof(_lib.SwinWeights) == 8 * 13
@@ -81,11 +81,11 @@ def test_persistent_kernels_do_not_spill():
     lstm = {k: v for k, v in usage.items() if "souffle_lstm_wavefront" in k}
     stages = {k: v for k, v in usage.items() if any(n in k for n in ("gemm_stage_ool", "ln_stage_ool", "attn_swin_stage",
                                                                      "ln_row_wide", "ln_gather_rows", "ln_stage_direct", "attn_store_probs", "attn_copy_probs"))}
-    assert len(mega) == 3 and lstm and len(stages) == 8
+    assert len(mega) == 4 and lstm and len(stages) == 8
     for k, (regs, st, ld) in {**mega, **lstm, **stages}.items():
-        # The build whose stages are out of line (ILi2E) may keep a few words of its per-stage dispatcher on the
-        # stack across the calls: that code runs once per stage, the stage functions themselves must stay clean.
-        limit = 32 if "souffle_megakernelILi2E" in k else 0
+        # A kernel may keep a few words of its per-stage dispatcher on the stack across its calls of out-of-line
+        # functions: that code runs once per stage.  The stage functions themselves must stay clean.
+        limit = 32 if "souffle_megakernel" in k else 0
         assert st <= limit and ld <= limit, f"{k} spills ({st} B stores, {ld} B loads, {regs} registers)"
     assert all(v[0] <= 168 for v in mega.values())    # 320 threads per CTA leave 168 registers per thread
 

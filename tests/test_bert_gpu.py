@@ -137,6 +137,34 @@ def test_full_size_batch64_all_sequences():
     assert (got - want).pow(2).mean().sqrt() < 2e-3
 
 
+def test_cta_pair_plan_matches_the_oracle_and_the_single_cta_plan():
+    """Plans on CTA pairs (cta_group::2 MMAs: 256-row tiles shared by the two CTAs of a cluster, two heads per pair in
+    the attention stage; opt-in through desc.pair_mma): every stage output against the oracle, and the layer output
+    against the default single-CTA plan."""
+    cfg = so.BertConfig(20, 128, 12, 64, 3072, "std")
+    enc, layers, x, lens, y = _run(cfg, 1241, ragged=True, zero_bias=False, keep_probs=True, tuning=dict(pair_mma=1))
+    assert enc.info()["pairs"] == 1 and enc.stage_info(0)["bm"] == 256
+    r = so.bert_layer(cfg, x, layers[0], lens)
+    for k in ("qkv", "probs", "ctx", "ln1", "fc1"):
+        assert _err(enc.buffer(k), r[k]) < TOL_LAYER, k
+    assert _err(y, r["out"]) < TOL_LAYER
+    single, _, _, _, y1 = _run(cfg, 1241, ragged=True, zero_bias=False)
+    assert single.info()["pairs"] == 0
+    assert (y - y1).abs().max() < 4e-3
+    # explicit pair tilings: narrow and wide tiles, split-K
+    _, _, _, _, y2 = _run(cfg, 1241, ragged=True, zero_bias=False,
+                          tuning=dict(pair_mma=1, bn_qkv=96, bn_fc1=64, bn_proj=32, split_proj=2, bn_fc2=256, split_fc2=3))
+    assert (y2 - y1).abs().max() < 4e-3
+    y_again = enc.forward(x.cuda(), lens.cuda()).float().cpu().reshape(y.shape)
+    enc.status()
+    assert torch.equal(y, y_again)
+    # a chain of layers at the benchmark batch on pairs (the attention phases of the barriers carry over from layer to layer)
+    cfg64 = so.BertConfig(64, 128, 12, 64, 3072, "std")
+    enc64, layers64, x64, lens64, y64 = _run(cfg64, 1242, n_layers=3, ragged=True, tuning=dict(pair_mma=1))
+    assert enc64.info()["pairs"] == 1
+    assert _err(y64, so.bert_stack(cfg64, x64, layers64, lens64)) < TOL_LAYER
+
+
 def test_tile_overrides_agree():
     """Different tilings / split-K factors are different summation orders of the same product."""
     cfg = so.BertConfig(2, 128, 12, 64, 3072, "std")
