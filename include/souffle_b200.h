@@ -63,7 +63,9 @@ typedef struct SouffleBertDesc {
   int32_t ffn;        /* intermediate size, multiple of 64 */
   int32_t n_layers;   /* >= 1: layers chained inside one launch */
   int32_t variant;    /* SouffleBertVariant */
-  int32_t keep_probs; /* 1: also materialise softmax probabilities of the LAST layer (parity output) */
+  int32_t keep_probs; /* 1: parity mode: the softmax probabilities of the LAST layer are materialised and that layer's
+                         stage outputs stay readable (souffle_bert_plan_buffer); 0: intermediates are dropped from L2
+                         as soon as their last reader has run and are never written to DRAM */
   float eps;          /* LayerNorm epsilon (applied in fp32) */
   /* Optional tiling overrides, 0 = choose automatically. */
   int32_t bn_qkv, bn_fc1, bn_proj, split_proj, bn_fc2, split_fc2;
@@ -143,7 +145,8 @@ int souffle_bert_forward_host_async(SouffleBertPlan* plan, const void* x_host, c
                                     void* y_host, souffle_stream_t stream);
 
 /* The stage outputs the reference binding returns (cpp/bert/bert_binding.cu:534), for the
- * LAST layer of the plan.  Valid after a forward call has completed. */
+ * LAST layer of a plan created with keep_probs = 1 (other plans do not keep them).  Valid after a forward call
+ * has completed. */
 typedef enum SouffleBertBuffer {
   SOUFFLE_BUF_QKV = 0,   /* fp16 [3][B][heads][S][d]            */
   SOUFFLE_BUF_PROBS = 1, /* fp16 [B*heads][S][S] (keep_probs=1) */

@@ -1579,8 +1579,9 @@ __device__ __noinline__ void ln_row_wide(const __half* row, const __half* gamma,
     uint32_t w0 = pack_h2(fmaf(z[j][0], rstd, nm), fmaf(z[j][1], rstd, nm));
     uint32_t w1 = pack_h2(fmaf(z[j][2], rstd, nm), fmaf(z[j][3], rstd, nm));
     if (gamma) {
-      const uint2 ug = __ldg(reinterpret_cast<const uint2*>(gamma + (lane + 32 * j) * 4));
-      const uint2 ub = __ldg(reinterpret_cast<const uint2*>(beta + (lane + 32 * j) * 4));
+      // plain loads: the vectors may have been staged in shared memory by the caller
+      const uint2 ug = *reinterpret_cast<const uint2*>(gamma + (lane + 32 * j) * 4);
+      const uint2 ub = *reinterpret_cast<const uint2*>(beta + (lane + 32 * j) * 4);
       const __half2 y0 = __hfma2(*reinterpret_cast<const __half2*>(&w0), *reinterpret_cast<const __half2*>(&ug.x),
                                  *reinterpret_cast<const __half2*>(&ub.x));
       const __half2 y1 = __hfma2(*reinterpret_cast<const __half2*>(&w1), *reinterpret_cast<const __half2*>(&ug.y),
@@ -1871,6 +1872,19 @@ __device__ __noinline__ void ln_stage_ool(const Stage& st, const MegaParams& p, 
   ln_stage<true>(st, p, cs, ring, ring_ptr, vec_s, rs, ctl, warp, lane);
 }
 
+// Intermediates that the previous stage read for the last time (the barrier behind it has been passed by every CTA):
+// this CTA's share of their lines is dropped from L2 before anything evicts them to DRAM.  Out of line: a few
+// instructions per thread and stage, whose registers are not charged to the stages.
+__device__ __noinline__ void drop_dead_buffers(const Stage& st) {
+#pragma unroll 1
+  for (int b = 0; b < 2; ++b) {
+    const uint32_t lines = st.dead_bytes[b] >> 7;
+    if (!lines) continue;
+    const char* base = reinterpret_cast<const char*>(st.dead_ptr[b]);
+    for (uint32_t i = blockIdx.x * kThreads + threadIdx.x; i < lines; i += gridDim.x * kThreads) discard_l2_128(base + ((size_t)i << 7));
+  }
+}
+
 template <int kFamily>
 __global__ void __launch_bounds__(kThreads, 1)
 souffle_megakernel(const __grid_constant__ CallArgs ca) {
@@ -1958,6 +1972,7 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
     __syncthreads();
     if (p.prof && threadIdx.x == 0) p.prof[((size_t)si * gridDim.x + blockIdx.x) * kProfSlots + 0] = clock_now();
     const Stage& st = cs.stage;
+    drop_dead_buffers(st);
     if constexpr (kFamily == kFamilySwin) {
       if (st.type == STAGE_GEMM) gemm_stage_ool(st, ca, cs, ring, vec_s, stage_s, rs, ctl, warp, lane);
       else if (st.type == STAGE_ATTN_SWIN) attn_swin_stage(st, ca, cs, ring, ring_ptr, stage_s, rs, ctl, warp, lane);

@@ -412,6 +412,8 @@ struct SouffleBertPlan {
   unsigned launch_id = 0;
   std::vector<Stage> stages;
   std::vector<const void*> stage_weights;   // per stage: the repacked [N][K] weight matrix of a GEMM stage, else null
+  struct Dead { size_t after_stage; const void* ptr; uint32_t bytes; };
+  std::vector<Dead> dead_after;             // buffers nobody reads again once stage `after_stage` has run
   std::vector<CUtensorMap> maps;
   std::vector<void*> allocs;
   Stage* d_stages = nullptr;
@@ -454,6 +456,16 @@ static int upload_program(SouffleBertPlan* p) {
       s.pf_ptr = p->stage_weights[i + 2];
       s.pf_bytes = (uint32_t)((size_t)g.N * g.K * 2) & ~15u;
     }
+    s.dead_bytes[0] = s.dead_bytes[1] = 0;
+    s.dead_ptr[0] = s.dead_ptr[1] = nullptr;
+  }
+  for (const SouffleBertPlan::Dead& dd : p->dead_after) {
+    if (dd.after_stage + 1 >= p->stages.size()) continue;          // nothing runs after it inside the launch
+    Stage& nx = p->stages[dd.after_stage + 1];
+    const int k = nx.dead_bytes[0] ? 1 : 0;
+    if (nx.dead_bytes[k]) continue;                                // both slots taken: the buffer is written back as before
+    nx.dead_ptr[k] = dd.ptr;
+    nx.dead_bytes[k] = dd.bytes;
   }
   if ((rc = plan_alloc(p, (void**)&p->d_stages, p->stages.size() * sizeof(Stage)))) return rc;
   if ((rc = plan_alloc(p, (void**)&p->d_maps, p->maps.size() * sizeof(CUtensorMap)))) return rc;
@@ -477,6 +489,13 @@ static int add_map(SouffleBertPlan* p, const void* ptr, uint64_t rows, uint64_t 
   *idx = (int)p->maps.size();
   p->maps.push_back(m);
   return SOUFFLE_OK;
+}
+
+// Marks `ptr` (`bytes` long) as dead once the stage just appended has run: the stage appended NEXT drops its lines from
+// L2.  Kept in a side table until the program is complete (see upload_program).
+static void note_dead(SouffleBertPlan* p, const void* ptr, size_t bytes) {
+  if (!ptr || bytes < 128 || bytes >= (1ull << 32) || (reinterpret_cast<uintptr_t>(ptr) & 127u)) return;
+  p->dead_after.push_back({p->stages.size() - 1, ptr, (uint32_t)(bytes & ~(size_t)127)});
 }
 
 // Remembers the weight matrix of the stage just appended (for the L2 prefetch, see upload_program).
@@ -740,6 +759,7 @@ static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* la
 
     // layer input / output routing
     const bool first = l == 0, last = l == L - 1;
+    const bool keep = last && d.keep_probs;      // the last layer's stage outputs stay readable for the host (parity mode)
     const int in_map = first ? -1 : m_act[(l - 1) & 1];
     const void* in_ptr = first ? nullptr : p->act[(l - 1) & 1];
     const int in_sel = first ? PTR_CALL_X : PTR_PLAN;
@@ -756,17 +776,21 @@ static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* la
     s.tm_qkv = m_qkv; s.batch = B; s.heads = Hh; s.seq = S; s.head_dim = hd; s.scale = scale;
     s.lens_from_call = 1; s.out = p->ctx; s.probs = (last && d.keep_probs) ? p->probs : nullptr;
     p->stages.push_back(s);
+    if (!keep) note_dead(p, p->qkv, (size_t)3 * M * H * 2);            // Q, K, V: read by the attention stage only
 
     s = blank_stage(STAGE_GEMM);                       // output projection -> fp32 partials
     s.tm_a = m_ctx; s.tm_b = m_wo; s.M = M; s.N = H; s.K = H; s.bm = t_proj.bm; s.bn = bn_proj; s.splitk = sp_proj;
     s.epi = EPI_PARTIAL; s.partial = p->partial;
     p->stages.push_back(s);
     note_weights(p, wo_t);
+    if (!keep) note_dead(p, p->ctx, (size_t)M * H * 2);               // attention output: read by the projection only
 
     s = blank_stage(STAGE_LN);                         // + bias + residual, LayerNorm 1
     s.M = M; s.N = H; s.ldo = H; s.partial = p->partial; s.n_partial = sp_proj; s.bias = proj_b;
     s.resid = in_ptr; s.resid_sel = in_sel; s.out = p->ln1; s.gamma = ln1_g; s.beta = ln1_b; s.eps = d.eps;
     p->stages.push_back(s);
+    note_dead(p, p->partial, (size_t)sp_proj * M * H * 4);             // the projection's planes
+    if (!first) note_dead(p, in_ptr, (size_t)M * H * 2);               // the previous layer's output: QKV and this residual were its readers
 
     s = blank_stage(STAGE_GEMM);                       // FC1 + bias + activation
     s.tm_a = m_ln1; s.tm_b = m_w1; s.M = M; s.N = F; s.K = H; s.bm = t_fc1.bm; s.bn = bn_fc1;
@@ -779,12 +803,17 @@ static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* la
     s.epi = EPI_PARTIAL; s.partial = p->partial;
     p->stages.push_back(s);
     note_weights(p, w2_t);
+    if (!keep) note_dead(p, p->fc1, (size_t)M * F * 2);               // FFN hidden layer: read by FC2 only
 
     s = blank_stage(STAGE_LN);                         // + bias + residual, LayerNorm 2
     s.M = M; s.N = H; s.ldo = H; s.partial = p->partial; s.n_partial = sp_fc2; s.bias = fc2_b;
     s.resid = p->ln1; s.resid_sel = PTR_PLAN; s.out = out_ptr; s.out_sel = out_sel;
     s.gamma = ln2_g; s.beta = ln2_b; s.eps = d.eps;
     p->stages.push_back(s);
+    if (!last) {
+      note_dead(p, p->partial, (size_t)sp_fc2 * M * H * 4);            // FC2's planes
+      note_dead(p, p->ln1, (size_t)M * H * 2);                         // LayerNorm 1 output: FC1 and this residual were its readers
+    }
   }
   if ((int)p->stages.size() > kMaxStages) return fail(SOUFFLE_BAD_SHAPE, "too many stages (%zu)", p->stages.size());
 
@@ -967,6 +996,8 @@ int souffle_bert_plan_buffer(SouffleBertPlan* plan, int which, void** ptr_out, s
     default: return fail(SOUFFLE_BAD_ARGUMENT, "unknown buffer id %d", which);
   }
   if (!ptr) return fail(SOUFFLE_BAD_ARGUMENT, "buffer %d was not requested at plan creation", which);
+  if (!d.keep_probs)
+    return fail(SOUFFLE_BAD_ARGUMENT, "stage outputs are kept readable only by plans created with keep_probs (others drop them from L2 once consumed)");
   *ptr_out = ptr;
   if (bytes_out) *bytes_out = bytes;
   return SOUFFLE_OK;

@@ -68,6 +68,10 @@ struct alignas(16) Stage {      // 16-byte multiples: records are fetched with b
   //      they wait at the barrier that ends this stage (weights never depend on an earlier stage) ----
   uint32_t pf_bytes;
   const void* pf_ptr;
+  // ---- buffers whose last reader was the stage before this one (multiples of 128 bytes, 128-byte aligned): their
+  //      lines are dropped from L2 at the start of this stage, so that dead intermediates are never written to DRAM ----
+  uint32_t dead_bytes[2];
+  const void* dead_ptr[2];
   // ---- derived on the host by finalize_stage(): the kernel's lone producer / MMA lanes would otherwise
   //      spend a few thousand cycles per stage in integer divisions ----
   int tiles_n, kchunks, items, slot_bytes, nslots;
