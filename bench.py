@@ -35,7 +35,7 @@ HIDDEN = HEADS * HEAD_DIM
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the timed kernel, from a one-pass
 # `ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum --clock-control none` capture of this command
 # (64 sequences per GPU) and of its 8-GPU shard size (8 sequences per GPU): {sequences per GPU: bytes}
-DRAM_BYTES_PER_LAUNCH = {64: 459_977_728 + 2_045_136_384, 8: 171_800_000 + 5_400_000}
+DRAM_BYTES_PER_LAUNCH = {64: 333_407_232 + 499_369_728, 8: 171_837_696 + 4_195_584}
 METRIC = "bert_base_12layer_seq128_batch64_sequences_per_second"
 WORKLOAD = "BERT-base 12-layer encoder, batch 64 (sharded by sequence), seq 128, lengths U[32,128]"
 SEED = 1239
@@ -226,7 +226,7 @@ def stage_profile(bert, so, batch: int, mhz: float):
     in microseconds at `mhz`."""
     cfg = so.BertConfig(batch, SEQ, HEADS, HEAD_DIM, FFN, "std")
     layers = [{k: v.cuda() for k, v in w.items()} for w in so.make_bert_weights(cfg, SEED + 2, 1)]
-    enc = bert.BertEncoder(batch, SEQ, HEADS, HEAD_DIM, FFN, layers, tuning={"profile": 1})
+    enc = bert.BertEncoder(batch, SEQ, HEADS, HEAD_DIM, FFN, layers, tuning={"profile": 1, "autotune": 1})
     x, lens = so.make_bert_input(cfg, SEED + 2, ragged=batch > 1)
     xs, ls = x.cuda(), (lens.cuda() if lens is not None else None)
     y = torch.empty_like(xs)

@@ -8,6 +8,7 @@ device memory and streams.
 from __future__ import annotations
 
 import ctypes as C
+import weakref
 from typing import Dict, List, Optional, Sequence, Union
 
 import torch
@@ -132,7 +133,7 @@ class BertEncoder:
         return out
 
 
-_layer_cache: Dict[tuple, BertEncoder] = {}
+_layer_cache: Dict[tuple, tuple] = {}    # key -> (plan, weak references to the weight tensors the plan was built from)
 
 
 def souffle_bert_layer(src: torch.Tensor, qkv_weight: torch.Tensor, attn_fc_weight: torch.Tensor,
@@ -145,7 +146,7 @@ def souffle_bert_layer(src: torch.Tensor, qkv_weight: torch.Tensor, attn_fc_weig
     Computes what the reference's fused kernels compute (REF_COMPAT variant).  Every
     opt_level 0..4 runs the same single fused launch; other values raise, where the reference
     prints and returns zeros (bert_binding.cu:529-531).  The plan (repacked weights) is cached
-    on the weights' addresses and versions.
+    for as long as the same weight tensors, unmodified, are passed again.
     """
     if opt_level not in (0, 1, 2, 3, 4):
         raise ValueError(f"opt level {opt_level} not supported")
@@ -156,16 +157,22 @@ def souffle_bert_layer(src: torch.Tensor, qkv_weight: torch.Tensor, attn_fc_weig
     B, S, H = src.shape
     F = feed_forward_fc1_weight.shape[1]
     heads = H // 64
-    key = (B, S, H, F) + tuple((t.data_ptr(), t._version) for t in
-                               (qkv_weight, attn_fc_weight, feed_forward_fc1_weight, feed_forward_fc2_weight))
-    enc = _layer_cache.get(key)
-    if enc is None:
+    weights = (qkv_weight, attn_fc_weight, feed_forward_fc1_weight, feed_forward_fc2_weight)
+    key = (B, S, H, F) + tuple((t.data_ptr(), t._version) for t in weights)
+    hit = _layer_cache.get(key)
+    # an address and a version can come back with other contents once a tensor has been freed: the entry only counts
+    # while the very tensor objects it was built from are alive
+    if hit is not None and not all(r() is t for r, t in zip(hit[1], weights)):
+        _layer_cache.pop(key)[0].close()
+        hit = None
+    if hit is None:
         if len(_layer_cache) >= 4:
-            _layer_cache.pop(next(iter(_layer_cache))).close()
+            _layer_cache.pop(next(iter(_layer_cache)))[0].close()
         w = dict(qkv_w=qkv_weight, proj_w=attn_fc_weight, fc1_w=feed_forward_fc1_weight,
                  fc2_w=feed_forward_fc2_weight)
-        enc = BertEncoder(B, S, heads, 64, F, [w], variant=REF_COMPAT, keep_probs=True)
-        _layer_cache[key] = enc
+        hit = (BertEncoder(B, S, heads, 64, F, [w], variant=REF_COMPAT, keep_probs=True), tuple(weakref.ref(t) for t in weights))
+        _layer_cache[key] = hit
+    enc = hit[0]
     out = enc.forward(src).reshape(B * S, H)
     # the copies of the intermediates are queued behind the launch while it runs; one wait at the end
     outs = [enc.buffer("qkv").reshape(3 * B, heads, S, 64), enc.buffer("probs"), enc.buffer("ctx"),

@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import ctypes as C
+import weakref
 from typing import Dict, Optional
 
 import torch
@@ -56,27 +57,35 @@ class LstmStack:
         _lib.check(self._lib.souffle_lstm_plan_status(self._h))
 
 
-_cache: Dict[tuple, LstmStack] = {}
+_cache: Dict[tuple, tuple] = {}      # key -> (plan, weak references to the weight tensors the plan was built from)
 
 
 def fused_lstm(input_timestep: torch.Tensor, weight_input_wavefront: torch.Tensor,
                weight_state_wavefront: torch.Tensor) -> torch.Tensor:
     """Drop-in for lstm_binding.fused_lstm: fp32 x [1,100,256], fp32 weights [40,256,256] x2 ->
     fp32 [1,100,256].  Weights are stored as fp16 on the device (exact when they are fp16-valued)
-    and the plan is cached on their addresses and versions.  Inputs are consumed one step late,
+    and the plan is cached for as long as the same weight tensors, unmodified, are passed again.  Inputs are consumed one step late,
     as the reference kernel does (lstm_reuse_shared_memory.cu:324-326).  Blocking, like the reference."""
     if not input_timestep.is_cuda:
         raise ValueError("input_timestep must be a CUDA tensor")
     if input_timestep.dim() != 3 or input_timestep.shape[0] != 1:
         raise ValueError("input_timestep must be [1, steps, hidden]")
     steps = input_timestep.shape[1]
-    key = (steps,) + tuple((t.data_ptr(), t._version, tuple(t.shape)) for t in (weight_input_wavefront, weight_state_wavefront))
-    plan = _cache.get(key)
-    if plan is None:
+    weights = (weight_input_wavefront, weight_state_wavefront)
+    key = (steps,) + tuple((t.data_ptr(), t._version, tuple(t.shape)) for t in weights)
+    hit = _cache.get(key)
+    # an address and a version can come back with other contents once a tensor has been freed: the entry only counts
+    # while the very tensor objects it was built from are alive
+    if hit is not None and not all(r() is t for r, t in zip(hit[1], weights)):
+        _cache.pop(key)[0].close()
+        hit = None
+    if hit is None:
         if len(_cache) >= 4:
-            _cache.pop(next(iter(_cache))).close()
-        plan = LstmStack(weight_input_wavefront, weight_state_wavefront, steps, ref_input_delay=True)
-        _cache[key] = plan
+            _cache.pop(next(iter(_cache)))[0].close()
+        hit = (LstmStack(weight_input_wavefront, weight_state_wavefront, steps, ref_input_delay=True),
+               tuple(weakref.ref(t) for t in weights))
+        _cache[key] = hit
+    plan = hit[0]
     y = plan.forward(input_timestep.to(torch.float32).contiguous())
     plan.status()
     return y

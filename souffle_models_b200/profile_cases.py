@@ -10,8 +10,11 @@ python/models/tee:1-2).  The counterpart here:
 
 Every case builds its plan on seeded random parameters, makes 3 warm-up calls and 5 timed ones (CUDA events) and
 prints the mean time per call.  Cases: bert_layer (1 x 128, one layer), bert_base (1 x 128, 12 layers), bert_layer_b64 (64 x 128
-with ragged lengths, one layer), bert_base_b8 and bert_base_b64 (12 layers at 8 and 64 sequences: one GPU's share of
-the 8-GPU and of the 1-GPU benchmark step), bert_layer_s384
+with ragged lengths, one layer), bert_layer_b64_pairs (the same on CTA pairs, desc.pair_mma; set SOUFFLE_PAIR_COOPERATIVE=0
+under Nsight Compute, which cannot capture a launch that is both clustered and cooperative), bert_base_b8 and
+bert_base_b64 (12 layers at 8 and 64 sequences: one GPU's share of the 8-GPU and of the 1-GPU benchmark step),
+gemm_fc1 (one 8192 x 3072 x 768 product through the plan-less GEMM entry: main loop and plain fp16 epilogue alone),
+bert_layer_s384
 (the reference's native shape and numerical variant through the blocking drop-in entry, which also returns the five
 intermediate tensors), bert_layer_s384_plan (the same launch called back to back), lstm (10 x 256, 100 steps), swin_mlp (256 x 512 x 2048),
 swin_pair (14 x 14 x 512, shifts 0 and 3), swin_stage (18 blocks + patch merging), se_module (the reference's ten
@@ -66,10 +69,14 @@ def make_case(name: str):
         x = _h((1, 128, 768), g)
         y = torch.empty_like(x)
         return (lambda: enc.forward(x, None, y)), enc.status
-    if name in ("bert_layer_b64", "bert_base_b8", "bert_base_b64"):
-        n = 1 if name == "bert_layer_b64" else 12
+    if name == "gemm_fc1":
+        a, w = _h((8192, 768), g), _h((768, 3072), g, 0.02)
+        return (lambda: swin.gemm(a, w, check=False)), (lambda: None)
+    if name in ("bert_layer_b64", "bert_layer_b64_pairs", "bert_base_b8", "bert_base_b64"):
+        n = 1 if name.startswith("bert_layer") else 12
         batch = 8 if name == "bert_base_b8" else 64
-        enc = bert.BertEncoder(batch, 128, 12, 64, 3072, _bert_layers(n, 768, 3072, g, True))
+        tuning = dict(pair_mma=1) if name.endswith("_pairs") else None
+        enc = bert.BertEncoder(batch, 128, 12, 64, 3072, _bert_layers(n, 768, 3072, g, True), tuning=tuning)
         x = _h((batch, 128, 768), g)
         lens = torch.randint(32, 129, (batch,), generator=g).to(torch.int32).cuda()
         y = torch.empty_like(x)

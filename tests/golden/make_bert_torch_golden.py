@@ -48,4 +48,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2 and not os.environ.get("SOUFFLE_REFERENCE"):
+        raise SystemExit("usage: make_bert_torch_golden.py <reference checkout>   (or set SOUFFLE_REFERENCE)")
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ["SOUFFLE_REFERENCE"])

@@ -13,11 +13,13 @@ pytestmark = pytest.mark.gpu
 # fp16 outputs after LayerNorm: max-abs 1e-2 against the fp32 golden for one layer, and for a chain of layers
 # against the oracle that rounds what the CUDA path stores in fp16 (emulate_fp16) -- the stated bar.  Against the
 # un-rounded fp32 golden a chain also carries the fp16 rounding of every activation handed from layer to layer
-# (1 ulp at |y| ~ 4 is 4e-3): that comparison is held to the reference test's own final-output tolerance of 2e-2
-# (cpp/bert/test_souffle_bert_layer.py:214) plus an rms bound of 2e-3, and the measured maxima are reported.
+# (1 ulp at |y| ~ 4 is 4e-3).  Measured on a B200: 12 layers at batch 1 6.7e-3; 12 layers at batch 64 1.04e-2 for the
+# worst of the 64 sequences (median sequence 7.3e-3), 9.8e-3 against the fp16-storage oracle.  The fp32-golden
+# comparison of a chain is therefore held to 1.5e-2 (the reference test's own final-output tolerance is 2e-2,
+# cpp/bert/test_souffle_bert_layer.py:214) plus an rms bound of 2e-3, and the measured maxima are reported.
 TOL_LAYER = 1e-2
 TOL_STACK_EMULATED = 1e-2
-TOL_STACK_FP32 = 2e-2
+TOL_STACK_FP32 = 1.5e-2
 
 
 def _report(name, value):

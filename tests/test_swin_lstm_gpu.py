@@ -88,6 +88,24 @@ def test_fused_lstm_drop_in_signature():
     assert (y.cpu() - so.lstm_forward(x, w_in, w_st, ref_input_delay=True)).abs().max() < 5e-3
 
 
+def test_fused_lstm_with_weights_fp16_cannot_represent():
+    """The drop-in entry takes the reference's fp32 weights and keeps them as fp16 on the device
+    (cpp/lstm/lstm_binding.cu:30-37 multiplies in fp32): with weights that are NOT fp16-valued the rounding of the
+    weights is part of the error.  Measured against the fp32 oracle on the unrounded weights."""
+    from souffle_models_b200 import lstm
+    g = torch.Generator().manual_seed(77)
+    w_in = (torch.rand(40, 256, 256, generator=g) - 0.5) / 8.0          # fp32, not rounded to fp16
+    w_st = (torch.rand(40, 256, 256, generator=g) - 0.5) / 8.0
+    x = torch.randn(1, 100, 256, generator=g)
+    assert not torch.equal(w_in, w_in.half().float())
+    y = lstm.fused_lstm(x.cuda(), w_in.cuda(), w_st.cuda())
+    want = so.lstm_forward(x, w_in, w_st, ref_input_delay=True)
+    err = (y.cpu() - want).abs()
+    _report("LSTM 10 x 256 x 100 with fp32 weights stored as fp16: max-abs on hidden states", err.max().item())
+    _report("LSTM 10 x 256 x 100 with fp32 weights stored as fp16: largest |h|", want.abs().max().item())
+    assert err.max() < 5e-3
+
+
 @pytest.mark.parametrize("P,M,N", [(1, 300, 768), (3, 64, 512), (2, 1000, 1024), (1, 5, 128)])
 def test_layernorm_entry_point(P, M, N):
     from souffle_models_b200 import swin
@@ -115,10 +133,9 @@ def test_swin_block_matches_oracle(shift):
     e16 = (y.float().cpu() - so.swin_block(cfg, x, p, shift, emulate_fp16=True)).abs().max().item()
     _report(f"Swin block shift {shift}: max-abs vs fp32 oracle", err.max().item())
     _report(f"Swin block shift {shift}: max-abs vs fp16-storage oracle", e16)
-    # the block's output is the un-normalised residual stream (|y| up to ~6, fp16 ulp 4e-3 there): 1e-2 against the
-    # oracle that rounds what the GPU stores in fp16, 2e-2 against the un-rounded one
+    # the block's output is the un-normalised residual stream (|y| up to ~6, fp16 ulp 4e-3 there); measured 3e-3
     assert e16 < 1e-2
-    assert err.max() < 2e-2 and err.pow(2).mean().sqrt() < 3e-3
+    assert err.max() < 1e-2 and err.pow(2).mean().sqrt() < 2e-3
     y2 = blk.forward(x.cuda())
     blk.status()
     assert torch.equal(y, y2)
@@ -136,7 +153,8 @@ def test_swin_shifted_pair_as_one_launch():
     mid = so.swin_block(cfg, x, ps[0], 0)
     want = so.swin_block(cfg, mid.half().float(), ps[1], 3)       # the block boundary is an fp16 tensor on the GPU
     err = (y.float().cpu() - want).abs()
-    assert err.max() < 3e-2 and err.pow(2).mean().sqrt() < 4e-3
+    _report("Swin shifted pair: max-abs vs fp32 oracle", err.max().item())
+    assert err.max() < 1.5e-2 and err.pow(2).mean().sqrt() < 2e-3
 
 
 def test_swin_block_batch2_window8():
@@ -148,7 +166,8 @@ def test_swin_block_batch2_window8():
     y = blk.forward(x.cuda())
     blk.status()
     want = torch.cat([so.swin_block(cfg, x[:256], p, 4), so.swin_block(cfg, x[256:], p, 4)])
-    assert (y.float().cpu() - want).abs().max() < 2e-2
+    _report("Swin block batch 2, window 8: max-abs vs fp32 oracle", (y.float().cpu() - want).abs().max().item())
+    assert (y.float().cpu() - want).abs().max() < 1e-2
 
 
 @pytest.mark.parametrize("batch,res,dim,heads,window", [(1, 14, 512, 16, 7), (2, 16, 256, 8, 8), (3, 14, 128, 4, 7)])
@@ -170,7 +189,8 @@ def test_swin_stage_with_patch_merging(batch, res, dim, heads, window):
     want = torch.cat([so.swin_patch_merge(cfg, so.swin_block(cfg, x[i * T:(i + 1) * T], p, shift).half().float(), m)
                       for i in range(batch)])
     err = (y.float().cpu() - want).abs()
-    assert err.max() < 2e-2 and err.pow(2).mean().sqrt() < 3e-3
+    _report(f"Swin block + patch merging, dim {dim}: max-abs vs fp32 oracle", err.max().item())
+    assert err.max() < 1.5e-2 and err.pow(2).mean().sqrt() < 3e-3
     y2 = plan.forward(x.cuda())
     plan.status()
     assert torch.equal(y, y2)
@@ -198,8 +218,8 @@ def test_swin_stage3_eighteen_blocks_and_merge():
     _report("Swin stage 3 (18 blocks + merge): max-abs vs fp16-storage oracle", e16.max().item())
     _report("Swin stage 3 (18 blocks + merge): rms vs fp32 oracle", e32.pow(2).mean().sqrt().item())
     assert torch.isfinite(got).all()
-    assert e32.max() < 3e-2 and e32.pow(2).mean().sqrt() < 4e-3
-    assert e16.max() < 3e-2
+    assert e32.max() < 1.5e-2 and e32.pow(2).mean().sqrt() < 3e-3          # measured 5.8e-3 / 1.4e-3
+    assert e16.max() < 1.5e-2                                               # measured 5.2e-3
 
 
 def test_swin_stage_entry_and_merge_shape_errors():
@@ -211,7 +231,7 @@ def test_swin_stage_entry_and_merge_shape_errors():
     y = swin.swin_stage(x.cuda(), [{k: v.cuda() for k, v in p.items()} for p in ps], {k: v.cuda() for k, v in m.items()})
     mid = so.swin_block(cfg, so.swin_block(cfg, x, ps[0], 0).half().float(), ps[1], 3)
     want = so.swin_patch_merge(cfg, mid.half().float(), m)
-    assert y.shape == (49, 1024) and (y.float().cpu() - want).abs().max() < 3e-2
+    assert y.shape == (49, 1024) and (y.float().cpu() - want).abs().max() < 1.5e-2
     big = so.SwinConfig(dim=768, heads=24)
     with pytest.raises(RuntimeError, match="patch merging"):
         swin.SwinBlock(1, 14, 768, 24, 7, 0, {k: v.cuda() for k, v in so.make_swin_params(big, 1).items()},
