@@ -222,8 +222,9 @@ STAGE_NAMES = ("qkv", "attention", "proj", "ln1", "fc1", "fc2", "ln2")
 
 def stage_profile(bert, so, batch: int, mhz: float):
     """Per-stage time of ONE encoder layer at `batch` sequences from the kernel's own stage clocks (desc.profile):
-    median over the CTAs of work (stage start -> the CTA reaches the grid barrier) and barrier wait, in SM cycles and
-    in microseconds at `mhz`."""
+    work (stage start -> the CTA reaches the grid barrier; median over the CTAs and the slowest CTA) and barrier wait
+    (median), in SM cycles, and the median CTA's work + wait in microseconds at `mhz`.  `kernel_us` is the wall clock
+    from the first CTA's entry to the last CTA's exit."""
     cfg = so.BertConfig(batch, SEQ, HEADS, HEAD_DIM, FFN, "std")
     layers = [{k: v.cuda() for k, v in w.items()} for w in so.make_bert_weights(cfg, SEED + 2, 1)]
     enc = bert.BertEncoder(batch, SEQ, HEADS, HEAD_DIM, FFN, layers, tuning={"profile": 1, "autotune": 1})
@@ -236,9 +237,10 @@ def stage_profile(bert, so, batch: int, mhz: float):
     pr = enc.read_profile().double()
     out = {}
     for si, name in enumerate(STAGE_NAMES):
-        work = (pr[si, :, 1] - pr[si, :, 0]).median().item()
+        w = pr[si, :, 1] - pr[si, :, 0]
+        work = w.median().item()
         bar = (pr[si, :, 2] - pr[si, :, 1]).median().item() if si + 1 < len(STAGE_NAMES) else 0.0
-        out[name] = {"work_cycles": work, "barrier_cycles": bar, "us": (work + bar) / mhz}
+        out[name] = {"work_cycles": work, "work_cycles_max": w.max().item(), "barrier_cycles": bar, "us": (work + bar) / mhz}
     k = pr[-1]
     out["kernel_us"] = (k[:, 4].max() - k[:, 3].min()).item() / 1000.0      # first CTA in -> last CTA out, wall clock
     enc.close()
