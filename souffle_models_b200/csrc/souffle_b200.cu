@@ -367,7 +367,22 @@ static int finalize_stage(Stage& s, int max_slots, int grid, bool pair = false) 
     if (s.nslots < 1) return fail(SOUFFLE_BAD_SHAPE, "LayerNorm rows of %d bytes do not fit the staging ring", row_bytes);
     return SOUFFLE_OK;
   }
+  if (s.type == STAGE_ATTN_SWIN) {
+    // The extents the window-attention stage relies on: a window's tokens fit the 64 rows of its Q/K/V/P tiles,
+    // one head's column of the relative-position table fits the staging area as fp32, the two heads of a
+    // 64-column pair exist, and the window-major buffers hold whole 64-row windows.
+    const int tbl = 2 * s.win - 1;
+    if (s.win < 1 || s.win * s.win > 64 || s.seq % s.win || tbl * tbl * 4 > kStageBytes || s.head_dim != 32 || (s.heads & 1) ||
+        s.heads * 32 != s.ldo || s.shift < 0 || s.shift >= s.win)
+      return fail(SOUFFLE_BAD_SHAPE, "window attention: window %d, grid %d, heads %d, row length %d are outside what the stage addresses",
+                  s.win, s.seq, s.heads, s.ldo);
+    return SOUFFLE_OK;
+  }
   if (s.type != STAGE_GEMM) return SOUFFLE_OK;
+  if ((s.epi == EPI_SWIN_QKV || s.epi == EPI_SWIN_PROJ) &&
+      (s.win < 1 || s.win * s.win > 64 || s.seq % s.win || s.heads * 32 != s.ldo ||
+       s.M != (s.epi == EPI_SWIN_QKV ? s.batch * s.seq * s.seq : s.batch * (s.seq / s.win) * (s.seq / s.win) * 64)))
+    return fail(SOUFFLE_BAD_SHAPE, "window-major epilogue: %d rows do not match batch %d, grid %d, window %d", s.M, s.batch, s.seq, s.win);
   if (s.bias && s.epi != EPI_PARTIAL && s.N * 4 > kVecBytes)
     return fail(SOUFFLE_BAD_SHAPE, "a GEMM stage with a bias vector is limited to %d output columns (got %d)", kVecBytes / 4, s.N);
   s.tiles_n = s.N / s.bn;
