@@ -161,7 +161,8 @@ __device__ bool grid_barrier(const MegaParams& p, const WaitCtl& ctl, int where,
     if (fetch) mbar_wait(smem_u32(&cs.rec_full), (uint32_t)where & 1u, ctl, 50);
   }
   __syncthreads();
-  fence_proxy_async();
+  fence_proxy_async_global();     // the other CTAs' global writes (acquired above) before this CTA's TMA and bulk-copy reads
+  fence_proxy_async_smem();       // this thread's accesses to shared memory before the next stage's copies into it
   return *ctl.abort_smem == 0;
 }
 

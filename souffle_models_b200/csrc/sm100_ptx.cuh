@@ -100,7 +100,10 @@ __device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
 // proxies and fences
 // ------------------------------------------------------------------------------------
 // Orders generic-proxy writes (st.global / st.shared) before later async-proxy reads (TMA, tcgen05).
+// The form without a state space measured ~900 cycles on a B200, the two restricted forms 3 and 10: hot paths name
+// the spaces they mean.
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
