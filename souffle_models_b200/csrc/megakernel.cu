@@ -206,6 +206,7 @@ struct EpiCtx {
   const __half* resid;
   __half* out;
   float* partial;
+  const CUtensorMap* tm_out;   // store map of the fp32 planes, or null: plain stores
   bool prof;
 };
 constexpr uint32_t kNoRow = 0xFFFFFFFFu;      // "this row is outside the matrix"
@@ -306,11 +307,39 @@ __device__ __forceinline__ uint32_t epi_col_offset(const Stage& st, const EpiCtx
 // offset is `own`; `so[i]` = output offset of row (8*i + lane/4) of the same 32-row block (staged stores).
 template <bool kSwin>
 __device__ __forceinline__ void epilogue_chunk32(const Stage& st, const EpiCtx& e, uint8_t* sbuf, const uint32_t (&r)[32],
-                                                 uint32_t own, const uint32_t (&so)[4], int col, int lane, unsigned& t_mid) {
+                                                 uint32_t own, const uint32_t (&so)[4], int col, int lane, unsigned& t_mid,
+                                                 uint32_t tma_row, int tma_plane, int& box, int nbox) {
   if (e.epi == EPI_PARTIAL) {
     // fp32 planes: two halves of 16 columns = 64 bytes per row each.  (Storing each thread's own 128-byte
     // row segment directly measured twice as slow: an instruction's cost grows with the lines it touches.)
     if (e.prof) t_mid = (unsigned)clock64();
+    if (e.tm_out) {
+      // Through the TMA: the thread writes its row's 64 bytes into a staging box (the layout of a 64B-swizzled box of
+      // 16 columns x 32 rows) and one lane hands the box to the copy engine.  A warp has `nbox` boxes, used round
+      // robin: two beside the operand ring while the main loop runs, twelve inside the ring for the CTA's last tile
+      // (whose operands have all been consumed) -- a box is rewritten once the copy issued from it has read it.
+      const int sw_w = (lane >> 1) & 3;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint8_t* buf = sbuf + box * kStageWarp;
+        if (lane == 0) {
+          if (nbox == 2) bulk_wait_group_read<1>(); else bulk_wait_group_read<11>();
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          *reinterpret_cast<uint4*>(buf + lane * kStageRow + ((i ^ sw_w) << 4)) =
+              make_uint4(r[16 * half + 4 * i], r[16 * half + 4 * i + 1], r[16 * half + 4 * i + 2], r[16 * half + 4 * i + 3]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && tma_row != kNoRow) {
+          tma_store_3d(e.tm_out, smem_u32(buf), col + 16 * half, (int)tma_row, tma_plane);
+          bulk_commit_group();
+        }
+        box = box + 1 == nbox ? 0 : box + 1;
+      }
+      return;
+    }
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
       uint8_t* rowptr[4];
@@ -588,16 +617,26 @@ __device__ __forceinline__ void gemm_stage(const Stage& st, const CallArgs& ca, 
     e.resid = reinterpret_cast<const __half*>(sel_ptr(st.resid_sel, st.resid, p));
     e.out = reinterpret_cast<__half*>(const_cast<void*>(sel_ptr(st.out_sel, st.out, p)));
     e.partial = st.partial;
+    e.tm_out = (st.epi == EPI_PARTIAL && st.out_tma) ? map_ptr(ca, st.tm_out) : nullptr;
     const bool prof = p.prof != nullptr;
     e.prof = prof;
-    uint8_t* sbuf = stage_s + (warp - 2) * kStageWarp;
+    // a warp's staging: 2 KB of the staging area, or -- for the boxes of TMA stores, which want two buffers -- 4 KB of
+    // the vector area and the staging area taken together (a stage that writes planes stages no bias)
+    uint8_t* sbuf = e.tm_out ? reinterpret_cast<uint8_t*>(vec_s) + (warp - 2) * 2 * kStageWarp : stage_s + (warp - 2) * kStageWarp;
     unsigned t_wait = 0, t_busy = 0, t_tmem = 0, t_math = 0, t_store = 0;   // cycle totals (32 bits are plenty)
     long long t_first = 0;
+    int box = 0;
     for (int item = first_item; item < g.items; item += item_step) {
       int mt, nt, ks;
       gemm_item(st, item, mt, nt, ks);
       const uint32_t acc0 = g.nh == 2 ? 0u : rs.acc;
       bool ok = true;
+      // TMA-store boxes of the CTA's last tile live in the operand ring: once its accumulator is complete every operand
+      // tile of the stage has been consumed, and nothing is loaded before the next stage
+      const bool last_tile = e.tm_out != nullptr && item + item_step >= g.items;
+      uint8_t* tile_sbuf = last_tile ? stage_s - kVecBytes - kRingBytes + (warp - 2) * 12 * kStageWarp : sbuf;
+      const int nbox = last_tile ? 12 : 2;
+      if (last_tile) box = 0;
       for (int h = 0; h < g.nh; ++h) {
         const uint32_t acc = acc0 + (uint32_t)h;
         const unsigned tw = prof ? (unsigned)clock64() : 0u;
@@ -629,7 +668,8 @@ __device__ __forceinline__ void gemm_stage(const Stage& st, const CallArgs& ca, 
             tm = (unsigned)clock64();
             t_tmem += tm - tl;
           }
-          epilogue_chunk32<kSwin>(st, e, sbuf, r, own, so, colbase + c * 32, lane, tmid);
+          epilogue_chunk32<kSwin>(st, e, tile_sbuf, r, own, so, colbase + c * 32, lane, tmid,
+                                  row0 < e.M ? (uint32_t)row0 : kNoRow, ks, box, nbox);
           if (prof) {
             t_math += tmid - tm;
             t_store += (unsigned)clock64() - tmid;
@@ -654,6 +694,11 @@ __device__ __forceinline__ void gemm_stage(const Stage& st, const CallArgs& ca, 
       if (!ok) break;
       if (g.nh == 1) rs.acc ^= 1u;
     }
+    if (e.tm_out && lane == 0) {          // the planes are complete before the CTA reports the stage done
+      bulk_wait_group_all();
+      fence_proxy_async_global();
+    }
+    __syncwarp();
     if (p.prof && warp == 2 && lane == 0) {
       long long* pr = p.prof + ((size_t)st.prof_index * gridDim.x + blockIdx.x) * kProfSlots;
       pr[6] = t_wait;

@@ -111,6 +111,23 @@ static int make_map_uncached(CUtensorMap* m, const void* ptr, uint64_t rows, uin
   return SOUFFLE_OK;
 }
 
+// fp32 planes [planes][rows][cols] as a store target: box = 16 columns x 32 rows x 1 plane (64-byte rows in shared
+// memory, 64B swizzle); rows of a box past `rows` are not written.
+static int make_plane_map(CUtensorMap* m, const void* ptr, uint64_t planes, uint64_t rows, uint64_t cols) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(SOUFFLE_CUDA_ERROR, "cuTensorMapEncodeTiled is not available from the driver");
+  if (!aligned16(ptr) || (cols * 4) % 16 != 0) return fail(SOUFFLE_BAD_POINTER, "tensor map needs 16-byte alignment");
+  cuuint64_t dims[3] = {cols, rows, planes};
+  cuuint64_t strides[2] = {cols * 4, rows * cols * 4};
+  cuuint32_t box[3] = {16, 32, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(SOUFFLE_CUDA_ERROR, "cuTensorMapEncodeTiled (planes) failed with CUresult %d", (int)r);
+  return SOUFFLE_OK;
+}
+
 // ------------------------------------------------------------------------------------
 // weight repack: [K][N] (reference layout) -> [N][K] so the B operand is K-major and any
 // tile width that is a multiple of 16 can be fed to the tensor cores.  Set-up only.
@@ -506,6 +523,24 @@ static int add_map(SouffleBertPlan* p, const void* ptr, uint64_t rows, uint64_t 
   return SOUFFLE_OK;
 }
 
+// The store map of a split-K GEMM stage's planes (see make_plane_map); sets the stage's tm_out / out_tma.
+static int add_plane_map(SouffleBertPlan* p, Stage& s) {
+  if ((int)p->maps.size() >= kMaxTensorMaps) return fail(SOUFFLE_BAD_SHAPE, "too many tensor maps");
+  if (s.N % 16) return SOUFFLE_OK;                     // (cannot happen: tile widths are multiples of 16) plain stores
+  CUtensorMap m;
+  int rc = make_plane_map(&m, s.partial, (uint64_t)s.splitk, (uint64_t)s.M, (uint64_t)s.N);
+  if (rc) return rc;
+  s.out_tma = 1;
+  for (size_t i = 0; i < p->maps.size(); ++i)          // the layers of a stack share their planes: one map serves them all
+    if (memcmp(&p->maps[i], &m, sizeof(m)) == 0) {
+      s.tm_out = (int)i;
+      return SOUFFLE_OK;
+    }
+  s.tm_out = (int)p->maps.size();
+  p->maps.push_back(m);
+  return SOUFFLE_OK;
+}
+
 // Marks `ptr` (`bytes` long) as dead once the stage just appended has run: the stage appended NEXT drops its lines from
 // L2.  Kept in a side table until the program is complete (see upload_program).
 static void note_dead(SouffleBertPlan* p, const void* ptr, size_t bytes) {
@@ -554,6 +589,11 @@ static void autotune_gemm(const Stage& proto, const Stage* ln_proto, const void*
     if (finalize_stage(g, 0, 1, pair)) continue;
     if (make_map_uncached(&args.call_maps[0], a, (uint64_t)proto.M, (uint64_t)proto.K, (uint32_t)(pair ? 128 : t.bm))) continue;
     if (make_map_uncached(&args.call_maps[1], w, (uint64_t)proto.N, (uint64_t)proto.K, (uint32_t)(pair ? t.bn / 2 : t.bn))) continue;
+    if (g.epi == EPI_PARTIAL) {
+      if (make_plane_map(&args.call_maps[2], g.partial, (uint64_t)t.split, (uint64_t)proto.M, (uint64_t)proto.N)) continue;
+      g.tm_out = -3;
+      g.out_tma = 1;
+    }
     int items = stage_items(g) * (pair ? 2 : 1);                // CTAs that have work
     args.p.n_stages = 1;
     if (ln_proto) {
@@ -796,6 +836,7 @@ static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* la
     s = blank_stage(STAGE_GEMM);                       // output projection -> fp32 partials
     s.tm_a = m_ctx; s.tm_b = m_wo; s.M = M; s.N = H; s.K = H; s.bm = t_proj.bm; s.bn = bn_proj; s.splitk = sp_proj;
     s.epi = EPI_PARTIAL; s.partial = p->partial;
+    if ((rc = add_plane_map(p, s))) return rc;
     p->stages.push_back(s);
     note_weights(p, wo_t);
     if (!keep) note_dead(p, p->ctx, (size_t)M * H * 2);               // attention output: read by the projection only
@@ -816,6 +857,7 @@ static int build_bert_plan(SouffleBertPlan* p, const SouffleBertLayerWeights* la
     s = blank_stage(STAGE_GEMM);                       // FC2 -> fp32 partials
     s.tm_a = m_fc1; s.tm_b = m_w2; s.M = M; s.N = H; s.K = F; s.bm = t_fc2.bm; s.bn = bn_fc2; s.splitk = sp_fc2;
     s.epi = EPI_PARTIAL; s.partial = p->partial;
+    if ((rc = add_plane_map(p, s))) return rc;
     p->stages.push_back(s);
     note_weights(p, w2_t);
     if (!keep) note_dead(p, p->fc1, (size_t)M * F * 2);               // FFN hidden layer: read by FC2 only

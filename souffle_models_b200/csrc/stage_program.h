@@ -35,6 +35,8 @@ struct alignas(16) Stage {      // 16-byte multiples: records are fetched with b
   // ---- GEMM ----
   int tm_a;          // tensor-map index of the A operand ([M][K], box 64 x bm); negative = per-call map
   int tm_b;          // tensor-map index of the B operand
+  int tm_out;        // EPI_PARTIAL with out_tma: tensor-map index of the fp32 planes viewed as [splitk][M][N] (box 16 columns x
+  int out_tma;       // 32 rows x 1 plane, 64B swizzle) through which the epilogue stores them; out_tma = 0: plain stores
   int M, N, K;
   int bm;            // tile height: 128, or 256 (two 128-row halves that share each B tile)
   int bn;            // tile width in N (multiple of 16, <= 256, divides N)
