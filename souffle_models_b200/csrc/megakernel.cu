@@ -1733,14 +1733,14 @@ __device__ __forceinline__ void ln_row_direct(const float* pl, int n_partial, in
 // Out of line: its registers are not charged to the stage interpreter.
 __device__ __noinline__ void ln_stage_direct(const Stage& st, const MegaParams& p, int warp, int lane) {
   const int N = st.N, M = st.M, P = st.n_partial, rb = st.bm, n_batches = st.items;
-  if (warp == 0 || warp - 1 >= rb) return;
+  if (warp >= rb) return;
   const __half* resid = reinterpret_cast<const __half*>(sel_ptr(st.resid_sel, st.resid, p));
   __half* out = reinterpret_cast<__half*>(const_cast<void*>(sel_ptr(st.out_sel, st.out, p)));
   const __half* bias = reinterpret_cast<const __half*>(st.bias);
   const __half* gamma = reinterpret_cast<const __half*>(st.gamma);
   const __half* beta = reinterpret_cast<const __half*>(st.beta);
   for (int blk = blockIdx.x; blk < n_batches; blk += gridDim.x) {
-    const int row = blk * rb + warp - 1;
+    const int row = blk * rb + warp;
     if (row >= M) break;
     const float* pl0 = st.partial + (size_t)row * N;
     const __half* ra = resid ? resid + (size_t)row * N : nullptr;
