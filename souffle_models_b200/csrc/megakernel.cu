@@ -27,7 +27,10 @@
 
 namespace souffle {
 
-constexpr int kThreads = 320;               // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
+constexpr int kThreads = 384;               // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue / softmax, warps 10..11 take rows of
+                                            // the LayerNorm stages only (registers are handed out per four warps: a block of
+                                            // ten warps is charged for twelve, so the two extra warps cost nothing)
+constexpr int kEpiWarps = 8, kEpiThreads = kEpiWarps * 32;
 constexpr int kRingBytes = 196608;          // 192 KiB operand ring (4 x 48 KiB, 3 x 64 KiB or 6 x 32 KiB slots)
 constexpr int kCtlBytes = 1024;             // barriers + control words
 constexpr int kVecBytes = 16384;             // per-stage vectors staged in shared memory (a GEMM's bias as fp32: N <= 4096)
@@ -472,10 +475,10 @@ __device__ __forceinline__ void gemm_stage(const Stage& st, const CallArgs& ca, 
   // the stage's bias vector -> shared memory (one global read per CTA instead of one per tile chunk)
   // (done by the epilogue warps alone; the producer and MMA warps start the main loop meanwhile)
   const float* bias_s = nullptr;
-  if (warp >= 2 && st.bias && st.epi != EPI_PARTIAL && st.N * 4 <= kVecBytes) {
+  if (warp >= 2 && warp < 2 + kEpiWarps && st.bias && st.epi != EPI_PARTIAL && st.N * 4 <= kVecBytes) {
     const uint4* src = reinterpret_cast<const uint4*>(st.bias);
     float4* dst = reinterpret_cast<float4*>(vec_s);
-    for (int i = threadIdx.x - 64; i < st.N / 8; i += kThreads - 64) {
+    for (int i = threadIdx.x - 64; i < st.N / 8; i += kEpiThreads) {
       const uint4 u = __ldg(src + i);
       const __half2* h = reinterpret_cast<const __half2*>(&u);
       const float2 f0 = __half22float2(h[0]), f1 = __half22float2(h[1]), f2 = __half22float2(h[2]), f3 = __half22float2(h[3]);
@@ -483,7 +486,7 @@ __device__ __forceinline__ void gemm_stage(const Stage& st, const CallArgs& ca, 
       dst[2 * i + 1] = make_float4(f2.x, f2.y, f3.x, f3.y);
     }
     bias_s = reinterpret_cast<const float*>(vec_s);
-    named_barrier_sync(1, kThreads - 64);
+    named_barrier_sync(1, kEpiThreads);
   }
 
   if (warp == 0) {
@@ -606,7 +609,7 @@ __device__ __forceinline__ void gemm_stage(const Stage& st, const CallArgs& ca, 
       }
     }
     __syncwarp();
-  } else {
+  } else if (warp < 2 + kEpiWarps) {
     // ---------------- epilogue: TMEM -> registers -> global (8 warps: lane quarter x column parity) --
     const int q = warp & 3, cpar = (warp - 2) >> 2;
     const uint32_t tmem = ctl_s.tmem_base + ((uint32_t)(q * 32) << 16);
@@ -834,7 +837,7 @@ __device__ __forceinline__ void attn_stage(const Stage& st, const CallArgs& ca, 
       }
     }
     __syncwarp();
-  } else {
+  } else if (warp < 2 + kEpiWarps) {
     // Both groups of four warps work on the same item: group 0 takes the first half of the 16-key blocks, group 1
     // the second half (a thread of each group owns query row r_in); row maxima and row sums are exchanged through
     // shared memory around two 256-thread barriers.  The output columns are split 32 / 32 likewise.
@@ -1109,7 +1112,7 @@ __device__ __forceinline__ void attn_stage_pp(const Stage& st, const CallArgs& c
       rs.o_bits = obits;
     }
     __syncwarp();
-  } else {
+  } else if (warp < 2 + kEpiWarps) {
     const int g = (warp - 2) >> 2, q = warp & 3;
     const int r_in = q * 32 + lane;
     const uint32_t tmem = ctl_s.tmem_base + ((uint32_t)(q * 32) << 16);
@@ -1769,7 +1772,7 @@ __device__ __forceinline__ void ln_stage(const Stage& st, const MegaParams& p, S
   const __half* gamma = reinterpret_cast<const __half*>(st.gamma);
   const __half* beta = reinterpret_cast<const __half*>(st.beta);
   // Warp 0 only feeds the ring (issuing a bulk copy of tens of KB stalls the issuing thread until the copy
-  // engine has taken the previous ones); warps 1..9 normalise rows, two per warp and round.
+  // engine has taken the previous ones); the other warps normalise rows, two per warp and round.
   constexpr int kComp = kThreads / 32 - 1;
   // Batch geometry comes from the host (finalize_stage): rows per batch -- up to 96 KB so that two batches are
   // in flight, at most two rows per warp, and few enough that every CTA gets work -- buffers, batch count.
@@ -1959,7 +1962,7 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&cs.tmem_full[i]), 1);
       // arrivals of the epilogue: every thread, or (pairs) one per epilogue warp of both CTAs on the leader's barrier
-      mbar_init(smem_u32(&cs.tmem_empty[i]), kPairK ? 2 * (kThreads / 32 - 2) : kThreads - 64);
+      mbar_init(smem_u32(&cs.tmem_empty[i]), kPairK ? 2 * kEpiWarps : kEpiThreads);
       mbar_init(smem_u32(&cs.o_empty[i]), 8);
     }
     mbar_init(smem_u32(&cs.rec_full), 1);
