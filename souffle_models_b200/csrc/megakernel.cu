@@ -1924,13 +1924,16 @@ __device__ __noinline__ void ln_stage_ool(const Stage& st, const MegaParams& p, 
 // Intermediates that the previous stage read for the last time (the barrier behind it has been passed by every CTA):
 // this CTA's share of their lines is dropped from L2 before anything evicts them to DRAM.  Out of line: a few
 // instructions per thread and stage, whose registers are not charged to the stages.
-__device__ __noinline__ void drop_dead_buffers(const Stage& st) {
+// Threads tid0 .. kThreads - 1 of every CTA share the work: all of them in front of a LayerNorm stage, the two spare
+// warps alone in front of the other stages, whose roles then start without it.
+__device__ __noinline__ void drop_dead_buffers(const Stage& st, int tid0) {
+  const int nthr = kThreads - tid0, tid = (int)threadIdx.x - tid0;
 #pragma unroll 1
   for (int b = 0; b < 2; ++b) {
     const uint32_t lines = st.dead_bytes[b] >> 7;
     if (!lines) continue;
     const char* base = reinterpret_cast<const char*>(st.dead_ptr[b]);
-    for (uint32_t i = blockIdx.x * kThreads + threadIdx.x; i < lines; i += gridDim.x * kThreads) discard_l2_128(base + ((size_t)i << 7));
+    for (uint32_t i = blockIdx.x * nthr + tid; i < lines; i += gridDim.x * nthr) discard_l2_128(base + ((size_t)i << 7));
   }
 }
 
@@ -2021,7 +2024,8 @@ souffle_megakernel(const __grid_constant__ CallArgs ca) {
     __syncthreads();
     if (p.prof && threadIdx.x == 0) p.prof[((size_t)si * gridDim.x + blockIdx.x) * kProfSlots + 0] = clock_now();
     const Stage& st = cs.stage;
-    drop_dead_buffers(st);
+    if (st.type == STAGE_LN) drop_dead_buffers(st, 0);
+    else if (warp >= 2 + kEpiWarps) drop_dead_buffers(st, (2 + kEpiWarps) * 32);
     if constexpr (kFamily == kFamilySwin) {
       if (st.type == STAGE_GEMM) gemm_stage_ool(st, ca, cs, ring, vec_s, stage_s, rs, ctl, warp, lane);
       else if (st.type == STAGE_ATTN_SWIN) attn_swin_stage(st, ca, cs, ring, ring_ptr, stage_s, rs, ctl, warp, lane);
