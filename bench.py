@@ -32,10 +32,13 @@ sys.path.insert(0, ROOT)
 
 BATCH, SEQ, HEADS, HEAD_DIM, FFN, LAYERS = 64, 128, 12, 64, 3072, 12
 HIDDEN = HEADS * HEAD_DIM
-# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the timed kernel, from a one-pass
-# `ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum --clock-control none` capture of this command
-# (64 sequences per GPU) and of its 8-GPU shard size (8 sequences per GPU): {sequences per GPU: bytes}
-DRAM_BYTES_PER_LAUNCH = {64: 333_407_232 + 499_369_728, 8: 171_837_696 + 4_195_584}
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the timed kernel at every shard size of this benchmark,
+# {sequences per GPU: bytes}, each from a one-pass capture of the 12-layer launch of that many sequences
+#   ncu --metrics gpu__time_duration.sum,dram__bytes_read.sum,dram__bytes_write.sum --clock-control none \
+#       -k regex:souffle_megakernel -s 4 -c 1 --csv python -m souffle_models_b200.profile_cases bert_base_b<n>
+# (the library as of the commit that introduced this table; tilings chosen by the cycle model, not timed)
+DRAM_BYTES_PER_LAUNCH = {64: 357_393_152 + 494_891_264, 32: 179_636_224 + 19_077_632, 16: 173_738_240 + 4_755_456,
+                         8: 171_836_160 + 4_379_392}
 METRIC = "bert_base_12layer_seq128_batch64_sequences_per_second"
 WORKLOAD = "BERT-base 12-layer encoder, batch 64 (sharded by sequence), seq 128, lengths U[32,128]"
 SEED = 1239

@@ -11,8 +11,8 @@ python/models/tee:1-2).  The counterpart here:
 Every case builds its plan on seeded random parameters, makes 3 warm-up calls and 5 timed ones (CUDA events) and
 prints the mean time per call.  Cases: bert_layer (1 x 128, one layer), bert_base (1 x 128, 12 layers), bert_layer_b64 (64 x 128
 with ragged lengths, one layer), bert_layer_b64_pairs (the same on CTA pairs, desc.pair_mma; set SOUFFLE_PAIR_COOPERATIVE=0
-under Nsight Compute, which cannot capture a launch that is both clustered and cooperative), bert_base_b8 and
-bert_base_b64 (12 layers at 8 and 64 sequences: one GPU's share of the 8-GPU and of the 1-GPU benchmark step),
+under Nsight Compute, which cannot capture a launch that is both clustered and cooperative), bert_base_b<n> (12 layers
+at n sequences, e.g. bert_base_b64, _b32, _b16, _b8: one GPU's share of the benchmark step on 1, 2, 4 and 8 GPUs),
 gemm_fc1 (one 8192 x 3072 x 768 product through the plan-less GEMM entry: main loop and plain fp16 epilogue alone),
 bert_layer_s384
 (the reference's native shape and numerical variant through the blocking drop-in entry, which also returns the five
@@ -72,9 +72,9 @@ def make_case(name: str):
     if name == "gemm_fc1":
         a, w = _h((8192, 768), g), _h((768, 3072), g, 0.02)
         return (lambda: swin.gemm(a, w, check=False)), (lambda: None)
-    if name in ("bert_layer_b64", "bert_layer_b64_pairs", "bert_base_b8", "bert_base_b64"):
+    if name in ("bert_layer_b64", "bert_layer_b64_pairs") or (name.startswith("bert_base_b") and name[11:].isdigit()):
         n = 1 if name.startswith("bert_layer") else 12
-        batch = 8 if name == "bert_base_b8" else 64
+        batch = int(name[11:]) if name.startswith("bert_base_b") else 64
         tuning = dict(pair_mma=1) if name.endswith("_pairs") else None
         enc = bert.BertEncoder(batch, 128, 12, 64, 3072, _bert_layers(n, 768, 3072, g, True), tuning=tuning)
         x = _h((batch, 128, 768), g)
