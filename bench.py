@@ -260,7 +260,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     so, cfg, layers, x, lens = make_workload(per)
     xs, ls = sharding.shard_batch(x, lens, rank, world)
     dev_layers = [{k: v.cuda() for k, v in w.items()} for w in layers]
-    enc = bert.BertEncoder(per, SEQ, HEADS, HEAD_DIM, FFN, dev_layers, tuning={"autotune": 1})
+    # every rank runs the same tilings (rank 0 times them, the others take its choice): identical work per rank, and
+    # outputs that do not depend on which rank computed a sequence
+    enc = sharding.encoder_with_common_tiling(
+        lambda tuning: bert.BertEncoder(per, SEQ, HEADS, HEAD_DIM, FFN, dev_layers, tuning=tuning), rank, world)
     x_d, l_d = xs.cuda(), ls.cuda()
     y_d = torch.empty_like(x_d)
     full = torch.empty(BATCH, SEQ, HIDDEN, dtype=torch.float16, device="cuda") if world > 1 else None

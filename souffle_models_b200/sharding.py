@@ -43,6 +43,33 @@ def gather_outputs(local: torch.Tensor, out: Optional[torch.Tensor] = None,
     return out
 
 
+_TILE_KEYS = ("bm_qkv", "bn_qkv", "bm_proj", "bn_proj", "split_proj", "bm_fc1", "bn_fc1", "bm_fc2", "bn_fc2", "split_fc2")
+
+
+def encoder_with_common_tiling(build, rank: int, world: int, group=None):
+    """One encoder per rank, all with the SAME tilings: `build(tuning)` makes a `bert.BertEncoder` for this rank's shard.
+
+    Rank 0 lets the library time the candidate tilings on its device (tuning autotune = 1) and broadcasts what it
+    chose (tile heights, widths and split-K depths of the four GEMM stages); the other ranks build their plans with
+    those values.  Timing is noisy enough that two ranks would otherwise now and then settle on different split-K
+    depths, and with them on different summation orders: the ranks' outputs for the same sequence would then differ
+    in the last bit, and their step times by a few per cent."""
+    if world == 1:
+        return build({"autotune": 1})
+    dev = "cuda" if dist.get_backend(group) == "nccl" else "cpu"
+    choice = torch.zeros(len(_TILE_KEYS), dtype=torch.int64, device=dev)
+    enc = None
+    if rank == 0:
+        enc = build({"autotune": 1})
+        q, p, f1, f2 = (enc.stage_info(i) for i in (0, 2, 4, 5))      # QKV, proj, FC1, FC2 of the first layer
+        choice = torch.tensor([q["bm"], q["bn"], p["bm"], p["bn"], p["splitk"], f1["bm"], f1["bn"], f2["bm"], f2["bn"],
+                               f2["splitk"]], dtype=torch.int64, device=dev)
+    dist.broadcast(choice, 0, group=group)
+    if rank != 0:
+        enc = build(dict(zip(_TILE_KEYS, (int(v) for v in choice.tolist()))))
+    return enc
+
+
 class ShardedHostPipeline:
     """One rank's end-to-end step of the sharded encoder with HOST buffers on both sides:
 

@@ -37,6 +37,20 @@ def _worker(rank, world, port, ret):
             gathered = pipe.step(xs, ls, out)
         pipe.drain()
         ok = ok and bool(torch.equal(gathered, x * 2 + 1)) and bool(torch.equal(out, xs * 2 + 1))
+        # common tilings: rank 0 "times" them, the other rank is built from its choice
+
+        class FakeEncoder:
+            def __init__(self, tuning):
+                self.tuning = tuning
+
+            def stage_info(self, i):
+                return {0: dict(bm=128, bn=256, splitk=1), 2: dict(bm=256, bn=192, splitk=1), 4: dict(bm=128, bn=256, splitk=1),
+                        5: dict(bm=256, bn=192, splitk=2)}[i]
+
+        enc = sharding.encoder_with_common_tiling(FakeEncoder, rank, world)
+        want = dict(bm_qkv=128, bn_qkv=256, bm_proj=256, bn_proj=192, split_proj=1, bm_fc1=128, bn_fc1=256, bm_fc2=256,
+                    bn_fc2=192, split_fc2=2)
+        ok = ok and enc.tuning == ({"autotune": 1} if rank == 0 else want)
         ret[rank] = ok
     finally:
         dist.destroy_process_group()
