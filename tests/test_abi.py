@@ -85,9 +85,10 @@ def test_persistent_kernels_do_not_spill():
     for k, (regs, st, ld) in {**mega, **lstm, **stages}.items():
         # A kernel may keep a few words of its per-stage dispatcher on the stack across its calls of out-of-line
         # functions: that code runs once per stage.  The stage functions themselves must stay clean.
-        limit = 32 if "souffle_megakernel" in k else 0
+        # (the opt-in CTA-pair build, ILi3E, is allowed twice that)
+        limit = (64 if "ILi3E" in k else 32) if "souffle_megakernel" in k else 0
         assert st <= limit and ld <= limit, f"{k} spills ({st} B stores, {ld} B loads, {regs} registers)"
-    assert all(v[0] <= 168 for v in mega.values())    # 320 threads per CTA leave 168 registers per thread
+    assert all(v[0] <= 168 for v in mega.values())    # 384 threads per CTA leave 168 registers per thread
 
 
 def test_packed_parameter_block_layout():
