@@ -1463,6 +1463,7 @@ static int build_swin_plan(SouffleSwinPlan* sp, const SouffleSwinWeights* blocks
     s = blank_stage(STAGE_GEMM);                           // FC2 -> fp32 planes
     s.tm_a = m_hid; s.tm_b = m_w2; s.M = T; s.N = C; s.K = F; s.bm = t_fc2.bm; s.bn = t_fc2.bn; s.splitk = t_fc2.split;
     s.epi = EPI_PARTIAL; s.partial = planes; s.ldo = C;
+    if ((rc = add_plane_map(p, s))) return rc;
     p->stages.push_back(s);
     note_weights(p, w2_t);
     s = blank_stage(STAGE_LN);                             // planes + bias + x1 -> block output (no normalisation)
@@ -1495,6 +1496,7 @@ static int build_swin_plan(SouffleSwinPlan* sp, const SouffleSwinWeights* blocks
     s = blank_stage(STAGE_GEMM);                             // reduction -> fp32 planes
     s.tm_a = m_merged; s.tm_b = m_wr; s.M = Tm; s.N = C2; s.K = C4; s.bm = t_red.bm; s.bn = t_red.bn; s.splitk = t_red.split;
     s.epi = EPI_PARTIAL; s.partial = planes2; s.ldo = C2;
+    if ((rc = add_plane_map(p, s))) return rc;
     p->stages.push_back(s);
     note_weights(p, wr_t);
     s = blank_stage(STAGE_LN);                               // sum of the planes -> y
