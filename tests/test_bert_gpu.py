@@ -57,6 +57,8 @@ def _err(a, b):
     (1, 128, 12, 3072, False, True),   # benchmark config 1
     (3, 128, 12, 3072, True, False),   # ragged lengths, non-zero biases and affine LayerNorm
     (2, 16, 4, 256, True, False),      # shortest supported sequence
+    (1, 48, 4, 256, False, False),     # 48 rows: the second 32-row box of a stored plane is cut off by the tensor's extent
+    (5, 16, 4, 256, True, False),      # 80 rows, five short sequences inside one 128-row tile
 ])
 def test_layer_matches_fp32_golden(B, S, heads, ffn, ragged, zero_bias):
     cfg = so.BertConfig(B, S, heads, 64, ffn, "std")
