@@ -12,9 +12,10 @@
 //   cpp/swin_transformer/kernels/swin_fused_ffn_m256n2048k512_m256n512k2048.cu:9-769 fc1 -> fc2
 //   cpp/swin_transformer/kernels/gemm_three_stages.h:8-379 and kernels/gemm_k6.cu:9-339 single GEMMs
 //
-// Warp roles (320 threads): warp 0 = TMA producer (one elected lane), warp 1 = MMA issuer and
+// Warp roles (384 threads): warp 0 = TMA producer (one elected lane), warp 1 = MMA issuer and
 // TMEM owner, warps 2..9 = epilogue (warp w reads TMEM lanes 32*(w%4) .. +31; two warps share a
-// lane quarter and take alternate 32-column chunks); warps 2..5 are the attention softmax warps.
+// lane quarter and take alternate 32-column chunks) and attention softmax warps; warps 10..11 are spare:
+// they take LayerNorm rows like every other warp and drop dead buffers from L2 in front of the other stages.
 // Every wait (mbarrier, grid barrier) is bounded by a wall-clock deadline; on expiry the CTA
 // records a status word, drains and returns, so a fault never leaves the GPU spinning.
 #include <cuda.h>
@@ -1899,9 +1900,9 @@ __device__ __forceinline__ void ln_stage(const Stage& st, const MegaParams& p, S
 // ------------------------------------------------------------------------------------
 // the kernel
 // ------------------------------------------------------------------------------------
-// 320 threads leave 168 registers per thread (the register file is handed out per four warps); the
-// epilogue is written to stay below that without spilling.
-// The kernel exists in three builds, so that each fits 168 registers with its stages inlined where that matters:
+// 384 threads leave 168 registers per thread (the register file is handed out per four warps, so ten warps would
+// leave no more); the epilogue is written to stay below that without spilling.
+// The kernel exists in four builds, so that each fits 168 registers with its stages inlined where that matters:
 //   kFamilyBert      BERT layers whose attention items outnumber the CTAs (two-pipeline attention), plain GEMMs,
 //                    LayerNorm; every stage inlined into one register allocation (fastest).
 //   kFamilyBertCoop  the same with the attention stage in which all eight softmax warps share one item: S up to

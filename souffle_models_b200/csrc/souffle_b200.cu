@@ -377,7 +377,7 @@ static int finalize_stage(Stage& s, int max_slots, int grid, bool pair = false) 
     // normalising warp and pass (no staging ring).  Measured faster than the ring at every batch size: twelve layers
     // at 16 sequences 0.87 against 0.93 ms, equal at 64.
     if (s.seq == 0 && s.N <= 1024) {
-      if (per_cta > comp + 1) per_cta = comp + 1;       // all ten warps take a row
+      if (per_cta > comp + 1) per_cta = comp + 1;       // every warp takes a row
       s.bm = per_cta;
       s.items = (s.M + per_cta - 1) / per_cta;
       s.nslots = 0;
